@@ -1,0 +1,151 @@
+"""Compiles the .cu files of this folder for sm_100a, one shared library per file, on first
+use, and loads them with ctypes.
+
+Libraries are built in-tree (`csrc/_build/`) when that folder can be written, else in a
+per-user folder under the system's temporary directory.  A library is named after its
+source and a hash of everything it is built from, so a changed source never loads a stale
+binary.  While nvcc runs, a line is printed now and then so that a first call does not look
+hung.  There is no fallback: a missing compiler or a failed build raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+from typing import Dict
+
+CSRC = Path(__file__).resolve().parent
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "--shared", "-Xcompiler", "-fPIC"]
+HEADERS = ["common.cuh"]
+
+# library name -> source file; every kernel family is its own library so that a model
+# compiles only what it uses.
+LIBRARIES = {
+    "elementwise": "elementwise.cu",
+    "gemm_simt": "gemm_simt.cu",
+    "attention_generic": "attention_generic.cu",
+    "sampling": "sampling.cu",
+    "gemm_bf16": "gemm_bf16.cu",
+    "attention_bf16": "attention_bf16.cu",
+}
+
+_loaded: Dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+
+
+class KernelBuildError(RuntimeError):
+    pass
+
+
+def _say(msg: str) -> None:
+    print(f"[qorvix_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("QORVIX_NVCC"), shutil.which("nvcc"),
+                 os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc"),
+                 "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise KernelBuildError("nvcc was not found (looked at $QORVIX_NVCC, PATH, $CUDA_HOME/bin, /usr/local/cuda/bin); "
+                           "the CUDA kernels cannot be built and there is no fallback")
+
+
+def build_dir() -> Path:
+    override = os.environ.get("QORVIX_BUILD_DIR")
+    cands = [Path(override)] if override else []
+    cands += [CSRC / "_build", Path(tempfile.gettempdir()) / f"qorvix_b200_build_{os.getuid()}"]
+    for d in cands:
+        try:
+            d.mkdir(parents=True, exist_ok=True)
+            probe = d / f".w{os.getpid()}"
+            probe.write_text("")
+            probe.unlink()
+            return d
+        except OSError:
+            continue
+    raise KernelBuildError(f"no writable build folder among {', '.join(map(str, cands))}")
+
+
+def _source_hash(src: Path) -> str:
+    h = hashlib.sha256()
+    for p in [src] + [CSRC / x for x in HEADERS]:
+        h.update(p.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()[:12]
+
+
+def library_path(name: str) -> Path:
+    src = CSRC / LIBRARIES[name]
+    return build_dir() / f"qv_{name}-{_source_hash(src)}.so"
+
+
+def compile_library(name: str, verbose: bool = True) -> Path:
+    """Builds one library if it is not there yet; returns its path."""
+    if name not in LIBRARIES:
+        raise KernelBuildError(f"unknown kernel library '{name}'")
+    src = CSRC / LIBRARIES[name]
+    if not src.is_file():
+        raise KernelBuildError(f"{src} is missing")
+    out = library_path(name)
+    if out.is_file():
+        return out
+    nvcc = find_nvcc()
+    tmp = out.with_name(out.name + f".tmp{os.getpid()}")
+    cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-o", str(tmp), str(src)]
+    if verbose:
+        _say(f"compiling {src.name} for sm_100a ...")
+    t0 = time.time()
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    done = threading.Event()
+
+    def ticker():
+        while not done.wait(10.0):
+            _say(f"  still compiling {src.name} ({time.time() - t0:.0f} s)")
+
+    th = threading.Thread(target=ticker, daemon=True)
+    th.start()
+    log, _ = proc.communicate()
+    done.set()
+    if proc.returncode != 0:
+        try:
+            tmp.unlink()
+        except OSError:
+            pass
+        raise KernelBuildError(f"nvcc failed on {src.name}:\n{log}")
+    os.replace(tmp, out)
+    for old in out.parent.glob(f"qv_{name}-*.so"):      # drop binaries of older sources
+        if old != out:
+            try:
+                old.unlink()
+            except OSError:
+                pass
+    if verbose:
+        _say(f"  built {out.name} in {time.time() - t0:.1f} s")
+    return out
+
+
+def load_library(name: str) -> ctypes.CDLL:
+    """The loaded library, compiled first if need be."""
+    with _lock:
+        lib = _loaded.get(name)
+        if lib is None:
+            path = compile_library(name)
+            try:
+                lib = ctypes.CDLL(str(path))
+            except OSError as e:
+                raise KernelBuildError(f"could not load {path}: {e}") from None
+            _loaded[name] = lib
+        return lib
+
+
+def build_all(verbose: bool = True) -> list:
+    return [compile_library(n, verbose) for n in LIBRARIES if (CSRC / LIBRARIES[n]).is_file()]

@@ -1,0 +1,200 @@
+// Memory-bound kernels of the step: embedding gather, (residual add +) RMSNorm (+ row
+// gather), rotary encoding fused with the paged key/value write, SwiGLU, casts.
+// Formulas follow the reference's CPU ops (runtime/src/ops.cpp:8-13 rmsnorm, :96-100 swiglu,
+// :127-148 split-half rope) and its CUDA twins (cuda/src/cuda_backend.cu:231-340), rebuilt
+// for batches of tokens, a float32 residual stream and a paged cache.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// out[t, :] = table[ids[t], :] as float32 (the residual stream is float32).
+template <typename TW>
+__global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ table,
+                             const int* __restrict__ ids, int d, int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;   // ids are validated on the host; never read out of bounds
+  const TW* row = table + (size_t)id * d;
+  float* o = out + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f(row[i]);
+}
+
+extern "C" int qv_embed(float* out, const void* table, const int* ids, int T, int d, int vocab,
+                        int table_dt, void* stream) {
+  if (T <= 0) return 0;
+  QV_DISPATCH_DT(table_dt, TW,
+                 embed_kernel<TW><<<T, 256, 0, (cudaStream_t)stream>>>(out, (const TW*)table, ids, d, vocab));
+  return qv_launch_status();
+}
+
+// ---------------------------------------------------------------- add + rmsnorm (+ gather)
+// row r reads source row s = row_idx ? row_idx[r] : r.
+//   x = residual[s] + (delta ? delta[s] : 0)        (float32 sum)
+//   if write_residual: residual[s] = x              (only without row_idx)
+//   out[r] = (x * rsqrt(mean(x^2) + eps)) * w
+// One block per row; the row is staged in shared memory so it is read once.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ residual,
+                                   const TD* __restrict__ delta, const float* __restrict__ w,
+                                   const int* __restrict__ row_idx, int d, float eps,
+                                   int write_residual) {
+  extern __shared__ float smem[];
+  float* xs = smem;            // d floats
+  float* red = smem + d;       // 33 floats
+  const int r = blockIdx.x;
+  const int s = row_idx ? row_idx[r] : r;
+  float* res = residual + (size_t)s * d;
+  const TD* dl = delta ? delta + (size_t)s * d : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float x = res[i];
+    if (dl) x += to_f(dl[i]);
+    xs[i] = x;
+    if (write_residual) res[i] = x;
+    ss += x * x;
+  }
+  const float total = block_sum(ss, red);
+  const float scale = 1.0f / sqrtf(total / (float)d + eps);
+  TO* o = out + (size_t)r * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f<TO>(xs[i] * scale * w[i]);
+}
+
+extern "C" int qv_add_rmsnorm(void* out, float* residual, const void* delta, const float* w,
+                              const int* row_idx, int rows, int d, float eps, int write_residual,
+                              int delta_dt, int out_dt, void* stream) {
+  if (rows <= 0) return 0;
+  const size_t smem = (size_t)(d + 33) * sizeof(float);
+  if (smem > 200 * 1024) return QV_ERR_TOO_LARGE;
+  if (row_idx && write_residual) return QV_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH_NORM(TD, TO)                                                                          \
+  do {                                                                                               \
+    if (smem > 48 * 1024)                                                                            \
+      cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                           (int)smem);                                                               \
+    add_rmsnorm_kernel<TD, TO><<<rows, 256, smem, st>>>((TO*)out, residual, (const TD*)delta, w,     \
+                                                        row_idx, d, eps, write_residual);            \
+  } while (0)
+  if (delta_dt == QV_DT_F32 && out_dt == QV_DT_F32) LAUNCH_NORM(float, float);
+  else if (delta_dt == QV_DT_BF16 && out_dt == QV_DT_BF16) LAUNCH_NORM(bf16, bf16);
+  else if (delta_dt == QV_DT_F32 && out_dt == QV_DT_BF16) LAUNCH_NORM(float, bf16);
+  else if (delta_dt == QV_DT_BF16 && out_dt == QV_DT_F32) LAUNCH_NORM(bf16, float);
+  else return QV_ERR_UNSUPPORTED;
+#undef LAUNCH_NORM
+  return qv_launch_status();
+}
+
+// ---------------------------------------------------------------- rotary + paged KV write
+// qkv[t] = [q: H*hd | k: Hkv*hd | v: Hkv*hd] in the compute dtype (row stride `ld`).
+// For token t at position p (table row p holds cos/sin of p*inv_freq[i], i < rot/2):
+//   q heads and k heads: pairs (i, i + rot/2) of the first `rot` dims are rotated
+//   (split-half), the other dims pass through.  q is rewritten in place; the rotated k and
+//   the plain v go to the cache slot of (request, position):
+//   page = block_table[seg, p / page], cache[page][0|1][kv head][p % page][:]
+// If `cache` is null only q and k are rotated in place (k is then written back to qkv).
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int ld, T* __restrict__ cache,
+                                     const float2* __restrict__ cos_sin, int table_rows,
+                                     const int* __restrict__ tok_pos, const int* __restrict__ tok_seg,
+                                     const int* __restrict__ block_table, int max_blocks, int H,
+                                     int Hkv, int hd, int rot, int page) {
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  T* row = qkv + (size_t)t * ld;
+  const int half = rot >> 1;
+  const float2* cs = cos_sin + (size_t)(pos < table_rows ? pos : table_rows - 1) * half;
+  T* kdst = nullptr;
+  T* vdst = nullptr;
+  if (cache) {
+    const int pg = block_table[(size_t)tok_seg[t] * max_blocks + pos / page];
+    const size_t page_elems = (size_t)2 * Hkv * page * hd;
+    kdst = cache + (size_t)pg * page_elems + (size_t)(pos % page) * hd;
+    vdst = kdst + (size_t)Hkv * page * hd;
+  }
+  // rotations: heads 0..H-1 are q, H..H+Hkv-1 are k
+  const int n_rot = (H + Hkv) * half;
+  for (int it = threadIdx.x; it < n_rot; it += blockDim.x) {
+    const int head = it / half, i = it - head * half;
+    T* v = row + (size_t)head * hd;
+    const float a = to_f(v[i]), b = to_f(v[i + half]);
+    const float2 c = cs[i];
+    const float ra = a * c.x - b * c.y;
+    const float rb = a * c.y + b * c.x;
+    if (head < H || !cache) {
+      v[i] = from_f<T>(ra);
+      v[i + half] = from_f<T>(rb);
+    } else {
+      T* kd = kdst + (size_t)(head - H) * page * hd;
+      kd[i] = from_f<T>(ra);
+      kd[i + half] = from_f<T>(rb);
+    }
+  }
+  if (!cache) return;
+  // pass-through dims of k (beyond rot) and all of v
+  const int tail = hd - rot;
+  for (int it = threadIdx.x; it < Hkv * tail; it += blockDim.x) {
+    const int head = it / tail, i = rot + (it - head * tail);
+    kdst[(size_t)head * page * hd + i] = row[(size_t)(H + head) * hd + i];
+  }
+  for (int it = threadIdx.x; it < Hkv * hd; it += blockDim.x) {
+    const int head = it / hd, i = it - head * hd;
+    vdst[(size_t)head * page * hd + i] = row[(size_t)(H + Hkv + head) * hd + i];
+  }
+}
+
+extern "C" int qv_rope_kv_write(void* qkv, int ld, void* cache, const float* cos_sin, int table_rows,
+                                const int* tok_pos, const int* tok_seg, const int* block_table,
+                                int max_blocks, int T, int H, int Hkv, int hd, int rot, int page,
+                                int dt, void* stream) {
+  if (T <= 0) return 0;
+  if (rot < 0 || rot > hd || (rot & 1)) return QV_ERR_UNSUPPORTED;
+  QV_DISPATCH_DT(dt, TT,
+                 rope_kv_write_kernel<TT><<<T, 256, 0, (cudaStream_t)stream>>>(
+                     (TT*)qkv, ld, (TT*)cache, (const float2*)cos_sin, table_rows, tok_pos, tok_seg,
+                     block_table, max_blocks, H, Hkv, hd, rot, page));
+  return qv_launch_status();
+}
+
+// ---------------------------------------------------------------- swiglu
+// gu[t] = [gate: f | up: f] (row stride 2f); out[t, i] = gate/(1+exp(-gate)) * up.
+template <typename T>
+__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, size_t n, int f) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / f;
+    const int i = (int)(idx - t * f);
+    const float g = to_f(gu[t * 2 * f + i]);
+    const float u = to_f(gu[t * 2 * f + f + i]);
+    out[idx] = from_f<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+extern "C" int qv_swiglu(void* out, const void* gu, int T, int f, int dt, void* stream) {
+  const size_t n = (size_t)T * f;
+  if (n == 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  QV_DISPATCH_DT(dt, TT, swiglu_kernel<TT><<<blocks, 256, 0, (cudaStream_t)stream>>>((TT*)out, (const TT*)gu, n, f));
+  return qv_launch_status();
+}
+
+// ---------------------------------------------------------------- casts
+template <typename TI, typename TO>
+__global__ void cast_kernel(TO* __restrict__ out, const TI* __restrict__ in, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_f<TO>(to_f(in[i]));
+}
+
+extern "C" int qv_cast(void* out, const void* in, long long n, int in_dt, int out_dt, void* stream) {
+  if (n <= 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (in_dt == QV_DT_F32 && out_dt == QV_DT_BF16) cast_kernel<float, bf16><<<blocks, 256, 0, st>>>((bf16*)out, (const float*)in, (size_t)n);
+  else if (in_dt == QV_DT_BF16 && out_dt == QV_DT_F32) cast_kernel<bf16, float><<<blocks, 256, 0, st>>>((float*)out, (const bf16*)in, (size_t)n);
+  else return QV_ERR_UNSUPPORTED;
+  return qv_launch_status();
+}
+
+extern "C" const char* qv_error_string(int code) {
+  if (code == QV_ERR_UNSUPPORTED) return "size or dtype not supported by this kernel";
+  if (code == QV_ERR_TOO_LARGE) return "size exceeds what this kernel can hold on chip";
+  return cudaGetErrorString((cudaError_t)code);
+}

@@ -1,0 +1,175 @@
+"""Python face of the CUDA kernels: each function checks its tensors and launches one kernel
+of this folder on torch's current stream.  Nothing here computes on the CPU or calls a
+library kernel; a missing or unbuildable library raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .build import KernelBuildError, load_library
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dt_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, not {dtype}")
+
+
+def _ptr(t):
+    return c_void_p(0) if t is None else c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel operands must live on a CUDA device; there is no CPU path")
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        lib = load_library("elementwise")
+        lib.qv_error_string.restype = ctypes.c_char_p
+        msg = lib.qv_error_string(c_int(rc)).decode()
+        raise KernelError(f"{what}: {msg} (code {rc})")
+
+
+def _i32(t, name):
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+
+
+# ------------------------------------------------------------------ elementwise
+
+def embed(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+    """out[t] (float32) = table[ids[t]]."""
+    _need_cuda(out, table, ids)
+    _i32(ids, "ids")
+    T, d = out.shape
+    assert out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous()
+    assert table.shape[1] == d and ids.numel() >= T
+    rc = load_library("elementwise").qv_embed(_ptr(out), _ptr(table), _ptr(ids), c_int(T), c_int(d),
+                                              c_int(table.shape[0]), c_int(dt_code(table.dtype)), _stream())
+    _check(rc, "embed")
+
+
+def add_rmsnorm(out, residual, delta, weight, eps: float, row_idx=None, write_residual=True) -> None:
+    """x = residual[s] (+ delta[s]); residual[s] = x if write_residual; out[r] = rmsnorm(x) * weight
+    with s = row_idx[r] if row_idx is given, else r.  residual and weight are float32."""
+    _need_cuda(out, residual, delta, weight, row_idx)
+    rows, d = out.shape
+    assert residual.dtype == torch.float32 and weight.dtype == torch.float32
+    assert residual.is_contiguous() and out.is_contiguous() and weight.numel() == d and residual.shape[1] == d
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape == residual.shape
+    if row_idx is not None:
+        _i32(row_idx, "row_idx")
+        assert row_idx.numel() >= rows
+        write_residual = False
+    else:
+        assert residual.shape[0] >= rows
+    ddt = dt_code(delta.dtype) if delta is not None else dt_code(out.dtype)
+    rc = load_library("elementwise").qv_add_rmsnorm(
+        _ptr(out), _ptr(residual), _ptr(delta), _ptr(weight), _ptr(row_idx), c_int(rows), c_int(d),
+        c_float(eps), c_int(1 if (write_residual and delta is not None) else 0), c_int(ddt),
+        c_int(dt_code(out.dtype)), _stream())
+    _check(rc, "add_rmsnorm")
+
+
+def rope_kv_write(qkv, cache_layer, cos_sin, tok_pos, tok_seg, block_table, H, Hkv, hd, rot, page) -> None:
+    """Rotates q (in place) and k, writes k and v of every token into its cache slot.
+    qkv [T, (H+2Hkv)*hd]; cache_layer [pages, 2, Hkv, page, hd] or None; cos_sin [rows, rot/2, 2] float32."""
+    _need_cuda(qkv, cache_layer, cos_sin, tok_pos, tok_seg, block_table)
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1 and qkv.shape[1] == (H + 2 * Hkv) * hd
+    if cos_sin is None:
+        assert rot == 0, "a rotation needs its cos/sin table"
+    else:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] * 2 == rot
+    _i32(tok_pos, "tok_pos"); _i32(tok_seg, "tok_seg"); _i32(block_table, "block_table")
+    if cache_layer is not None:
+        assert cache_layer.dtype == qkv.dtype and cache_layer.is_contiguous()
+        assert tuple(cache_layer.shape[1:]) == (2, Hkv, page, hd)
+    rc = load_library("elementwise").qv_rope_kv_write(
+        _ptr(qkv), c_int(qkv.stride(0)), _ptr(cache_layer), _ptr(cos_sin),
+        c_int(cos_sin.shape[0] if cos_sin is not None else 1),
+        _ptr(tok_pos), _ptr(tok_seg), _ptr(block_table), c_int(block_table.shape[-1]), c_int(T),
+        c_int(H), c_int(Hkv), c_int(hd), c_int(rot), c_int(page), c_int(dt_code(qkv.dtype)), _stream())
+    _check(rc, "rope_kv_write")
+
+
+def swiglu(out, gu) -> None:
+    """gu [T, 2f] = [gate | up] -> out [T, f] = silu(gate) * up."""
+    _need_cuda(out, gu)
+    T, f = out.shape
+    assert gu.shape == (T, 2 * f) and gu.is_contiguous() and out.is_contiguous() and gu.dtype == out.dtype
+    rc = load_library("elementwise").qv_swiglu(_ptr(out), _ptr(gu), c_int(T), c_int(f),
+                                               c_int(dt_code(out.dtype)), _stream())
+    _check(rc, "swiglu")
+
+
+def cast(out, src) -> None:
+    _need_cuda(out, src)
+    assert out.numel() == src.numel() and out.is_contiguous() and src.is_contiguous()
+    rc = load_library("elementwise").qv_cast(_ptr(out), _ptr(src), c_longlong(src.numel()),
+                                             c_int(dt_code(src.dtype)), c_int(dt_code(out.dtype)), _stream())
+    _check(rc, "cast")
+
+
+# ------------------------------------------------------------------ matrix products
+
+def gemm_simt(c, a, w, accumulate=False) -> None:
+    """c[M,N] (+)= a[M,K] @ w[N,K]^T with float32 multiply-adds on the CUDA cores."""
+    _need_cuda(c, a, w)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and c.shape == (M, N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    rc = load_library("gemm_simt").qv_gemm_simt(
+        _ptr(c), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(w.stride(0)),
+        c_int(c.stride(0)), c_int(dt_code(a.dtype)), c_int(dt_code(w.dtype)), c_int(dt_code(c.dtype)),
+        c_int(1 if accumulate else 0), _stream())
+    _check(rc, "gemm_simt")
+
+
+# ------------------------------------------------------------------ attention
+
+def attention_generic(out, q, cache_layer, tok_pos, tok_seg, block_table, H, Hkv, hd, page, window, scale) -> None:
+    """out[t, h*hd:(h+1)*hd] = causal GQA attention of query (t, h) over its request's pages.
+    q may be a column slice of the qkv buffer (row stride given by its stride)."""
+    _need_cuda(out, q, cache_layer, tok_pos, tok_seg, block_table)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == cache_layer.dtype
+    assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (2, Hkv, page, hd)
+    _i32(tok_pos, "tok_pos"); _i32(tok_seg, "tok_seg"); _i32(block_table, "block_table")
+    rc = load_library("attention_generic").qv_attention_generic(
+        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(cache_layer), _ptr(tok_pos),
+        _ptr(tok_seg), _ptr(block_table), c_int(block_table.shape[-1]), c_int(T), c_int(H), c_int(Hkv),
+        c_int(hd), c_int(page), c_int(window), c_float(scale), c_int(dt_code(q.dtype)), _stream())
+    _check(rc, "attention_generic")
+
+
+# ------------------------------------------------------------------ dispatch
+
+def gemm(out, x, w) -> None:
+    """out = x @ w^T with the kernel that fits the dtypes and the shape."""
+    gemm_simt(out, x, w)
+
+
+def attention(out, q, cache_layer, ctx, block_table, H, Hkv, hd, page, window, scale) -> None:
+    """Attention of every token of the step over its request's pages."""
+    attention_generic(out, q, cache_layer, ctx.tok_pos, ctx.tok_seg, block_table, H, Hkv, hd, page, window, scale)

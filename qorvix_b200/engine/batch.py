@@ -1,0 +1,120 @@
+"""One step's batch: requests with their next tokens, flattened for the kernels.
+
+The reference's step is one token of one session (runtime/include/qorvix/runtime/inference_engine.hpp:13-17,
+51); here a step is any mix of segments, a segment being the next n >= 1 tokens of one
+request (n > 1: a portion of a prompt; n = 1: usually a decoded token).  All integer
+arrays of a step travel to the device in one copy from one pinned buffer.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+
+@dataclass
+class StepEntry:
+    """The next `tokens` of request `req_id`; `want` are the places among these tokens whose
+    logits are asked for (may be empty)."""
+    req_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class StepContext:
+    """What parts see of a step.  Device tensors are int32."""
+    num_tokens: int
+    num_segments: int
+    num_wanted: int
+    token_ids: torch.Tensor            # [T]
+    tok_pos: torch.Tensor              # [T] absolute position of each token in its request
+    tok_seg: torch.Tensor              # [T] segment of each token
+    seg_q_start: torch.Tensor          # [S+1] first row of each segment
+    seg_pos0: torch.Tensor             # [S] position of each segment's first token
+    seg_slot: torch.Tensor             # [S] request slot (index into fixed-size state)
+    want_rows: torch.Tensor            # [R] rows whose logits are wanted
+    block_tables: Dict[int, torch.Tensor]      # cache group -> [S, max_blocks]
+    # host copies, for decisions that must not wait for the device
+    seg_len: List[int] = field(default_factory=list)
+    seg_start_pos: List[int] = field(default_factory=list)
+    seg_slots: List[int] = field(default_factory=list)
+    seg_first: List[bool] = field(default_factory=list)     # the request's first portion
+    max_q_len: int = 0
+    max_ctx_len: int = 0
+
+    @property
+    def decode_only(self) -> bool:
+        return self.max_q_len == 1
+
+    def any_block_table(self) -> torch.Tensor:
+        for t in self.block_tables.values():
+            return t
+        return self.seg_pos0.reshape(-1, 1)
+
+
+class BatchBuilder:
+    """Packs the integer arrays of a step into one pinned host buffer and one device buffer."""
+
+    def __init__(self, device, pin: bool = True):
+        self.device = torch.device(device)
+        self._pin = pin and self.device.type == "cuda"
+        self._host: Optional[torch.Tensor] = None
+
+    def _host_buffer(self, n: int) -> torch.Tensor:
+        if self._host is None or self._host.numel() < n:
+            cap = max(1024, 1 << (n - 1).bit_length())
+            self._host = torch.empty(cap, dtype=torch.int32, pin_memory=self._pin)
+        return self._host[:n]
+
+    def build(self, segs: List[dict], group_tables: Dict[int, List[List[int]]], scratch_page: int) -> StepContext:
+        """segs: dicts with tokens, pos0, slot, want, first.  group_tables[g][s] = page ids of
+        segment s in cache group g (-1 entries, given back to the pool, read as the scratch page)."""
+        S = len(segs)
+        T = sum(len(s["tokens"]) for s in segs)
+        R = sum(len(s["want"]) for s in segs)
+        widths = {g: max(1, max((len(t) for t in tabs), default=1)) for g, tabs in group_tables.items()}
+        total = 3 * T + (S + 1) + 2 * S + R + sum(S * w for w in widths.values())
+        host = self._host_buffer(max(total, 1))
+        flat: List[int] = []
+        ids, pos, seg, qstart, pos0, slots, rows = [], [], [], [0], [], [], []
+        for si, s in enumerate(segs):
+            n = len(s["tokens"])
+            ids.extend(s["tokens"])
+            pos.extend(range(s["pos0"], s["pos0"] + n))
+            seg.extend([si] * n)
+            base = qstart[-1]
+            rows.extend(base + w for w in s["want"])
+            qstart.append(base + n)
+            pos0.append(s["pos0"])
+            slots.append(s["slot"])
+        flat = ids + pos + seg + qstart + pos0 + slots + rows
+        offsets = {}
+        for g, tabs in group_tables.items():
+            offsets[g] = len(flat)
+            w = widths[g]
+            for t in tabs:
+                flat.extend((p if p >= 0 else scratch_page) for p in t)
+                flat.extend([scratch_page] * (w - len(t)))
+        host[: len(flat)] = torch.tensor(flat, dtype=torch.int32) if flat else host[:0]
+        dev = host.to(self.device, non_blocking=True) if self.device.type == "cuda" else host.clone()
+        o = 0
+
+        def take(n):
+            nonlocal o
+            v = dev[o:o + n]
+            o += n
+            return v
+
+        token_ids, tok_pos, tok_seg = take(T), take(T), take(T)
+        seg_q_start, seg_pos0, seg_slot, want_rows = take(S + 1), take(S), take(S), take(R)
+        block_tables = {g: dev[offsets[g]: offsets[g] + S * widths[g]].view(S, widths[g]) for g in group_tables}
+        lens = [len(s["tokens"]) for s in segs]
+        return StepContext(
+            num_tokens=T, num_segments=S, num_wanted=R, token_ids=token_ids, tok_pos=tok_pos,
+            tok_seg=tok_seg, seg_q_start=seg_q_start, seg_pos0=seg_pos0, seg_slot=seg_slot,
+            want_rows=want_rows, block_tables=block_tables, seg_len=lens,
+            seg_start_pos=[s["pos0"] for s in segs], seg_slots=[s["slot"] for s in segs],
+            seg_first=[s["first"] for s in segs], max_q_len=max(lens, default=0),
+            max_ctx_len=max((s["pos0"] + len(s["tokens"]) for s in segs), default=0))

@@ -1,0 +1,142 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+It runs only the tokens it is given, as one batch, from the cache that earlier steps
+left; prompt portions stand beside single decoded tokens, cut anywhere.  This is the seam the
+reference calls IInferenceEngine::forward / forwardBatch
+(runtime/include/qorvix/runtime/inference_engine.hpp:36-97), widened from one token of one
+session to any mix of segments.  The scheduler, the generation entry point and the trace
+replay tool all drive the model through this one class.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Dict, Hashable, Iterable, List, Optional, Sequence
+
+import torch
+
+from ..cache import CacheManager, OutOfPages, OutOfSlots
+from ..config import load_config, lookup_architecture
+from ..models.text_model import TextModel
+from ..parts.base import Runtime
+from ..weights import Checkpoint, TensorSource
+from .batch import BatchBuilder, StepContext, StepEntry
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype must be bfloat16 or float32, not {dtype}")
+        return dtype
+    if str(dtype) not in _DTYPES:
+        raise ValueError(f"dtype must be one of {', '.join(_DTYPES)}, not {dtype!r}")
+    return _DTYPES[str(dtype)]
+
+
+class ModelRunner:
+    def __init__(self, model_dir=None, *, config=None, tensors=None, dtype="bfloat16", max_tokens: int = 4096,
+                 page_size: int = 16, max_requests: int = 8, max_model_len: Optional[int] = None,
+                 device="cuda"):
+        """model_dir: folder with config.json and model.safetensors; or config + tensors (a
+        mapping name -> tensor) for a model held in memory.  max_tokens sizes the page pool."""
+        self.device = torch.device(device)
+        _require_cuda(self.device)
+        self.dtype = parse_dtype(dtype)
+        if model_dir is not None:
+            self.config = load_config(model_dir)
+            source = TensorSource(checkpoint=Checkpoint(model_dir), device=self.device,
+                                  compute_dtype=self.dtype, where=str(Path(model_dir) / "model.safetensors"))
+        else:
+            if config is None or tensors is None:
+                raise ValueError("give a model folder, or a configuration together with its tensors")
+            self.config = config
+            source = TensorSource(tensors=tensors, device=self.device, compute_dtype=self.dtype, where="tensors in memory")
+        entry = lookup_architecture(self.config.architecture)
+        self.spec = entry.build_spec(self.config)
+        self.page_size = int(page_size)
+        pool_tokens = -(-int(max_tokens) // self.page_size) * self.page_size
+        limit = self.spec.max_position if self.spec.max_position else pool_tokens
+        self.max_model_len = int(max_model_len) if max_model_len else min(limit, pool_tokens)
+        self.rt = Runtime(device=self.device, dtype=self.dtype, max_positions=self.max_model_len,
+                          page_size=self.page_size)
+        self.model = TextModel(self.spec, source, self.rt)
+        self.cache = CacheManager(self.model.cache_needs(), max_tokens=pool_tokens, page_size=self.page_size,
+                                  max_requests=max_requests, device=self.device, dtype=self.dtype)
+        self.vocab_size = self.spec.vocab_size
+        self._builder = BatchBuilder(self.device)
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # ------------------------------------------------------------------ planning
+    def can_run(self, entries: Sequence[StepEntry]) -> bool:
+        """Whether slots and pages suffice for all entries together (nothing is taken)."""
+        return self.cache.can_reserve([(e.req_id, len(e.tokens)) for e in entries])
+
+    def length(self, req_id) -> int:
+        return self.cache.length(req_id) if self.cache.has(req_id) else 0
+
+    # ------------------------------------------------------------------ the step
+    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Admits new requests, reserves pages for every entry (all or nothing) and builds the
+        step's context.  Raises OutOfPages / OutOfSlots with nothing changed."""
+        seen = set()
+        for e in entries:
+            if e.req_id in seen:
+                raise ValueError(f"request {e.req_id!r} appears twice in one step")
+            seen.add(e.req_id)
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.req_id!r} brings no tokens")
+            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
+            if bad:
+                raise ValueError(f"request {e.req_id!r}: token id {bad[0]} is outside the vocabulary of {self.vocab_size}")
+            if any(not 0 <= int(w) < n for w in e.want):
+                raise ValueError(f"request {e.req_id!r}: a wanted place is outside its {n} tokens")
+            if self.length(e.req_id) + n > self.max_model_len:
+                raise ValueError(f"request {e.req_id!r} would hold {self.length(e.req_id) + n} tokens, "
+                                 f"more than the engine's limit of {self.max_model_len}")
+        if not self.cache.can_reserve([(e.req_id, len(e.tokens)) for e in entries]):
+            new = sum(1 for e in entries if not self.cache.has(e.req_id))
+            if new > self.cache.free_slots():
+                raise OutOfSlots(f"{new} new requests but only {self.cache.free_slots()} free request slots")
+            raise OutOfPages(f"the step needs more pages than the {self.cache.free_pages()} that are free")
+        segs = []
+        for e in entries:
+            first = not self.cache.has(e.req_id)
+            if first:
+                self.cache.admit(e.req_id)
+            ok = self.cache.reserve(e.req_id, len(e.tokens))
+            assert ok, "reservation was checked for the whole step"
+            segs.append(dict(tokens=[int(t) for t in e.tokens], pos0=self.cache.length(e.req_id),
+                             slot=self.cache.slot(e.req_id), want=[int(w) for w in e.want], first=first))
+        tables = {g: [self.cache.block_table(e.req_id, g) for e in entries] for g in self.cache.paged_groups()}
+        return self._builder.build(segs, tables, self.cache.scratch_page)
+
+    def step(self, entries: Sequence[StepEntry], end: Iterable[Hashable] = ()) -> Optional[torch.Tensor]:
+        """Runs one batch.  Returns float32 logits [number of wanted places, vocab] on the device,
+        ordered by entry and then by `want`, or None when nothing is wanted.  Requests in `end`
+        are finished after this step and what they hold is given back."""
+        entries = list(entries)
+        logits = None
+        if entries:
+            ctx = self.prepare(entries)
+            logits = self.model.forward(ctx, self.cache)
+            for e in entries:
+                self.cache.commit(e.req_id, len(e.tokens))
+            self.steps_run += 1
+            self.tokens_run += ctx.num_tokens
+        for req_id in end:
+            self.release(req_id)
+        return logits
+
+    def release(self, req_id) -> None:
+        if self.cache.has(req_id):
+            self.cache.release(req_id)
+
+
+def _require_cuda(device: torch.device) -> None:
+    if device.type != "cuda":
+        raise RuntimeError("qorvix_b200 runs on a CUDA device only (sm_100a); there is no CPU path")
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device is available; qorvix_b200 has no CPU path")

@@ -1,0 +1,58 @@
+"""A decoder assembled from a ModelSpec: embedding, blocks in the spec's order, final norm,
+output head.  It knows nothing of any one architecture; the counterpart of the
+reference's TextModel::forwardFromState (runtime/src/text_model.cpp:133-176) for a batch of
+tokens from several requests.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..csrc import ops
+from ..parts.base import Runtime
+from ..parts.linear import Linear
+from ..parts.registry import build_part
+
+
+class TextModel:
+    def __init__(self, spec, source, rt: Runtime):
+        self.spec = spec
+        self.rt = rt
+        source.check(spec.expected_shapes(), optional=spec.optional_tensors)
+        self.embedding = source.get(spec.embedding)
+        self.blocks = [build_part("block", _BlockView(layer), source, rt) for layer in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm, source, rt)
+        self.lm_head = Linear(source.get(spec.lm_head)) if spec.lm_head is not None else Linear(self.embedding)
+        self.order: List[int] = list(spec.order)
+
+    # what each layer wants of the cache manager: (cache_spec | None, layer it reads from | None)
+    def cache_needs(self):
+        needs = []
+        for b in self.blocks:
+            m = getattr(b, "mixer", None)
+            needs.append((m.cache_spec() if m is not None else None,
+                          m.reads_cache_of() if m is not None else None))
+        return needs
+
+    def forward(self, ctx, cache) -> Optional[torch.Tensor]:
+        """Runs the tokens of `ctx`; returns float32 logits [wanted rows, vocab] (None if none wanted)."""
+        T = ctx.num_tokens
+        residual = torch.empty((T, self.spec.hidden_size), device=self.rt.device, dtype=torch.float32)
+        ops.embed(residual, self.embedding, ctx.token_ids)
+        pending = None
+        for li in self.order:
+            residual, pending = self.blocks[li].forward(residual, pending, ctx, cache.layer_view(li))
+        if ctx.num_wanted == 0:
+            return None
+        h = self.final_norm.add_norm(residual, pending, rows=ctx.want_rows)
+        return self.lm_head(h, out_dtype=torch.float32)
+
+
+class _BlockView:
+    """Lets a LayerSpec be built through the block registry: its `kind` is the arrangement."""
+
+    def __init__(self, layer):
+        self.kind = layer.block
+        self.mixer, self.feed_forward = layer.mixer, layer.feed_forward
+        self.mixer_norm, self.ffn_norm = layer.mixer_norm, layer.ffn_norm

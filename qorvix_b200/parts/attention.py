@@ -1,0 +1,67 @@
+"""Causal grouped-query attention over the paged cache (reference: runtime/src/text_model.cpp:78-116,
+146-158).  q, k and v come from one fused projection; the rotation of q and k and the
+write of k and v into the request's pages are one kernel; attention reads keys and values
+from the pages only, so a prompt portion and a single decoded token take the same path.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.spec import PagedKVSpec
+from ..csrc import ops
+from .base import Mixer
+from .linear import Linear
+from .registry import build_part, register_part
+
+
+class Attention(Mixer):
+    def __init__(self, spec, source, rt):
+        self.spec = spec
+        self.rt = rt
+        self.H, self.Hkv, self.hd = spec.num_heads, spec.num_kv_heads, spec.head_dim
+        if self.H % self.Hkv:
+            raise ValueError(f"num_heads {self.H} is not a multiple of num_kv_heads {self.Hkv}")
+        mats = [source.get(spec.q_proj)]
+        if spec.kv_from is None:
+            mats += [source.get(spec.k_proj), source.get(spec.v_proj)]
+        dt = torch.float32 if any(m.dtype == torch.float32 for m in mats) else mats[0].dtype
+        self.qkv_proj = Linear(torch.cat([m.to(dt) for m in mats], dim=0))
+        del mats
+        self.o_proj = Linear(source.get(spec.o_proj))
+        self.position = build_part("position", spec.position, source, rt)
+        self.window = int(spec.window)
+        self.scale = float(spec.scale)
+
+    def cache_spec(self):
+        if self.spec.kv_from is not None:
+            return None
+        return PagedKVSpec(self.Hkv, self.hd, self.window)
+
+    def reads_cache_of(self):
+        return self.spec.kv_from
+
+    def forward(self, x, ctx, cache):
+        T = x.shape[0]
+        H, Hkv, hd = self.H, self.Hkv, self.hd
+        own_kv = self.spec.kv_from is None
+        qkv = self.qkv_proj(x, out_dtype=self.rt.dtype)                     # [T, (H+2Hkv)*hd] or [T, H*hd]
+        table = self.position.table() if self.position is not None else None
+        bt = ctx.block_tables[cache.group]
+        if own_kv:
+            if table is not None:
+                ops.rope_kv_write(qkv, cache.tensor, table, ctx.tok_pos, ctx.tok_seg, bt, H, Hkv, hd,
+                                  table.shape[1] * 2, cache.page_size)
+            else:
+                if self.position is not None:
+                    self.position.apply(qkv, ctx, H, Hkv, hd)
+                ops.rope_kv_write(qkv, cache.tensor, None, ctx.tok_pos, ctx.tok_seg, bt,
+                                  H, Hkv, hd, 0, cache.page_size)
+        elif self.position is not None:
+            self.position.apply(qkv, ctx, H, 0, hd)
+        out = torch.empty((T, H * hd), device=x.device, dtype=self.rt.dtype)
+        ops.attention(out, qkv[:, : H * hd], cache.tensor, ctx, bt, H, Hkv, hd, cache.page_size,
+                      self.window, self.scale)
+        return self.o_proj(out, out_dtype=self.rt.dtype)
+
+
+register_part("mixer", "attention", Attention)

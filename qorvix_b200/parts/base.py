@@ -1,0 +1,67 @@
+"""The interfaces parts have, and the runtime they are built with.
+
+Mixer         forward(x[T,d], ctx, cache) -> [T,d] in the compute dtype; cache_spec() says what
+              it keeps per request (cache.spec.PagedKVSpec / FixedStateSpec / None);
+              reads_cache_of() names another layer whose cache it reads instead.
+FeedForward   forward(x[T,d], ctx) -> [T,d].
+Norm          add_norm(residual, delta, out=None, rows=None): residual (float32) += delta, returns the
+              normed rows in the compute dtype.  The sum and the norm are computed in float32.
+Position      table() -> float32 [positions, rotary_dim/2, 2] of (cos, sin) if it is a rotation
+              the attention kernels can fuse, else None; apply(qkv, ctx, H, Hkv, hd) rotates q and k
+              in place for mixers that do not fuse it.
+Block         forward(residual, pending, ctx, cache) -> (residual, pending): `pending` is a
+              delta not yet added to the residual stream, so that the next norm adds it in
+              the same pass.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+
+@dataclass
+class Runtime:
+    """What parts need to know about where they run."""
+    device: torch.device
+    dtype: torch.dtype                 # compute dtype: torch.bfloat16 or torch.float32
+    max_positions: int                 # rows of position tables
+    page_size: int = 16
+
+    def empty(self, *shape, dtype=None) -> torch.Tensor:
+        return torch.empty(shape, device=self.device, dtype=dtype or self.dtype)
+
+
+class Mixer:
+    def cache_spec(self):
+        return None
+
+    def reads_cache_of(self) -> Optional[int]:
+        return None
+
+    def forward(self, x, ctx, cache):
+        raise NotImplementedError
+
+
+class FeedForward:
+    def forward(self, x, ctx):
+        raise NotImplementedError
+
+
+class Norm:
+    def add_norm(self, residual, delta, rows=None):
+        raise NotImplementedError
+
+
+class PositionEncoding:
+    def table(self):
+        return None
+
+    def apply(self, qkv, ctx, num_heads, num_kv_heads, head_dim):
+        raise NotImplementedError
+
+
+class Block:
+    def forward(self, residual, pending, ctx, cache):
+        raise NotImplementedError

@@ -1,0 +1,28 @@
+"""y = x W^T, the one matrix product every projection uses.  The kernel is chosen by the
+weight's dtype and the shape: float32 weights run on the CUDA cores in true float32;
+bfloat16 weights run on the tensor-core kernels where the shape allows, else on the same
+CUDA-core kernel with float32 accumulation.  All of them are kernels of this package.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor):
+        assert weight.dim() == 2
+        self.weight = weight.contiguous()
+        self.out_features, self.in_features = weight.shape
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor = None, out_dtype: torch.dtype = None) -> torch.Tensor:
+        M = x.shape[0]
+        if out is None:
+            out = torch.empty((M, self.out_features), device=x.device, dtype=out_dtype or x.dtype)
+        if M == 0:
+            return out
+        ops.gemm(out, x, self.weight)
+        return out
+
+    __call__ = forward

@@ -1,0 +1,31 @@
+"""SwiGLU feed-forward: down(silu(gate x) * up x), dense, no bias
+(reference: runtime/src/text_model.cpp:162-168, runtime/src/ops.cpp:96-100).  gate and up
+are one fused projection."""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import FeedForward
+from .linear import Linear
+from .registry import register_part
+
+
+class SwiGLU(FeedForward):
+    def __init__(self, spec, source, rt):
+        self.rt = rt
+        self.f = int(spec.intermediate_size)
+        g, u = source.get(spec.gate_proj), source.get(spec.up_proj)
+        dt = torch.float32 if (g.dtype == torch.float32 or u.dtype == torch.float32) else g.dtype
+        self.gate_up = Linear(torch.cat([g.to(dt), u.to(dt)], dim=0))
+        del g, u
+        self.down = Linear(source.get(spec.down_proj))
+
+    def forward(self, x, ctx):
+        gu = self.gate_up(x, out_dtype=self.rt.dtype)
+        act = torch.empty((x.shape[0], self.f), device=x.device, dtype=self.rt.dtype)
+        ops.swiglu(act, gu)
+        return self.down(act, out_dtype=self.rt.dtype)
+
+
+register_part("feed_forward", "swiglu", SwiGLU)

@@ -1,0 +1,178 @@
+"""The engine against the plain implementation under every way of cutting and batching."""
+import pytest
+import torch
+
+from helpers import TINY, PlainModel, assert_close_logits, make_model_dir, random_tokens
+from qorvix_b200 import ModelRunner, StepEntry
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+CASES = [("A", 1.0), ("B", 1.0), ("C", 1.0), ("B", 8.0), ("A", 12.0)]
+
+
+@pytest.fixture(scope="module")
+def models():
+    out = {}
+    for name, sharpen in CASES:
+        d = make_model_dir(TINY[name], seed=7 + len(out), sharpen=sharpen)
+        out[(name, sharpen)] = (d, PlainModel(d))
+    return out
+
+
+def _runner(model_dir, dtype, max_tokens, **kw):
+    return ModelRunner(model_dir, dtype=dtype, max_tokens=max_tokens, page_size=16, max_requests=4, **kw)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", CASES)
+def test_whole_requests(models, case, dtype):
+    d, pm = models[case]
+    cfg = TINY[case[0]]
+    r = _runner(d, dtype, 128)
+    for n, seed in ((1, 1), (2, 2), (3, 3), (17, 4), (64, 5), (100, 6)):
+        toks = random_tokens(cfg.vocab_size, n, seed)
+        out = r.step([StepEntry("w", toks, list(range(n)))], end=["w"])
+        assert_close_logits(out, pm.logits(toks), dtype, f"whole n={n}", sharp=case[1] > 1)
+    r.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", CASES)
+def test_prefill_then_decode_last_32(models, case, dtype):
+    d, pm = models[case]
+    cfg = TINY[case[0]]
+    n = 100
+    toks = random_tokens(cfg.vocab_size, n, 11)
+    ref = pm.logits(toks)
+    r = _runner(d, dtype, 128)
+    head = n - 32
+    outs = [r.step([StepEntry("p", toks[:head], list(range(head)))])]
+    for i in range(head, n):
+        outs.append(r.step([StepEntry("p", [toks[i]], [0])]))
+    r.step([], end=["p"])
+    assert_close_logits(torch.cat(outs), ref, dtype, "prefill + 32 decoded", sharp=case[1] > 1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", CASES)
+def test_portions_of_changing_size(models, case, dtype):
+    d, pm = models[case]
+    cfg = TINY[case[0]]
+    toks = random_tokens(cfg.vocab_size, 111, 12)
+    ref = pm.logits(toks)
+    r = _runner(d, dtype, 128)
+    outs, i = [], 0
+    for n in (7, 2, 19, 3, 2, 16, 1, 31, 2, 17, 11):
+        outs.append(r.step([StepEntry("c", toks[i:i + n], list(range(n)))]))
+        i += n
+    assert i == 111
+    r.step([], end=["c"])
+    assert_close_logits(torch.cat(outs), ref, dtype, "portions", sharp=case[1] > 1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", CASES)
+def test_mixed_batches_with_page_reuse(models, case, dtype):
+    """Up to four live requests, portions of some beside decoded tokens of others, in a pool
+    so small (256 tokens) that pages of finished requests are handed to later ones."""
+    d, pm = models[case]
+    cfg = TINY[case[0]]
+    lengths = [70, 45, 100, 33, 90, 64, 21, 58]
+    reqs = {f"r{i}": random_tokens(cfg.vocab_size, n, 100 + i) for i, n in enumerate(lengths)}
+    r = _runner(d, dtype, 256)
+    cursor = {k: 0 for k in reqs}
+    got = {k: [] for k in reqs}
+    waiting = list(reqs)
+    live = []
+    portion_sizes = [13, 2, 24, 5, 16, 3, 30, 7]
+    step = 0
+    pages_seen = set()
+    reused = False
+    while waiting or live:
+        while waiting and len(live) < 4:
+            need = -(-len(reqs[waiting[0]]) // 64) * 64
+            held = sum(-(-len(reqs[k]) // 64) * 64 for k in live)
+            if held + need > 256:
+                break
+            live.append(waiting.pop(0))
+        entries, ends = [], []
+        for j, k in enumerate(live):
+            toks, c = reqs[k], cursor[k]
+            prefill_len = len(toks) - 12           # the last 12 tokens are fed one by one
+            if c < prefill_len:
+                n = min(portion_sizes[(step + j) % len(portion_sizes)], prefill_len - c)
+            else:
+                n = 1
+            if (step + j) % 5 == 4 and len(live) > 1:
+                continue                           # this request sits the step out
+            entries.append(StepEntry(k, toks[c:c + n], list(range(n))))
+        if not entries:
+            step += 1
+            continue
+        for e in entries:
+            if cursor[e.req_id] + len(e.tokens) == len(reqs[e.req_id]):
+                ends.append(e.req_id)
+        out = r.step(entries, end=[])
+        for e in entries:
+            if cursor[e.req_id] == 0 and pages_seen & set(r.cache.block_table(e.req_id, 0)):
+                reused = True
+        row = 0
+        for e in entries:
+            n = len(e.tokens)
+            got[e.req_id].append(out[row:row + n])
+            row += n
+            cursor[e.req_id] += n
+        for k in ends:
+            pages_seen.update(r.cache.block_table(k, 0))
+            r.release(k)
+            live.remove(k)
+        r.cache.check_invariants()
+        step += 1
+    assert reused, "the pool was meant to be small enough for pages to be used again"
+    assert r.cache.free_pages() == 256 // 16
+    for k, toks in reqs.items():
+        assert_close_logits(torch.cat(got[k]), pm.logits(toks), dtype, f"mixed {k}", sharp=case[1] > 1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(models, dtype):
+    d, pm = models[("B", 8.0)]
+    cfg = TINY["B"]
+    toks = random_tokens(cfg.vocab_size, 250, 21)
+    ref = pm.logits(toks)
+    r = _runner(d, dtype, 256)
+    outs = [r.step([StepEntry("l", toks[:5], list(range(5)))])]
+    for i in range(5, 250):
+        outs.append(r.step([StepEntry("l", [toks[i]], [0])]))
+    assert_close_logits(torch.cat(outs), ref, dtype, "long decoding", sharp=True)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_want_subset_and_order(models, dtype):
+    d, pm = models[("A", 12.0)]
+    cfg = TINY["A"]
+    a = random_tokens(cfg.vocab_size, 20, 31)
+    b = random_tokens(cfg.vocab_size, 9, 32)
+    r = _runner(d, dtype, 128)
+    out = r.step([StepEntry("a", a, [19, 0, 7]), StepEntry("b", b, []), StepEntry("c", b[:4], [3])])
+    ref = torch.stack([pm.logits(a)[19], pm.logits(a)[0], pm.logits(a)[7], pm.logits(b[:4])[3]])
+    assert_close_logits(out, ref, dtype, "wanted rows", sharp=True)
+    assert r.step([StepEntry("b", [b[0]], [])]) is None
+
+
+def test_float32_is_bitwise_stable_across_cuts(models):
+    """The 32-bit path accumulates every output in an order fixed by its position alone."""
+    d, _ = models[("B", 8.0)]
+    cfg = TINY["B"]
+    toks = random_tokens(cfg.vocab_size, 80, 41)
+    r = _runner(d, "float32", 256)
+    whole = r.step([StepEntry("x", toks, list(range(80)))], end=["x"])
+    outs, i = [], 0
+    other = random_tokens(cfg.vocab_size, 30, 42)
+    r.step([StepEntry("o", other[:10], [])])
+    for n in (5, 2, 33, 1, 1, 38):
+        res = r.step([StepEntry("o", [other[10 + len(outs)]], [0]), StepEntry("y", toks[i:i + n], list(range(n)))])
+        outs.append(res[1:])
+        i += n
+    assert torch.equal(torch.cat(outs), whole)
