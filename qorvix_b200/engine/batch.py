@@ -60,13 +60,20 @@ class BatchBuilder:
     def __init__(self, device, pin: bool = True):
         self.device = torch.device(device)
         self._pin = pin and self.device.type == "cuda"
-        self._host: Optional[torch.Tensor] = None
+        # The copy to the device is asynchronous, so a pinned buffer may be rewritten only after
+        # its last copy has run: a small ring of buffers, each guarded by an event.
+        self._ring: List[list] = [[None, None] for _ in range(4)]
+        self._turn = 0
 
-    def _host_buffer(self, n: int) -> torch.Tensor:
-        if self._host is None or self._host.numel() < n:
+    def _host_buffer(self, n: int):
+        self._turn = (self._turn + 1) % len(self._ring)
+        slot = self._ring[self._turn]
+        if slot[1] is not None:
+            slot[1].synchronize()
+        if slot[0] is None or slot[0].numel() < n:
             cap = max(1024, 1 << (n - 1).bit_length())
-            self._host = torch.empty(cap, dtype=torch.int32, pin_memory=self._pin)
-        return self._host[:n]
+            slot[0] = torch.empty(cap, dtype=torch.int32, pin_memory=self._pin)
+        return slot[0][:n], slot
 
     def build(self, segs: List[dict], group_tables: Dict[int, List[List[int]]], scratch_page: int) -> StepContext:
         """segs: dicts with tokens, pos0, slot, want, first.  group_tables[g][s] = page ids of
@@ -76,7 +83,7 @@ class BatchBuilder:
         R = sum(len(s["want"]) for s in segs)
         widths = {g: max(1, max((len(t) for t in tabs), default=1)) for g, tabs in group_tables.items()}
         total = 3 * T + (S + 1) + 2 * S + R + sum(S * w for w in widths.values())
-        host = self._host_buffer(max(total, 1))
+        host, ring_slot = self._host_buffer(max(total, 1))
         flat: List[int] = []
         ids, pos, seg, qstart, pos0, slots, rows = [], [], [], [0], [], [], []
         for si, s in enumerate(segs):
@@ -98,7 +105,13 @@ class BatchBuilder:
                 flat.extend((p if p >= 0 else scratch_page) for p in t)
                 flat.extend([scratch_page] * (w - len(t)))
         host[: len(flat)] = torch.tensor(flat, dtype=torch.int32) if flat else host[:0]
-        dev = host.to(self.device, non_blocking=True) if self.device.type == "cuda" else host.clone()
+        if self.device.type == "cuda":
+            dev = host.to(self.device, non_blocking=True)
+            if ring_slot[1] is None:
+                ring_slot[1] = torch.cuda.Event()
+            ring_slot[1].record()
+        else:
+            dev = host.clone()
         o = 0
 
         def take(n):
