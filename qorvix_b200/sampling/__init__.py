@@ -1,0 +1,2 @@
+from .params import SamplingParams
+from .sampler import RequestSamplerState, Sampler

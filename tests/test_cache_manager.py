@@ -1,0 +1,132 @@
+"""The cache manager's bookkeeping (no GPU): no page lost, held twice or freed twice."""
+import random
+
+import pytest
+
+from qorvix_b200.cache import CacheManager, FixedStateSpec, OutOfSlots, PageError, PagedKVSpec, PagePool
+
+KV = PagedKVSpec(num_kv_heads=2, head_dim=16)
+WIN = PagedKVSpec(num_kv_heads=2, head_dim=16, window=40)
+STATE = FixedStateSpec(shape=(4, 8), dtype="float32")
+
+
+def manager(needs, tokens=256, max_requests=4, allocate=False):
+    return CacheManager(needs, max_tokens=tokens, page_size=16, max_requests=max_requests, device="cpu",
+                        allocate=allocate)
+
+
+def test_pool_hands_out_low_ids_first_and_refuses_double_free():
+    p = PagePool(4)
+    assert p.alloc(2) == [0, 1]
+    assert p.alloc(3) is None and p.num_free == 2          # all or nothing
+    p.free([0])
+    assert p.alloc(1) == [0]                               # freed pages are used again at once
+    with pytest.raises(PageError):
+        p.free([3])                                        # never handed out
+    p.free([1])
+    with pytest.raises(PageError):
+        p.free([1])
+
+
+def test_pages_are_taken_on_page_edges():
+    m = manager([(KV, None), (KV, None)])
+    m.admit("a")
+    assert m.reserve("a", 16) and len(m.block_table("a", 0)) == 1
+    m.commit("a", 16)
+    assert m.reserve("a", 1) and len(m.block_table("a", 0)) == 2
+    m.commit("a", 1)
+    assert m.reserve("a", 15) and len(m.block_table("a", 0)) == 2
+    m.commit("a", 15)
+    assert m.length("a") == 32 and m.free_pages() == 14
+    m.check_invariants()
+    m.release("a")
+    assert m.free_pages() == 16
+    m.check_invariants()
+
+
+def test_groups_by_need_and_shared_cache():
+    needs = [(KV, None), (WIN, None), (None, 0), (KV, None), (STATE, None)]
+    m = manager(needs, allocate=True)
+    assert len(m.groups) == 3 and m.groups[0].layers == [0, 3] and m.groups[1].layers == [1]
+    assert m.layer_view(2).group == 0 and m.layer_view(2).tensor.data_ptr() == m.layer_view(0).tensor.data_ptr()
+    assert m.layer_view(4).kind == "state" and tuple(m.layer_view(4).tensor.shape) == (4, 4, 8)
+    assert tuple(m.layer_view(0).tensor.shape) == (17, 2, 2, 16, 16)       # 16 pages + the scratch page
+    with pytest.raises(ValueError):
+        manager([(None, 1), (None, None)])
+
+
+def test_window_pages_go_back_when_the_window_has_passed():
+    m = manager([(KV, None), (WIN, None)])
+    m.admit("a")
+    total = 0
+    for n in (30, 30, 30, 1, 1, 40):
+        assert m.reserve("a", n)
+        m.commit("a", n)
+        total += n
+        full = m.block_table("a", 0)
+        win = m.block_table("a", 1)
+        assert all(p >= 0 for p in full) and len(full) == -(-total // 16)
+        first_needed = max(0, total - 40 + 1)
+        for b, p in enumerate(win):
+            assert (p < 0) == ((b + 1) * 16 <= first_needed)
+        m.check_invariants()
+    assert m.free_pages(1) > m.free_pages(0)
+    m.release("a")
+    assert m.free_pages(0) == 16 and m.free_pages(1) == 16
+
+
+def test_reservation_is_all_or_nothing_over_groups():
+    m = manager([(KV, None), (WIN, None)], tokens=64)
+    m.admit("a"); m.admit("b")
+    assert m.reserve("a", 48); m.commit("a", 48)
+    before = (m.free_pages(0), m.free_pages(1))
+    assert not m.reserve("b", 32)
+    assert (m.free_pages(0), m.free_pages(1)) == before and m.block_table("b", 0) == []
+    assert m.can_reserve([("b", 16)]) and not m.can_reserve([("b", 16), ("a", 1), (None, 1)])
+
+
+def test_state_slots_are_zeroed_on_admission_and_reused():
+    m = manager([(STATE, None)], max_requests=2, allocate=True)
+    s = m.admit("a")
+    m.layer_view(0).tensor[s].fill_(7.0)
+    m.admit("b")
+    with pytest.raises(OutOfSlots):
+        m.admit("c")
+    m.release("a")
+    s2 = m.admit("c")
+    assert s2 == s and float(m.layer_view(0).tensor[s2].abs().sum()) == 0.0
+    m.check_invariants()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_keep_every_page_accounted_for(seed):
+    rng = random.Random(seed)
+    m = manager([(KV, None), (WIN, None), (KV, None)], tokens=320, max_requests=5)
+    live, counter = {}, 0
+    for _ in range(600):
+        op = rng.random()
+        if op < 0.25 and m.free_slots():
+            counter += 1
+            rid = f"r{counter}"
+            m.admit(rid)
+            live[rid] = 0
+        elif op < 0.8 and live:
+            rid = rng.choice(list(live))
+            n = rng.choice([1, 1, 1, 2, 7, 16, 33])
+            before = {g: m.free_pages(g) for g in m.paged_groups()}
+            if m.reserve(rid, n):
+                m.commit(rid, n)
+                live[rid] += n
+                assert m.length(rid) == live[rid]
+            else:
+                assert {g: m.free_pages(g) for g in m.paged_groups()} == before
+        elif live:
+            rid = rng.choice(list(live))
+            m.release(rid)
+            del live[rid]
+            with pytest.raises(KeyError):
+                m.release(rid)
+        m.check_invariants()
+    for rid in list(live):
+        m.release(rid)
+    assert all(m.free_pages(g) == m.num_pages for g in m.paged_groups()) and m.free_slots() == 5

@@ -1,0 +1,136 @@
+"""Generation through the Python entry point, the scheduler on the real engine, the command
+line and bin/trace_run."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TINY, PlainModel, assert_close_logits, make_model_dir, random_tokens
+from qorvix_b200 import LLM, SamplingParams
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def model_b():
+    d = make_model_dir(TINY["B"], seed=3, sharpen=6.0)
+    return d, PlainModel(d)
+
+
+@pytest.fixture(scope="module")
+def model_a():
+    d = make_model_dir(TINY["A"], seed=4, sharpen=10.0)
+    return d, PlainModel(d)
+
+
+def test_greedy_generation_matches_plain_float32(model_b, model_a):
+    for (d, pm), name in ((model_b, "B"), (model_a, "A")):
+        llm = LLM(d, dtype="float32", max_tokens=512, max_concurrent=4, max_batch_tokens=48)
+        prompts = [random_tokens(TINY[name].vocab_size, n, 60 + n) for n in (1, 5, 33, 70)]
+        res = llm.generate(prompts, SamplingParams.greedy_params(max_new_tokens=12))
+        for p, r in zip(prompts, res):
+            assert r.tokens == pm.greedy(p, 12) and r.finish_reason == "max_new_tokens"
+        assert llm.runner.cache.free_pages() == 512 // 16
+
+
+def test_greedy_generation_bfloat16_follows_plain(model_b):
+    d, pm = model_b
+    llm = LLM(d, dtype="bfloat16", max_tokens=512, max_concurrent=4)
+    prompts = [random_tokens(TINY["B"].vocab_size, n, 80 + n) for n in (9, 40)]
+    res = llm.generate(prompts, SamplingParams.greedy_params(max_new_tokens=10))
+    for p, r in zip(prompts, res):
+        want = pm.greedy(p, 10)
+        # the first token comes from the same context in both; later ones may part ways after a near tie
+        full = pm.logits(p)[-1]
+        top2 = torch.topk(full, 2).values
+        if float(top2[0] - top2[1]) > 0.05 * float(full.abs().max()):
+            assert r.tokens[0] == want[0]
+        assert len(r.tokens) == 10
+
+
+def test_preemption_recomputes_to_the_same_tokens(model_b):
+    d, pm = model_b
+    prompts = [random_tokens(TINY["B"].vocab_size, 20, 90 + i) for i in range(3)]
+    roomy = LLM(d, dtype="float32", max_tokens=1024, max_concurrent=3)
+    want = [r.tokens for r in roomy.generate(prompts, SamplingParams.greedy_params(max_new_tokens=40))]
+    tight = LLM(d, dtype="float32", max_tokens=128, max_concurrent=3)       # 8 pages for 3 x 60 tokens
+    res = tight.generate(prompts, SamplingParams.greedy_params(max_new_tokens=40))
+    assert tight.last_stats["preemptions"] >= 1
+    assert [r.tokens for r in res] == want
+    assert want[0] == pm.greedy(prompts[0], 40)
+    assert tight.runner.cache.free_pages() == 8
+
+
+def test_sampling_is_reproducible_and_independent_of_the_batch(model_b):
+    d, _ = model_b
+    llm = LLM(d, dtype="float32", max_tokens=512, max_concurrent=4)
+    p1, p2 = random_tokens(384, 12, 1), random_tokens(384, 30, 2)
+    sp = SamplingParams(temperature=0.9, top_k=20, top_p=0.9, min_p=0.02, seed=7, max_new_tokens=16)
+    alone = llm.generate([p1], sp)[0].tokens
+    again = llm.generate([p1], sp)[0].tokens
+    both = llm.generate([p2, p1], [SamplingParams(seed=9, max_new_tokens=5), sp])[1].tokens
+    other = llm.generate([p1], SamplingParams(temperature=0.9, top_k=20, top_p=0.9, min_p=0.02, seed=8, max_new_tokens=16))[0].tokens
+    assert alone == again == both and len(alone) == 16
+    assert other != alone
+
+
+def test_eos_from_config_stops_generation(model_a):
+    d, pm = model_a
+    prompt = random_tokens(256, 10, 5)
+    free_run = pm.greedy(prompt, 8)
+    eos = free_run[3]
+    llm = LLM(d, dtype="float32", max_tokens=256)
+    llm.eos_token_ids = (eos,)
+    r = llm.generate([prompt], SamplingParams.greedy_params(max_new_tokens=8))[0]
+    cut = free_run.index(eos)
+    assert r.tokens == free_run[:cut] and r.hit_eos and r.finish_reason == "eos"
+
+
+def _run_trace(model_dir, dtype, steps, out_dir, max_tokens):
+    env = dict(os.environ)
+    p = subprocess.run([str(ROOT / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype, "--out", str(out_dir),
+                        "--max-tokens", str(max_tokens)], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    return p.stdout.split("\n")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_b, tmp_path, dtype):
+    d, pm = model_b
+    a, b = random_tokens(384, 70, 11), random_tokens(384, 40, 12)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:50], "want": [0, 49]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[50:52], "want": []}, {"id": "b", "tokens": b[:33], "want": [32]}], "end": []},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[33:], "want": [6]}], "end": ["b"]},
+        {"step": 3, "entries": [{"id": "a", "tokens": a[52:], "want": list(range(18))}], "end": ["a"]},
+        {"step": 4, "entries": [{"id": "c", "tokens": b, "want": [39]}], "end": ["c"]},
+    ]
+    lines = _run_trace(d, dtype, steps, tmp_path, 128)
+    assert [l for l in lines if l.startswith("done")] == [f"done {i}" for i in range(5)]
+    V = 384
+    get = lambda i: torch.from_numpy(np.fromfile(tmp_path / f"{i}.f32", dtype="<f4").reshape(-1, V))
+    assert_close_logits(get(0), pm.logits(a)[[0, 49]], dtype, "step 0", sharp=True)
+    assert_close_logits(get(1), pm.logits(b)[[32]], dtype, "step 1", sharp=True)
+    assert_close_logits(get(2), pm.logits(b)[[39]], dtype, "step 2", sharp=True)
+    assert_close_logits(get(3), pm.logits(a)[52:], dtype, "step 3", sharp=True)
+    assert_close_logits(get(4), pm.logits(b)[[39]], dtype, "step 4", sharp=True)
+
+
+def test_command_line_generate_and_info(model_a):
+    d, pm = model_a
+    prompt = random_tokens(256, 6, 8)
+    p = subprocess.run([sys.executable, str(ROOT / "bin" / "qorvix"), "generate", str(d), "--tokens", ",".join(map(str, prompt)),
+                        "--max", "5", "--temp", "0", "--dtype", "float32"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = p.stdout.strip().split("\n")
+    assert [int(t) for t in lines[1].split()] == pm.greedy(prompt, 5)
+    assert "6 prompt tokens, 5 generated" in p.stdout
+    q = subprocess.run([sys.executable, str(ROOT / "bin" / "qorvix"), "model-info", str(d)], capture_output=True, text=True, timeout=120)
+    assert json.loads(q.stdout)["hidden_size"] == 64

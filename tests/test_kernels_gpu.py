@@ -1,0 +1,243 @@
+"""Each kernel alone against a plain PyTorch float32/float64 reference of the same op, at sizes
+other than the tiny models': widths and vocabularies that are no power of two, head sizes in
+steps of 16, odd numbers of heads and groups."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+from qorvix_b200.csrc import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rnd(*shape, seed=0, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    table = rnd(333, 72, seed=1, dtype=dtype)
+    ids = torch.tensor([0, 332, 5, 5, 100], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 72, device=DEV)
+    ops.embed(out, table, ids)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("d", [72, 1000, 4096, 5120])
+def test_add_rmsnorm(dtype, d):
+    res = rnd(9, d, seed=2)
+    delta = rnd(9, d, seed=3, dtype=dtype)
+    w = rnd(d, seed=4) * 0.1 + 1.0
+    ref_sum = res.double() + delta.double()
+    ref = plain.rmsnorm(ref_sum, w.double(), 1e-6)
+    out = torch.empty(9, d, device=DEV, dtype=dtype)
+    r2 = res.clone()
+    ops.add_rmsnorm(out, r2, delta, w, 1e-6)
+    assert torch.allclose(r2.double(), ref_sum, rtol=1e-6, atol=1e-6)            # the sum is float32
+    assert torch.allclose(out.double(), ref, **tol(dtype))
+    # no delta: the residual stays as it is
+    r3 = res.clone()
+    ops.add_rmsnorm(out, r3, None, w, 1e-6)
+    assert torch.equal(r3, res)
+    assert torch.allclose(out.double(), plain.rmsnorm(res.double(), w.double(), 1e-6), **tol(dtype))
+    # gathered rows: only those are normed, nothing is written back
+    rows = torch.tensor([7, 0, 7], dtype=torch.int32, device=DEV)
+    out3 = torch.empty(3, d, device=DEV, dtype=dtype)
+    r4 = res.clone()
+    ops.add_rmsnorm(out3, r4, delta, w, 1e-6, row_idx=rows)
+    assert torch.equal(r4, res)
+    assert torch.allclose(out3.double(), ref[rows.long()], **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(dtype):
+    gu = rnd(7, 2 * 172, seed=5, dtype=dtype, scale=3.0)
+    out = torch.empty(7, 172, device=DEV, dtype=dtype)
+    ops.swiglu(out, gu)
+    ref = plain.swiglu(gu[:, :172].double(), gu[:, 172:].double())
+    assert torch.allclose(out.double(), ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("dt", [(torch.float32, torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                (torch.bfloat16, torch.bfloat16, torch.float32), (torch.bfloat16, torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("shape", [(1, 100, 72), (5, 331, 200), (70, 64, 172), (130, 257, 1000)])
+def test_gemm_simt(dt, shape):
+    M, N, K = shape
+    a = rnd(M, K, seed=6, dtype=dt[0])
+    w = rnd(N, K, seed=7, dtype=dt[1], scale=0.1)
+    c = torch.empty(M, N, device=DEV, dtype=dt[2])
+    ops.gemm_simt(c, a, w)
+    ref = a.double() @ w.double().t()
+    if dt[2] == torch.float32:
+        assert torch.allclose(c.double(), ref, rtol=1e-5, atol=1e-5 * math.sqrt(K))
+    else:
+        assert torch.allclose(c.double(), ref, rtol=1e-2, atol=1e-2)
+    if dt[2] == torch.float32:
+        c2 = c.clone()
+        ops.gemm_simt(c2, a, w, accumulate=True)
+        assert torch.allclose(c2.double(), 2 * ref, rtol=1e-5, atol=2e-5 * math.sqrt(K))
+
+
+def _paged_setup(dtype, T_ctx, H, Hkv, hd, page, seed, rot=None, n_pages=None, sharp=1.5):
+    """One request of T_ctx tokens whose pages are scattered through the pool.  Inputs have
+    standard deviation `sharp`: 1.5 gives scores of a few units, peaked enough to tell keys apart
+    and small enough that float32 rounding of a score stays below the comparison's bound."""
+    rot = hd if rot is None else rot
+    n_blocks = -(-T_ctx // page)
+    n_pages = n_pages or n_blocks + 5
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed))[:n_blocks]
+    bt = perm.to(torch.int32).reshape(1, -1).to(DEV)
+    qkv = rnd(T_ctx, (H + 2 * Hkv) * hd, seed=seed + 1, dtype=dtype, scale=sharp)
+    cache = torch.zeros(n_pages, 2, Hkv, page, hd, device=DEV, dtype=dtype)
+    pos = torch.arange(T_ctx, dtype=torch.int32, device=DEV)
+    seg = torch.zeros(T_ctx, dtype=torch.int32, device=DEV)
+    inv = plain.plain_inv_freq(rot, 10000.0) if rot else None
+    table = None
+    if rot:
+        ang = torch.arange(T_ctx, dtype=torch.float64)[:, None] * inv[None, :]
+        table = torch.stack([ang.cos(), ang.sin()], -1).float().contiguous().to(DEV)
+    return qkv, cache, bt, pos, seg, table, inv
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv,hd,rot,page", [(4, 4, 16, 16, 16), (6, 2, 48, 48, 16), (5, 1, 80, 32, 32), (8, 2, 128, 128, 64)])
+def test_rope_kv_write(dtype, H, Hkv, hd, rot, page):
+    T = 150
+    qkv, cache, bt, pos, seg, table, inv = _paged_setup(dtype, T, H, Hkv, hd, page, seed=11, rot=rot)
+    src = qkv.clone().double().cpu().reshape(T, H + 2 * Hkv, hd)
+    ops.rope_kv_write(qkv, cache, table, pos, seg, bt, H, Hkv, hd, rot, page)
+    ref_rot = plain.rope(src[:, : H + Hkv, :rot], torch.arange(T), inv)
+    ref = src.clone()
+    ref[:, : H + Hkv, :rot] = ref_rot
+    got_q = qkv[:, : H * hd].double().cpu().reshape(T, H, hd)
+    assert torch.allclose(got_q, ref[:, :H], **tol(dtype))
+    btl = bt[0].tolist()
+    for t in (0, 1, page - 1, page, T - 1):
+        k = cache[btl[t // page], 0, :, t % page, :].double().cpu()
+        v = cache[btl[t // page], 1, :, t % page, :].double().cpu()
+        assert torch.allclose(k, ref[t, H:H + Hkv], **tol(dtype))
+        assert torch.equal(v, src[t, H + Hkv:])
+    # the untouched part of the qkv buffer (k, v) is as it was
+    assert torch.equal(qkv[:, H * hd:].double().cpu().reshape(T, 2 * Hkv, hd), src[:, H:])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv,hd,page,window", [(4, 4, 16, 16, 0), (6, 2, 48, 16, 0), (5, 1, 80, 32, 0),
+                                                  (8, 2, 128, 64, 0), (3, 3, 32, 16, 37), (16, 2, 64, 16, 0)])
+def test_attention_generic(dtype, H, Hkv, hd, page, window):
+    T = 150
+    qkv, cache, bt, pos, seg, table, inv = _paged_setup(dtype, T, H, Hkv, hd, page, seed=21, rot=0)
+    ops.rope_kv_write(qkv, cache, None, pos, seg, bt, H, Hkv, hd, 0, page)
+    out = torch.empty(T, H * hd, device=DEV, dtype=dtype)
+    scale = 1.0 / math.sqrt(hd)
+
+    class Ctx:
+        tok_pos, tok_seg = pos, seg
+    ops.attention_generic(out, qkv[:, : H * hd], cache, pos, seg, bt, H, Hkv, hd, page, window, scale)
+    src = qkv.double().cpu().reshape(T, H + 2 * Hkv, hd)
+    ref = plain.attention(src[:, :H], src[:, H:H + Hkv], src[:, H + Hkv:], window=window).reshape(T, H * hd)
+    assert torch.allclose(out.double().cpu(), ref, **tol(dtype))
+
+
+def test_attention_generic_finds_a_far_key():
+    """One early key is made to match the last query strongly; missing it changes the output wholly."""
+    H, Hkv, hd, page, T = 2, 1, 64, 16, 700
+    qkv, cache, bt, pos, seg, _, _ = _paged_setup(torch.float32, T, H, Hkv, hd, page, seed=31, rot=0, sharp=0.3)
+    q = qkv.view(T, H + 2, hd)
+    q[3, H] = q[T - 1, 0] * 40.0                       # key of position 3 lines up with the last query of head 0
+    q[3, H + 1] = 100.0                                # and its value stands out
+    ops.rope_kv_write(qkv, cache, None, pos, seg, bt, H, Hkv, hd, 0, page)
+    out = torch.empty(T, H * hd, device=DEV)
+    ops.attention_generic(out, qkv[:, : H * hd], cache, pos, seg, bt, H, Hkv, hd, page, 0, 1.0 / 8.0)
+    assert float(out[T - 1, :hd].min()) > 99.0
+    src = qkv.double().cpu().reshape(T, H + 2, hd)
+    ref = plain.attention(src[:, :H], src[:, H:H + 1], src[:, H + 1:]).reshape(T, H * hd)
+    assert torch.allclose(out.double().cpu(), ref, rtol=1e-4, atol=1e-4)
+
+
+def test_argmax_first_maximum_wins():
+    logits = rnd(6, 1001, seed=41)
+    logits[2, 17] = logits[2, 900] = 50.0
+    logits[3] = 0.0
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops.argmax(out, logits)
+    ref = [plain.argmax(row) for row in logits.cpu()]
+    assert out.tolist() == ref and ref[2] == 17 and ref[3] == 0
+
+
+def _sample(logits, temperature, top_k, top_p, min_p, u, recent=None, pens=(1.0, 0.0, 0.0)):
+    rows = logits.shape[0]
+    f = lambda v: torch.full((rows,), float(v), device=DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    uu = torch.tensor(u, dtype=torch.float32, device=DEV) if not isinstance(u, float) else f(u)
+    rc = None
+    if recent is not None:
+        rc = torch.tensor(recent, dtype=torch.int32, device=DEV)
+    ops.sample(out, logits.clone(), f(temperature), torch.full((rows,), top_k, dtype=torch.int32, device=DEV),
+               f(top_p), f(min_p), uu, rc, f(pens[0]) if rc is not None else None,
+               f(pens[1]) if rc is not None else None, f(pens[2]) if rc is not None else None)
+    return out.tolist()
+
+
+@pytest.mark.parametrize("top_k,top_p,min_p", [(0, 1.0, 0.0), (5, 1.0, 0.0), (0, 0.7, 0.0), (0, 1.0, 0.2),
+                                               (40, 0.95, 0.05), (1, 1.0, 0.0), (7, 0.5, 0.1)])
+def test_sampler_draws_only_from_the_reference_candidate_set(top_k, top_p, min_p):
+    V, rows = 777, 64
+    logits = rnd(1, V, seed=51, scale=2.0).repeat(rows, 1)
+    us = [(i + 0.5) / rows for i in range(rows)]
+    got = _sample(logits, 0.9, top_k, top_p, min_p, us)
+    ids, probs = plain.candidate_set(logits[0].cpu().numpy(), 0.9, top_k, top_p, min_p)
+    allowed = set(int(i) for i in ids)
+    assert set(got) <= allowed
+    # inverse CDF in id order over the same set: the draws must follow it exactly
+    order = sorted(allowed)
+    p = {int(i): float(pr) for i, pr in zip(ids, probs)}
+    cdf = np.cumsum([p[i] for i in order]) / sum(p.values())
+    for u, g in zip(us, got):
+        j = int(np.searchsorted(cdf, u, side="right"))
+        assert g == order[min(j, len(order) - 1)] or abs(cdf[min(j, len(cdf) - 1)] - u) < 1e-4 or (j > 0 and abs(cdf[j - 1] - u) < 1e-4)
+
+
+def test_sampler_statistics_follow_the_distribution():
+    V, rows = 50, 4096
+    logits = rnd(1, V, seed=52, scale=1.5).repeat(rows, 1)
+    g = torch.Generator().manual_seed(3)
+    us = torch.rand(rows, generator=g).tolist()
+    got = np.bincount(_sample(logits, 1.0, 0, 1.0, 0.0, us), minlength=V) / rows
+    p = torch.softmax(logits[0].double().cpu(), 0).numpy()
+    assert np.abs(got - p).max() < 0.03
+
+
+def test_sampler_greedy_ties_and_penalties():
+    V = 300
+    logits = torch.zeros(3, V, device=DEV)
+    assert _sample(logits, 0.0, 0, 1.0, 0.0, 0.3) == [0, 0, 0]                 # all equal: lowest id
+    assert _sample(logits, 1.0, 1, 1.0, 0.0, 0.9) == [0, 0, 0]                 # top-k 1 among ties keeps exactly one
+    logits = rnd(2, V, seed=53)
+    logits[:, 10] = 9.0
+    logits[:, 20] = 8.5
+    assert _sample(logits, 0.0, 0, 1.0, 0.0, 0.5) == [10, 10]
+    recent = [[10, 10, 3, -1], [4, 5, 6, -1]]                                    # row 0 has seen token 10 twice
+    got = _sample(logits, 0.0, 0, 1.0, 0.0, 0.5, recent=recent, pens=(1.1, 0.5, 0.0))
+    ref = [int(np.argmax(plain.apply_penalties(logits[r].cpu().numpy(), [t for t in recent[r] if t >= 0], 1.1, 0.5, 0.0)))
+           for r in range(2)]
+    assert got == ref == [20, 10]
+
+
+def test_sampler_same_row_same_number_same_token_whatever_the_batch():
+    V = 5000
+    a = rnd(1, V, seed=54, scale=2.0)
+    alone = _sample(a, 0.8, 40, 0.95, 0.05, 0.4321)[0]
+    batch = torch.cat([rnd(3, V, seed=55), a, rnd(2, V, seed=56)])
+    us = [0.1, 0.9, 0.5, 0.4321, 0.7, 0.2]
+    assert _sample(batch, 0.8, 40, 0.95, 0.05, us)[3] == alone
