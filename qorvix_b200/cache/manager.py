@@ -98,7 +98,8 @@ class CacheManager:
                                             self.page_size, g.spec.head_dim), device=self.device, dtype=dtype)
             elif isinstance(g.spec, FixedStateSpec):
                 if allocate:
-                    g.tensor = torch.zeros((len(g.layers), self.max_requests, *g.spec.shape),
+                    # one more slot than requests: the last is scratch for padded rows of a captured step
+                    g.tensor = torch.zeros((len(g.layers), self.max_requests + 1, *g.spec.shape),
                                            device=self.device, dtype=_DTYPES.get(g.spec.dtype, g.spec.dtype))
             else:
                 raise TypeError(f"unknown cache spec {g.spec!r}")
@@ -110,6 +111,10 @@ class CacheManager:
     @property
     def scratch_page(self) -> int:
         return self.num_pages
+
+    @property
+    def scratch_slot(self) -> int:
+        return self.max_requests
 
     def paged_groups(self) -> List[int]:
         return [i for i, g in enumerate(self.groups) if g.pool is not None]
@@ -129,6 +134,10 @@ class CacheManager:
 
     def slot(self, req_id) -> int:
         return self._requests[req_id].slot
+
+    def epoch(self, req_id) -> int:
+        """A number that differs between two admissions of the same request id."""
+        return self._requests[req_id].admitted_at
 
     def live_requests(self) -> list:
         return list(self._requests)

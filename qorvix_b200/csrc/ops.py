@@ -40,7 +40,22 @@ def _need_cuda(*tensors):
             raise KernelError("kernel operands must live on a CUDA device; there is no CPU path")
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far (replays of captured steps add their kernels)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
 def _check(rc: int, what: str):
+    global _launches
+    _launches += 1
     if rc != 0:
         lib = load_library("elementwise")
         lib.qv_error_string.restype = ctypes.c_char_p

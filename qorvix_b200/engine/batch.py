@@ -64,6 +64,7 @@ class BatchBuilder:
         # its last copy has run: a small ring of buffers, each guarded by an event.
         self._ring: List[list] = [[None, None] for _ in range(4)]
         self._turn = 0
+        self.h2d_bytes = 0                       # bytes copied to the device so far
 
     def _host_buffer(self, n: int):
         self._turn = (self._turn + 1) % len(self._ring)
@@ -107,6 +108,7 @@ class BatchBuilder:
         host[: len(flat)] = torch.tensor(flat, dtype=torch.int32) if flat else host[:0]
         if self.device.type == "cuda":
             dev = host.to(self.device, non_blocking=True)
+            self.h2d_bytes += host.numel() * 4
             if ring_slot[1] is None:
                 ring_slot[1] = torch.cuda.Event()
             ring_slot[1].record()

@@ -37,7 +37,7 @@ def parse_dtype(dtype) -> torch.dtype:
 class ModelRunner:
     def __init__(self, model_dir=None, *, config=None, tensors=None, dtype="bfloat16", max_tokens: int = 4096,
                  page_size: int = 16, max_requests: int = 8, max_model_len: Optional[int] = None,
-                 device="cuda"):
+                 device="cuda", use_graphs: bool = True, max_graph_batch: int = 64):
         """model_dir: folder with config.json and model.safetensors; or config + tensors (a
         mapping name -> tensor) for a model held in memory.  max_tokens sizes the page pool."""
         self.device = torch.device(device)
@@ -65,6 +65,9 @@ class ModelRunner:
                                   max_requests=max_requests, device=self.device, dtype=self.dtype)
         self.vocab_size = self.spec.vocab_size
         self._builder = BatchBuilder(self.device)
+        self.use_graphs = bool(use_graphs)
+        self.max_graph_batch = int(max_graph_batch)
+        self._graphs: Dict[int, object] = {}
         self.steps_run = 0
         self.tokens_run = 0
 
@@ -77,7 +80,24 @@ class ModelRunner:
         return self.cache.length(req_id) if self.cache.has(req_id) else 0
 
     # ------------------------------------------------------------------ the step
-    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+    @property
+    def h2d_bytes(self) -> int:
+        return self._builder.h2d_bytes
+
+    def decode_graph(self, n: int):
+        """The captured decode step that holds n requests (captured on first use)."""
+        from .decode_graph import DecodeGraph, _bucket
+        cap = _bucket(n)
+        if cap not in self._graphs:
+            self._graphs[cap] = DecodeGraph(self, cap)
+        return self._graphs[cap]
+
+    def decoder(self, req_ids):
+        """A greedy decode loop over live requests whose tokens stay on the device."""
+        from .decode_graph import DecodeLoop
+        return DecodeLoop(self, req_ids)
+
+    def prepare(self, entries: Sequence[StepEntry], build: bool = True):
         """Admits new requests, reserves pages for every entry (all or nothing) and builds the
         step's context.  Raises OutOfPages / OutOfSlots with nothing changed."""
         seen = set()
@@ -109,8 +129,11 @@ class ModelRunner:
             ok = self.cache.reserve(e.req_id, len(e.tokens))
             assert ok, "reservation was checked for the whole step"
             segs.append(dict(tokens=[int(t) for t in e.tokens], pos0=self.cache.length(e.req_id),
-                             slot=self.cache.slot(e.req_id), want=[int(w) for w in e.want], first=first))
+                             slot=self.cache.slot(e.req_id), want=[int(w) for w in e.want], first=first,
+                             rid=(e.req_id, self.cache.epoch(e.req_id))))
         tables = {g: [self.cache.block_table(e.req_id, g) for e in entries] for g in self.cache.paged_groups()}
+        if not build:
+            return segs, tables
         return self._builder.build(segs, tables, self.cache.scratch_page)
 
     def step(self, entries: Sequence[StepEntry], end: Iterable[Hashable] = ()) -> Optional[torch.Tensor]:
@@ -119,7 +142,22 @@ class ModelRunner:
         are finished after this step and what they hold is given back."""
         entries = list(entries)
         logits = None
-        if entries:
+        if entries and self.use_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries):
+            # decode-only: replay the captured step
+            segs, tables = self.prepare(entries, build=False)
+            graph = self.decode_graph(len(entries))
+            graph.run(segs, tables, with_tokens=True)
+            rows = [i for i, e in enumerate(entries) if len(e.want)]
+            if rows:
+                if len(rows) == len(entries):
+                    logits = graph.logits[: len(rows)].clone()
+                else:
+                    logits = graph.logits[torch.tensor(rows, device=self.device)]
+            for e in entries:
+                self.cache.commit(e.req_id, 1)
+            self.steps_run += 1
+            self.tokens_run += len(entries)
+        elif entries:
             ctx = self.prepare(entries)
             logits = self.model.forward(ctx, self.cache)
             for e in entries:

@@ -49,7 +49,7 @@ def test_groups_by_need_and_shared_cache():
     m = manager(needs, allocate=True)
     assert len(m.groups) == 3 and m.groups[0].layers == [0, 3] and m.groups[1].layers == [1]
     assert m.layer_view(2).group == 0 and m.layer_view(2).tensor.data_ptr() == m.layer_view(0).tensor.data_ptr()
-    assert m.layer_view(4).kind == "state" and tuple(m.layer_view(4).tensor.shape) == (4, 4, 8)
+    assert m.layer_view(4).kind == "state" and tuple(m.layer_view(4).tensor.shape) == (5, 4, 8)      # 4 request slots + the scratch slot
     assert tuple(m.layer_view(0).tensor.shape) == (17, 2, 2, 16, 16)       # 16 pages + the scratch page
     with pytest.raises(ValueError):
         manager([(None, 1), (None, None)])
