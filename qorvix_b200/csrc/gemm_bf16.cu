@@ -1,0 +1,412 @@
+// C[M,N] = A[M,K] * W[N,K]^T in bfloat16 on the 5th-generation tensor cores (sm_100a):
+// operands staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), products
+// issued by one thread with tcgen05.mma, float32 accumulators in tensor memory, read back with
+// tcgen05.ld for the epilogue.  The reference multiplies one row at a time on the CUDA cores
+// (cuda/src/cuda_backend.cu:291-312); this kernel is its replacement for both phases:
+//
+//   * many tokens (prefill): the token rows are the 128-row MMA operand, 128 weight rows the
+//     other; one CTA per 128x128 tile, two CTAs per SM so one tile's epilogue overlaps the
+//     other's main loop.
+//   * few tokens (decode, M <= 64): operands are swapped.  128 weight rows are the 128-row MMA
+//     operand and the tokens (padded to 16/32/64) the narrow one, so every weight byte is
+//     streamed from HBM exactly once through a deep TMA ring.  Matrices with few row tiles are
+//     also split along K so that enough CTAs pull from HBM at once; the partial sums go to a
+//     float32 workspace and the last CTA of a tile to arrive adds them in a fixed order
+//     (split 0, 1, 2, ...), so the result does not depend on which CTA came last.
+//
+// Every wait on an mbarrier is bounded; when one gives up it records a code in *err and the
+// CTA winds down (tensor memory is freed) instead of hanging the device.
+#include "common.cuh"
+#include <cuda.h>
+
+#define BM 128          // rows of the wide MMA operand (UMMA M)
+#define BK 64           // k elements per stage: 128 bytes, one swizzle span
+#define WAIT_LIMIT (1u << 22)
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false (and *err = code) when the barrier never flipped.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicExch(err, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes, groups of 8
+// rows 1024 bytes apart (SBO); LBO is not used by swizzled K-major layouts; version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;                 // leading byte offset (ignored), encoded 16 bytes
+  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                 // descriptor version
+  d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor, kind::f16: D float32, A and B bfloat16, both K-major, M x N.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+template <typename TC> __device__ __forceinline__ void store_out(TC* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+struct GemmArgs {
+  void* C;             // output [tokens, features], row stride ldc
+  float* workspace;    // split-K partial sums [splits][tokens][features] (swap mode only)
+  int* counters;       // one per (row tile, col tile), zero between launches
+  int* err;
+  int rows_wide;       // rows of the operand that feeds the 128-row side
+  int rows_narrow;     // rows of the other operand
+  int K;
+  int ldc;
+  int kblocks_per_split;
+  int splits;
+};
+
+// BN: columns of the accumulator (rows of the narrow operand per tile).  SWAP: the wide operand
+// is the weight matrix (features) and the narrow one the tokens, so the tile is C^T.
+template <int BN, int STAGES, bool SWAP, typename TC>
+__global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_wide,
+                                                      const __grid_constant__ CUtensorMap map_narrow,
+                                                      const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* accum = empty + STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(accum + 1);
+  int* flag_slot = (int*)(tmem_slot + 1);
+  int* ok_slots = flag_slot + 1;          // one per epilogue warp
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wide0 = blockIdx.x * BM;
+  const int narrow0 = blockIdx.y * BN;
+  const int split = blockIdx.z;
+  const int total_kb = (args.K + BK - 1) / BK;
+  const int kb0 = split * args.kblocks_per_split;
+  int num_kb = total_kb - kb0;
+  if (num_kb > args.kblocks_per_split) num_kb = args.kblocks_per_split;
+  if (num_kb < 0) num_kb = 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(accum, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, args.err, 1)) break;
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        uint8_t* a = tiles + s * STAGE_BYTES;
+        tma_load_2d(a, &map_wide, &full[s], (kb0 + kb) * BK, wide0);
+        tma_load_2d(a + A_BYTES, &map_narrow, &full[s], (kb0 + kb) * BK, narrow0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        ok = mbar_wait(&full[s], ph, args.err, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
+        const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BK / 16; ++kk)    // 16 k elements = 32 bytes = 2 descriptor units
+          umma_f16(tmem_base, da + 2 * kk, db + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&empty[s]);                  // frees the stage when these MMAs have read it
+      }
+      umma_commit(accum);                        // accumulator complete (or nothing was issued)
+    }
+  } else {
+    // epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31
+    const int q = warp & 3;
+    // one lane per warp polls; the four warps then agree, so that either all of them take the
+    // barriers below or none does
+    int ok_i = 1;
+    if (lane == 0) {
+      ok_i = mbar_wait(accum, 0, args.err, 3) ? 1 : 0;
+      ok_slots[q] = ok_i;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool ok = ok_slots[0] && ok_slots[1] && ok_slots[2] && ok_slots[3];
+    tc_fence_after();
+    const int wide_row = wide0 + q * 32 + lane;          // row of the wide operand this thread holds
+    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+    TC* C = (TC*)args.C;
+    if (ok && num_kb > 0) {
+      if (!SWAP) {
+        // thread = token row wide_row; columns = features narrow0 + c
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c0, r);
+          tmem_wait_ld();
+          if (wide_row < args.rows_wide) {
+            TC* dst = C + (size_t)wide_row * args.ldc + narrow0 + c0;
+            const int ncols = args.rows_narrow - (narrow0 + c0);
+            if (sizeof(TC) == 2 && ncols >= 32 && (((uintptr_t)dst) & 15) == 0) {
+              uint4* d4 = (uint4*)dst;
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+                  w[j] = *(uint32_t*)&h;
+                }
+                d4[v] = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            } else if (sizeof(TC) == 4 && ncols >= 32 && (((uintptr_t)dst) & 15) == 0) {
+              float4* d4 = (float4*)dst;
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                d4[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+            } else {
+              for (int j = 0; j < 32 && j < ncols; ++j) store_out<TC>(dst + j, __uint_as_float(r[j]));
+            }
+          }
+        }
+      } else {
+        // thread = feature wide_row; columns = tokens narrow0 + c
+        const bool frow = wide_row < args.rows_wide;
+        const int ntok = args.rows_narrow;
+        if (args.splits == 1) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(taddr + c0, r);
+            tmem_wait_ld();
+            if (frow) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int t = narrow0 + c0 + j;
+                if (t < ntok) store_out<TC>(C + (size_t)t * args.ldc + wide_row, __uint_as_float(r[j]));
+              }
+            }
+          }
+        } else {
+          float* ws = args.workspace + (size_t)split * ntok * args.rows_wide;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(taddr + c0, r);
+            tmem_wait_ld();
+            if (frow) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int t = narrow0 + c0 + j;
+                if (t < ntok) ws[(size_t)t * args.rows_wide + wide_row] = __uint_as_float(r[j]);
+              }
+            }
+          }
+          // the last CTA of this tile to arrive adds the partial sums in split order
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 64) {
+            const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+            const int prev = atomicAdd(&args.counters[tile], 1);
+            *flag_slot = (prev == args.splits - 1) ? 1 : 0;
+            if (prev == args.splits - 1) args.counters[tile] = 0;     // ready for the next launch
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (*flag_slot) {
+            __threadfence();
+            if (frow) {
+              for (int j = 0; j < BN; ++j) {
+                const int t = narrow0 + j;
+                if (t >= ntok) break;
+                float acc = 0.f;
+                for (int s = 0; s < args.splits; ++s)
+                  acc += __ldcg(args.workspace + ((size_t)s * ntok + t) * args.rows_wide + wide_row);
+                store_out<TC>(C + (size_t)t * args.ldc + wide_row, acc);
+              }
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 2-D bfloat16 matrix [rows, K] with row stride ld elements; box = 64 k x box_rows, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, bool SWAP, typename TC>
+int launch(const CUtensorMap& mw, const CUtensorMap& mn, const GemmArgs& args, dim3 grid, cudaStream_t st) {
+  constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  gemm_tc_kernel<BN, STAGES, SWAP, TC><<<grid, 192, smem, st>>>(mw, mn, args);
+  return qv_launch_status();
+}
+
+}  // namespace
+
+// Smallest workspace (bytes) and number of counters that any call with M <= 64 may need.
+extern "C" long long qv_gemm_bf16_workspace_bytes(int max_features) { return (long long)8 * 64 * (long long)max_features * 4; }
+
+// C (bf16 or f32) [M,N] = A (bf16) [M,K] * W (bf16) [N,K]^T.  Returns QV_ERR_UNSUPPORTED for shapes
+// the tensor-core path does not take (the caller then uses the CUDA-core kernel):
+// K not a multiple of 8 elements, or operands whose rows do not start on 16-byte boundaries.
+extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
+                               int c_dt, float* workspace, long long workspace_bytes, int* counters, int n_counters,
+                               int* err, int force_splits, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K < 8 || (K & 7) || (lda & 7) || (ldw & 7)) return QV_ERR_UNSUPPORTED;
+  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return QV_ERR_UNSUPPORTED;
+  if (c_dt != QV_DT_BF16 && c_dt != QV_DT_F32) return QV_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  GemmArgs args;
+  args.C = C; args.workspace = workspace; args.counters = counters; args.err = err;
+  args.K = K; args.ldc = ldc;
+  const int total_kb = (K + BK - 1) / BK;
+  CUtensorMap mw, mn;
+  if (M <= 64) {
+    // swap: weights on the 128-row side, tokens on the narrow side
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const int tiles = (N + BM - 1) / BM;
+    int splits = 1;
+    if (force_splits > 0) splits = force_splits;
+    else if (tiles < 96) {                          // too few CTAs to pull full bandwidth: split along K
+      splits = (148 + tiles - 1) / tiles;
+      if (splits > 8) splits = 8;
+    }
+    if (splits > total_kb) splits = total_kb;
+    if (splits > 1 && (workspace == nullptr || counters == nullptr || tiles > n_counters ||
+                       (long long)splits * M * N * 4 > workspace_bytes)) splits = 1;
+    int per = (total_kb + splits - 1) / splits;
+    splits = (total_kb + per - 1) / per;            // no empty split
+    args.rows_wide = N; args.rows_narrow = M; args.kblocks_per_split = per; args.splits = splits;
+    if (!make_map(&mw, W, N, K, ldw, BM) || !make_map(&mn, A, M, K, lda, bn)) return QV_ERR_UNSUPPORTED;
+    dim3 grid(tiles, 1, splits);
+#define SWAP_LAUNCH(BN_, ST_)                                                                     \
+  (c_dt == QV_DT_BF16 ? launch<BN_, ST_, true, bf16>(mw, mn, args, grid, st) : launch<BN_, ST_, true, float>(mw, mn, args, grid, st))
+    if (bn == 16) return SWAP_LAUNCH(16, 6);
+    if (bn == 32) return SWAP_LAUNCH(32, 5);
+    return SWAP_LAUNCH(64, 4);
+#undef SWAP_LAUNCH
+  }
+  // many tokens: tokens on the 128-row side, 128 weight rows per tile
+  args.rows_wide = M; args.rows_narrow = N; args.kblocks_per_split = total_kb; args.splits = 1;
+  if (!make_map(&mw, A, M, K, lda, BM) || !make_map(&mn, W, N, K, ldw, 128)) return QV_ERR_UNSUPPORTED;
+  dim3 grid((M + BM - 1) / BM, (N + 127) / 128, 1);
+  if (grid.y > 65535) return QV_ERR_TOO_LARGE;
+  if (c_dt == QV_DT_BF16) return launch<128, 3, false, bf16>(mw, mn, args, grid, st);
+  return launch<128, 3, false, float>(mw, mn, args, grid, st);
+}

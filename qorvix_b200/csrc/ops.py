@@ -161,6 +161,50 @@ def gemm_simt(c, a, w, accumulate=False) -> None:
     _check(rc, "gemm_simt")
 
 
+_tc_state = {}
+
+
+def _tc_buffers(device):
+    """Per device: split-K workspace, tile counters and the error word of the tensor-core kernels.
+    Calls on one stream run one after another, so they can share these."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    st = _tc_state.get(key)
+    if st is None:
+        st = dict(workspace=torch.empty(32 << 20, dtype=torch.uint8, device=device),
+                  counters=torch.zeros(4096, dtype=torch.int32, device=device),
+                  err=torch.zeros(1, dtype=torch.int32, device=device))
+        _tc_state[key] = st
+    return st
+
+
+def gemm_bf16_tc(c, a, w, force_splits: int = 0) -> bool:
+    """c[M,N] (bf16 or f32) = a[M,K] @ w[N,K]^T on the tcgen05 tensor cores.  False when the
+    shape is one the kernel refuses (K not a multiple of 8, unaligned rows); nothing is written then."""
+    _need_cuda(c, a, w)
+    M, K = a.shape
+    N = w.shape[0]
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K and c.shape == (M, N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    st = _tc_buffers(a.device)
+    rc = load_library("gemm_bf16").qv_gemm_bf16_tc(
+        _ptr(c), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(w.stride(0)),
+        c_int(c.stride(0)), c_int(dt_code(c.dtype)), _ptr(st["workspace"]), c_longlong(st["workspace"].numel()),
+        _ptr(st["counters"]), c_int(st["counters"].numel()), _ptr(st["err"]), c_int(force_splits), _stream())
+    if rc == -2:
+        return False
+    _check(rc, "gemm_bf16_tc")
+    return True
+
+
+def check_kernel_errors() -> None:
+    """Raises if a kernel gave up on a bounded wait since the last check (synchronises)."""
+    for key, st in _tc_state.items():
+        code = int(st["err"].item())
+        if code:
+            st["err"].zero_()
+            raise KernelError(f"a tensor-core kernel on device {key} gave up waiting on a barrier (code {code})")
+
+
 # ------------------------------------------------------------------ attention
 
 def attention_generic(out, q, cache_layer, tok_pos, tok_seg, block_table, H, Hkv, hd, page, window, scale) -> None:
@@ -181,7 +225,10 @@ def attention_generic(out, q, cache_layer, tok_pos, tok_seg, block_table, H, Hkv
 # ------------------------------------------------------------------ dispatch
 
 def gemm(out, x, w) -> None:
-    """out = x @ w^T with the kernel that fits the dtypes and the shape."""
+    """out = x @ w^T with the kernel that fits the dtypes and the shape: bfloat16 operands go to
+    the tensor-core kernel when it takes the shape, everything else to the CUDA-core kernel."""
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and gemm_bf16_tc(out, x, w):
+        return
     gemm_simt(out, x, w)
 
 

@@ -1,0 +1,68 @@
+"""The tcgen05 matrix product alone, against a float64 product of the same bfloat16 inputs."""
+import pytest
+import torch
+
+from qorvix_b200.csrc import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).to(DEV)
+
+
+def check(M, N, K, out_dtype, force_splits=0, lda=None):
+    a_full = rnd(M, lda or K, seed=M + K)
+    a = a_full[:, :K]
+    w = rnd(N, K, seed=N + 1, scale=0.05)
+    c = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+    assert ops.gemm_bf16_tc(c, a, w, force_splits=force_splits)
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    ref = a.double() @ w.double().t()
+    tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
+    err = (c.double() - ref).abs().max().item()
+    assert err <= tol * max(1.0, ref.abs().max().item()), f"M={M} N={N} K={K}: max err {err}"
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 256), (256, 384, 4096), (200, 1000, 328),
+                                   (2048, 6144, 4096), (65, 136, 72), (300, 331, 1000)])
+def test_many_tokens(M, N, K, out_dtype):
+    check(M, N, K, out_dtype)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 6144, 4096), (8, 4096, 14336), (16, 256, 128), (17, 1000, 328),
+                                   (33, 4096, 4096), (64, 28672, 4096), (5, 331, 72), (64, 128256, 1024)])
+def test_few_tokens_swapped(M, N, K, out_dtype):
+    check(M, N, K, out_dtype)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 8])
+def test_split_k_sums_in_a_fixed_order(splits):
+    M, N, K = 8, 512, 4096
+    a, w = rnd(M, K, seed=1), rnd(N, K, seed=2, scale=0.05)
+    outs = []
+    for _ in range(3):
+        c = torch.empty(M, N, device=DEV, dtype=torch.float32)
+        assert ops.gemm_bf16_tc(c, a, w, force_splits=splits)
+        outs.append(c)
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])      # run to run identical
+    ref = a.double() @ w.double().t()
+    assert (outs[0].double() - ref).abs().max().item() < 2e-3 * ref.abs().max().item()
+
+
+def test_strided_activations_and_refused_shapes():
+    check(40, 256, 128, torch.bfloat16, lda=384)            # a column slice of a wider buffer
+    a, w = rnd(4, 100, seed=3), rnd(64, 100, seed=4)
+    c = torch.zeros(4, 64, device=DEV, dtype=torch.bfloat16)
+    assert not ops.gemm_bf16_tc(c, a, w)                    # K = 100 is no multiple of 8: refused, untouched
+    assert float(c.abs().sum()) == 0.0
+    ops.gemm(c, a, w)                                       # the dispatcher falls back to the CUDA cores
+    ref = a.double() @ w.double().t()
+    assert (c.double() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
