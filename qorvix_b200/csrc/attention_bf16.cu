@@ -1,0 +1,415 @@
+// Causal grouped-query attention over the paged bfloat16 cache on the tensor cores, for
+// serving: a flash-attention kernel for prompt portions and a split-KV kernel for decoded
+// tokens.  Formula and masking are those of the reference's CPU model
+// (runtime/src/text_model.cpp:83-114: kv head = h / (H/Hkv), score = q.k / sqrt(hd) for keys up
+// to the query's position, softmax, weighted sum of V); its CUDA kernel keeps every score of a
+// sequence in shared memory and runs the softmax on one thread
+// (cuda/src/cuda_backend.cu:347-395), which neither scales to long contexts nor batches.
+//
+// Both kernels work on blocks of 16 keys with mma.sync m16n8k16 (bf16 in, float32 out) and an
+// online softmax in float32.  Operands go from global memory (L1/L2) straight into MMA
+// fragments, without shared memory: a dot product may sum its terms in any order, so the k
+// index of a fragment is mapped to head dims in the order in which one 16-byte load delivers
+// them (the same mapping for Q and K), and for P.V the output dims are permuted likewise, with
+// byte permutes pairing the values of two keys.  Keys are read through the request's block
+// table; a block of 16 keys never straddles a page (pages are multiples of 16 tokens).
+//
+//   prefill: one CTA = 64 query tokens of one head (4 warps x 16 rows); each warp walks the
+//            keys of its rows.  Grid (query tiles, heads, segments).
+//   decode:  one CTA = one token, one kv head, one slice of the keys; the rows of the MMA
+//            tile are the query heads that share the kv head; the 4 warps take alternate
+//            16-key blocks and merge through shared memory; slices merge in a second kernel.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *(uint32_t*)&h;
+}
+
+template <int N> struct Words { uint32_t w[N]; };
+template <int N> __device__ __forceinline__ Words<N> load_words(const bf16* p);
+template <> __device__ __forceinline__ Words<4> load_words<4>(const bf16* p) {
+  const uint4 v = *(const uint4*)p; Words<4> r; r.w[0] = v.x; r.w[1] = v.y; r.w[2] = v.z; r.w[3] = v.w; return r;
+}
+template <> __device__ __forceinline__ Words<2> load_words<2>(const bf16* p) {
+  const uint2 v = *(const uint2*)p; Words<2> r; r.w[0] = v.x; r.w[1] = v.y; return r;
+}
+template <> __device__ __forceinline__ Words<1> load_words<1>(const bf16* p) {
+  Words<1> r; r.w[0] = *(const uint32_t*)p; return r;
+}
+
+// Sizes that follow from the head size.
+template <int HD> struct Shape {
+  static constexpr int KW = (HD % 32 == 0) ? 4 : 2;       // 32-bit words per thread per K/Q load
+  static constexpr int KCH = HD / (KW * 8);               // chunks of KW*8 dims along the dot product
+  static constexpr int VW = (HD % 64 == 0) ? 4 : ((HD % 32 == 0) ? 2 : 1);   // words per thread per V load
+  static constexpr int VCH = HD / (VW * 16);              // chunks of VW*16 output dims
+  static constexpr int NT = HD / 8;                       // output n-tiles
+};
+
+// Q rows g and g+8 of a 16-row tile as A fragments, in the k order of the K loads.
+template <int HD> struct QFrag { uint32_t w[Shape<HD>::KCH][2][Shape<HD>::KW]; };
+
+template <int HD>
+__device__ __forceinline__ void load_q(QFrag<HD>& q, const bf16* row_lo, const bf16* row_hi, int tg) {
+  constexpr int KW = Shape<HD>::KW;
+#pragma unroll
+  for (int c = 0; c < Shape<HD>::KCH; ++c) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const bf16* p = r ? row_hi : row_lo;
+      if (p) {
+        Words<KW> v = load_words<KW>(p + c * KW * 8 + tg * KW * 2);
+#pragma unroll
+        for (int i = 0; i < KW; ++i) q.w[c][r][i] = v.w[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < KW; ++i) q.w[c][r][i] = 0u;
+      }
+    }
+  }
+}
+
+// Running softmax state of rows g and g+8 and their output fragments.
+template <int HD> struct RowState {
+  float m[2], l[2];
+  float o[Shape<HD>::NT][4];
+  __device__ __forceinline__ void init() {
+    m[0] = m[1] = -INFINITY; l[0] = l[1] = 0.f;
+#pragma unroll
+    for (int i = 0; i < Shape<HD>::NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  }
+};
+
+// One block of 16 keys starting at absolute key index `base` (a multiple of 16).
+// kpage / vpage: this kv head's K and V rows of the page that holds the block, at the block's
+// first key.  Row r in {0,1} (tile rows g, g+8) sees keys in [lo[r], hi[r]] (inclusive).
+template <int HD>
+__device__ __forceinline__ void block16(RowState<HD>& st, const QFrag<HD>& q, const bf16* __restrict__ kblk,
+                                        const bf16* __restrict__ vblk, int base, const int* lo, const int* hi,
+                                        float scale_log2, int g, int tg) {
+  constexpr int KW = Shape<HD>::KW, KCH = Shape<HD>::KCH, VW = Shape<HD>::VW, VCH = Shape<HD>::VCH;
+  float s[2][4];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    const bf16* krow = kblk + (size_t)(8 * j + g) * HD + tg * KW * 2;
+#pragma unroll
+    for (int c = 0; c < KCH; ++c) {
+      const Words<KW> kw = load_words<KW>(krow + c * KW * 8);
+#pragma unroll
+      for (int step = 0; step < KW / 2; ++step)
+        mma_bf16(s[j], q.w[c][0][2 * step], q.w[c][1][2 * step], q.w[c][0][2 * step + 1], q.w[c][1][2 * step + 1],
+                 kw.w[2 * step], kw.w[2 * step + 1]);
+    }
+  }
+  // mask, running maximum
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int r = e >> 1;
+      const int key = base + 8 * j + 2 * tg + (e & 1);
+      const float v = (key >= lo[r] && key <= hi[r]) ? s[j][e] * scale_log2 : -INFINITY;
+      s[j][e] = v;
+      mx[r] = fmaxf(mx[r], v);
+    }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+  }
+  float corr[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const float m_new = fmaxf(st.m[r], mx[r]);
+    // a row with no visible key so far keeps m = -inf; exp2(-inf - (-inf)) must not be formed
+    corr[r] = (m_new == -INFINITY) ? 1.f : exp2f(st.m[r] - m_new);
+    st.m[r] = m_new;
+    st.l[r] *= corr[r];
+  }
+  uint32_t p[4];     // A fragment of P: a0 (row g, keys 2tg..), a1 (row g+8), a2 (row g, keys 8+2tg..), a3
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    float e[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const int r = x >> 1;
+      e[x] = (s[j][x] == -INFINITY) ? 0.f : exp2f(s[j][x] - st.m[r]);
+      st.l[r] += e[x];
+    }
+    p[2 * j] = pack_bf16(e[0], e[1]);
+    p[2 * j + 1] = pack_bf16(e[2], e[3]);
+  }
+#pragma unroll
+  for (int i = 0; i < Shape<HD>::NT; ++i) {
+    st.o[i][0] *= corr[0]; st.o[i][1] *= corr[0];
+    st.o[i][2] *= corr[1]; st.o[i][3] *= corr[1];
+  }
+  // P.V: this thread supplies keys 2tg, 2tg+1, 8+2tg, 9+2tg for output column n = g of each n-tile;
+  // n-tile e of chunk c is head dim c*VW*16 + g*VW*2 + e.
+  const bf16* v0 = vblk + (size_t)(2 * tg) * HD + g * VW * 2;
+#pragma unroll
+  for (int c = 0; c < VCH; ++c) {
+    const Words<VW> a = load_words<VW>(v0 + c * VW * 16);
+    const Words<VW> b = load_words<VW>(v0 + HD + c * VW * 16);
+    const Words<VW> cc = load_words<VW>(v0 + 8 * HD + c * VW * 16);
+    const Words<VW> d = load_words<VW>(v0 + 9 * HD + c * VW * 16);
+#pragma unroll
+    for (int e = 0; e < VW * 2; ++e) {
+      const int w = e >> 1;
+      const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+      const uint32_t b0 = __byte_perm(a.w[w], b.w[w], sel);
+      const uint32_t b1 = __byte_perm(cc.w[w], d.w[w], sel);
+      mma_bf16(st.o[c * VW * 2 + e], p[0], p[1], p[2], p[3], b0, b1);
+    }
+  }
+}
+
+// Output fragment (n-tile index i = c*VW*2 + e, column n) -> head dim.
+template <int HD> __device__ __forceinline__ int out_dim(int i, int n) {
+  constexpr int VW = Shape<HD>::VW;
+  const int c = i / (VW * 2), e = i - c * VW * 2;
+  return c * VW * 16 + n * VW * 2 + e;
+}
+
+// ---------------------------------------------------------------- prefill
+template <int HD>
+__global__ void __launch_bounds__(128) attn_prefill_kernel(bf16* __restrict__ out, int ld_out, const bf16* __restrict__ q, int ld_q,
+                                                           const bf16* __restrict__ cache, const int* __restrict__ seg_q_start,
+                                                           const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
+                                                           int max_blocks, int H, int Hkv, int page, int window, float scale_log2) {
+  const int seg = blockIdx.z, h = blockIdx.y;
+  const int q0 = seg_q_start[seg], qlen = seg_q_start[seg + 1] - q0;
+  const int tile0 = blockIdx.x * 64;
+  if (tile0 >= qlen) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
+  const int r0 = tile0 + warp * 16;                 // first row of this warp within the segment
+  if (r0 >= qlen) return;
+  const int pos0 = seg_pos0[seg];
+  const int kvh = h / (H / Hkv);
+  const int* bt = block_table + (size_t)seg * max_blocks;
+  const int rows[2] = {r0 + g, r0 + g + 8};
+  const bool valid[2] = {rows[0] < qlen, rows[1] < qlen};
+  QFrag<HD> qf;
+  load_q<HD>(qf, valid[0] ? q + (size_t)(q0 + rows[0]) * ld_q + (size_t)h * HD : nullptr,
+             valid[1] ? q + (size_t)(q0 + rows[1]) * ld_q + (size_t)h * HD : nullptr, tg);
+  int lo[2], hi[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    hi[r] = valid[r] ? pos0 + rows[r] : -1;
+    lo[r] = (window > 0 && hi[r] - window + 1 > 0) ? hi[r] - window + 1 : 0;
+  }
+  const int last_row = (r0 + 15 < qlen ? r0 + 15 : qlen - 1);
+  const int k_end = pos0 + last_row;                              // last key any row of this warp sees
+  int k_begin = 0;
+  if (window > 0) { const int f = pos0 + r0 - window + 1; k_begin = f > 0 ? (f & ~15) : 0; }
+  RowState<HD> st;
+  st.init();
+  const size_t page_elems = (size_t)2 * Hkv * page * HD;
+  const size_t v_off = (size_t)Hkv * page * HD;
+  for (int base = k_begin; base <= k_end; base += 16) {
+    const bf16* kblk = cache + (size_t)bt[base / page] * page_elems + ((size_t)kvh * page + (base % page)) * HD;
+    block16<HD>(st, qf, kblk, kblk + v_off, base, lo, hi, scale_log2, g, tg);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+    st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if (!valid[r]) continue;
+    const float inv = 1.f / st.l[r];
+    bf16* orow = out + (size_t)(q0 + rows[r]) * ld_out + (size_t)h * HD;
+#pragma unroll
+    for (int i = 0; i < Shape<HD>::NT; ++i) {
+      orow[out_dim<HD>(i, 2 * tg)] = __float2bfloat16_rn(st.o[i][2 * r] * inv);
+      orow[out_dim<HD>(i, 2 * tg + 1)] = __float2bfloat16_rn(st.o[i][2 * r + 1] * inv);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- decode
+// partial results of a slice: [token][head][slice][HD + 2] floats (out unnormalised, then m, l)
+template <int HD>
+__global__ void __launch_bounds__(128) attn_decode_kernel(bf16* __restrict__ out, int ld_out, const bf16* __restrict__ q, int ld_q,
+                                                          const bf16* __restrict__ cache, const int* __restrict__ tok_pos,
+                                                          const int* __restrict__ tok_seg, const int* __restrict__ block_table,
+                                                          int max_blocks, int H, int Hkv, int page, int window, float scale_log2,
+                                                          int splits, float* __restrict__ partial) {
+  extern __shared__ float sm[];                 // [4 warps][16 rows][HD + 2]
+  const int t = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
+  const int G = H / Hkv;
+  const int pos = tok_pos[t];
+  const int* bt = block_table + (size_t)tok_seg[t] * max_blocks;
+  const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int start = first & ~15;
+  const int total = pos + 1 - start;
+  int chunk = (total + splits - 1) / splits;
+  chunk = (chunk + 63) & ~63;
+  const int k_begin = start + split * chunk;
+  int k_stop = k_begin + chunk;                  // exclusive
+  if (k_stop > pos + 1) k_stop = pos + 1;
+  const bf16* qtok = q + (size_t)t * ld_q + (size_t)kvh * G * HD;
+  QFrag<HD> qf;
+  load_q<HD>(qf, g < G ? qtok + (size_t)g * HD : nullptr, g + 8 < G ? qtok + (size_t)(g + 8) * HD : nullptr, tg);
+  const int lo[2] = {first, first};
+  const int hi[2] = {g < G ? pos : -1, g + 8 < G ? pos : -1};
+  RowState<HD> st;
+  st.init();
+  const size_t page_elems = (size_t)2 * Hkv * page * HD;
+  const size_t v_off = (size_t)Hkv * page * HD;
+  for (int base = k_begin + 16 * warp; base < k_stop; base += 64) {
+    const bf16* kblk = cache + (size_t)bt[base / page] * page_elems + ((size_t)kvh * page + (base % page)) * HD;
+    block16<HD>(st, qf, kblk, kblk + v_off, base, lo, hi, scale_log2, g, tg);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+    st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+  }
+  // each warp leaves its rows in shared memory
+  constexpr int ROW = HD + 2;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = g + 8 * r;
+    if (row >= G) continue;
+    float* dst = sm + ((size_t)warp * 16 + row) * ROW;
+#pragma unroll
+    for (int i = 0; i < Shape<HD>::NT; ++i) {
+      dst[out_dim<HD>(i, 2 * tg)] = st.o[i][2 * r];
+      dst[out_dim<HD>(i, 2 * tg + 1)] = st.o[i][2 * r + 1];
+    }
+    if (tg == 0) { dst[HD] = st.m[r]; dst[HD + 1] = st.l[r]; }
+  }
+  __syncthreads();
+  // merge the 4 warps in a fixed order (warp 0, 1, 2, 3)
+  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+    const int row = idx / HD, d = idx - row * HD;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, sm[((size_t)w * 16 + row) * ROW + HD]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float* src = sm + ((size_t)w * 16 + row) * ROW;
+      const float f = (src[HD] == -INFINITY) ? 0.f : exp2f(src[HD] - m);
+      acc += src[d] * f;
+      l += src[HD + 1] * f;
+    }
+    const int h = kvh * G + row;
+    if (splits == 1) {
+      out[(size_t)t * ld_out + (size_t)h * HD + d] = __float2bfloat16_rn(acc / l);
+    } else {
+      float* dst = partial + (((size_t)t * H + h) * splits + split) * ROW;
+      dst[d] = acc;
+      if (d == 0) { dst[HD] = m; dst[HD + 1] = l; }
+    }
+  }
+}
+
+// merges the slices of one (token, head) in slice order
+__global__ void attn_combine_kernel(bf16* __restrict__ out, int ld_out, const float* __restrict__ partial, int H, int hd, int splits) {
+  const int t = blockIdx.y, h = blockIdx.x;
+  const int row = hd + 2;
+  const float* src = partial + ((size_t)t * H + h) * splits * row;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, src[(size_t)s * row + hd]);
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.f, l = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = src[(size_t)s * row + hd];
+      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+      acc += src[(size_t)s * row + d] * f;
+      l += src[(size_t)s * row + hd + 1] * f;
+    }
+    out[(size_t)t * ld_out + (size_t)h * hd + d] = __float2bfloat16_rn(acc / l);
+  }
+}
+
+template <int HD>
+int launch_prefill(bf16* out, int ld_out, const bf16* q, int ld_q, const bf16* cache, const int* seg_q_start, const int* seg_pos0,
+                   const int* bt, int max_blocks, int S, int max_q_len, int H, int Hkv, int page, int window, float scale_log2,
+                   cudaStream_t st) {
+  dim3 grid((max_q_len + 63) / 64, H, S);
+  attn_prefill_kernel<HD><<<grid, 128, 0, st>>>(out, ld_out, q, ld_q, cache, seg_q_start, seg_pos0, bt, max_blocks, H, Hkv, page,
+                                               window, scale_log2);
+  return qv_launch_status();
+}
+
+template <int HD>
+int launch_decode(bf16* out, int ld_out, const bf16* q, int ld_q, const bf16* cache, const int* tok_pos, const int* tok_seg,
+                  const int* bt, int max_blocks, int T, int H, int Hkv, int page, int window, float scale_log2, int splits,
+                  float* partial, cudaStream_t st) {
+  const size_t smem = (size_t)4 * 16 * (HD + 2) * sizeof(float);
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(splits, Hkv, T);
+  attn_decode_kernel<HD><<<grid, 128, smem, st>>>(out, ld_out, q, ld_q, cache, tok_pos, tok_seg, bt, max_blocks, H, Hkv, page,
+                                                  window, scale_log2, splits, partial);
+  int rc = qv_launch_status();
+  if (rc || splits == 1) return rc;
+  attn_combine_kernel<<<dim3(H, T), HD < 128 ? 64 : 128, 0, st>>>(out, ld_out, partial, H, HD, splits);
+  return qv_launch_status();
+}
+
+}  // namespace
+
+#define FOR_HEAD_DIMS(X) X(16) X(32) X(48) X(64) X(80) X(96) X(112) X(128)
+
+// Floats of workspace that qv_attn_decode_bf16 needs for `splits` > 1.
+extern "C" long long qv_attn_decode_workspace_floats(int T, int H, int hd, int splits) {
+  return splits > 1 ? (long long)T * H * splits * (hd + 2) : 0;
+}
+
+// Prompt portions (any mix of segments).  Refuses head sizes other than 16..128 in steps of 16,
+// pages that are no multiple of 16, and operands that are not 16-byte aligned row by row.
+extern "C" int qv_attn_prefill_bf16(void* out, int ld_out, const void* q, int ld_q, const void* cache, const int* seg_q_start,
+                                    const int* seg_pos0, const int* block_table, int max_blocks, int S, int max_q_len, int H,
+                                    int Hkv, int hd, int page, int window, float scale, void* stream) {
+  if (S <= 0 || max_q_len <= 0) return 0;
+  if (Hkv <= 0 || H % Hkv || page % 16 || (ld_q & 7) || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15)) return QV_ERR_UNSUPPORTED;
+  if (S > 65535 || H > 65535) return QV_ERR_TOO_LARGE;
+  const float sl2 = scale * 1.4426950408889634f;
+#define CASE(D)                                                                                                          \
+  if (hd == D)                                                                                                           \
+    return launch_prefill<D>((bf16*)out, ld_out, (const bf16*)q, ld_q, (const bf16*)cache, seg_q_start, seg_pos0, block_table, \
+                             max_blocks, S, max_q_len, H, Hkv, page, window, sl2, (cudaStream_t)stream);
+  FOR_HEAD_DIMS(CASE)
+#undef CASE
+  return QV_ERR_UNSUPPORTED;
+}
+
+// One query row per token (decoded tokens; also right, if slow, for any token of a portion).
+// The query heads of one kv head form the MMA tile, so H / Hkv must not exceed 16.
+extern "C" int qv_attn_decode_bf16(void* out, int ld_out, const void* q, int ld_q, const void* cache, const int* tok_pos,
+                                   const int* tok_seg, const int* block_table, int max_blocks, int T, int H, int Hkv, int hd,
+                                   int page, int window, float scale, int splits, float* partial, void* stream) {
+  if (T <= 0) return 0;
+  if (Hkv <= 0 || H % Hkv || H / Hkv > 16 || page % 16 || (ld_q & 7) || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15))
+    return QV_ERR_UNSUPPORTED;
+  if (splits < 1 || (splits > 1 && !partial) || T > 65535 || Hkv > 65535) return QV_ERR_UNSUPPORTED;
+  const float sl2 = scale * 1.4426950408889634f;
+#define CASE(D)                                                                                                         \
+  if (hd == D)                                                                                                          \
+    return launch_decode<D>((bf16*)out, ld_out, (const bf16*)q, ld_q, (const bf16*)cache, tok_pos, tok_seg, block_table, \
+                            max_blocks, T, H, Hkv, page, window, sl2, splits, partial, (cudaStream_t)stream);
+  FOR_HEAD_DIMS(CASE)
+#undef CASE
+  return QV_ERR_UNSUPPORTED;
+}

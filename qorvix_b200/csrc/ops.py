@@ -232,42 +232,67 @@ def gemm(out, x, w) -> None:
     gemm_simt(out, x, w)
 
 
+def attention_prefill_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, Hkv, hd, page,
+                           window, scale) -> bool:
+    """Flash attention of prompt portions (any mix of segments) over the paged bfloat16 cache.
+    False when the kernel refuses the sizes."""
+    _need_cuda(out, q, cache_layer, seg_q_start, seg_pos0, block_table)
+    assert q.dtype == out.dtype == cache_layer.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and cache_layer.is_contiguous()
+    assert tuple(cache_layer.shape[1:]) == (2, Hkv, page, hd)
+    _i32(seg_q_start, "seg_q_start"); _i32(seg_pos0, "seg_pos0"); _i32(block_table, "block_table")
+    rc = load_library("attention_bf16").qv_attn_prefill_bf16(
+        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(cache_layer), _ptr(seg_q_start), _ptr(seg_pos0),
+        _ptr(block_table), c_int(block_table.shape[-1]), c_int(S), c_int(max_q_len), c_int(H), c_int(Hkv), c_int(hd),
+        c_int(page), c_int(window), c_float(scale), _stream())
+    if rc == -2:
+        return False
+    _check(rc, "attention_prefill_bf16")
+    return True
+
+
+def decode_splits(T: int, Hkv: int, max_ctx: int) -> int:
+    """How many slices of the keys each (token, kv head) is cut into, so that about two CTAs per
+    SM are busy; a function of the step's shape only (a captured step keeps it)."""
+    want = -(-2 * 148 // max(1, T * Hkv))
+    return max(1, min(16, want, -(-max_ctx // 64)))
+
+
+def attention_decode_bf16(out, q, cache_layer, tok_pos, tok_seg, block_table, H, Hkv, hd, page, window, scale,
+                          splits: int = 1) -> bool:
+    """Attention of single query tokens (split over `splits` slices of the keys).  False when refused."""
+    _need_cuda(out, q, cache_layer, tok_pos, tok_seg, block_table)
+    T = q.shape[0]
+    assert q.dtype == out.dtype == cache_layer.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and cache_layer.is_contiguous()
+    assert tuple(cache_layer.shape[1:]) == (2, Hkv, page, hd)
+    _i32(tok_pos, "tok_pos"); _i32(tok_seg, "tok_seg"); _i32(block_table, "block_table")
+    partial = None
+    if splits > 1:
+        partial = torch.empty(T * H * splits * (hd + 2), dtype=torch.float32, device=q.device)
+    rc = load_library("attention_bf16").qv_attn_decode_bf16(
+        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(cache_layer), _ptr(tok_pos), _ptr(tok_seg),
+        _ptr(block_table), c_int(block_table.shape[-1]), c_int(T), c_int(H), c_int(Hkv), c_int(hd), c_int(page),
+        c_int(window), c_float(scale), c_int(splits), _ptr(partial), _stream())
+    if rc == -2:
+        return False
+    _check(rc, "attention_decode_bf16")
+    if splits > 1:
+        add_launches(1)                              # the merge of the slices
+    return True
+
+
 def attention(out, q, cache_layer, ctx, block_table, H, Hkv, hd, page, window, scale) -> None:
-    """Attention of every token of the step over its request's pages."""
+    """Attention of every token of the step over its request's pages.  bfloat16: the tensor-core
+    kernels (split-KV for steps of single tokens, flash attention otherwise) when they take the
+    sizes; float32, and sizes they refuse: the CUDA-core kernel."""
+    if q.dtype == torch.bfloat16:
+        if ctx.max_q_len == 1:
+            splits = decode_splits(q.shape[0], Hkv, ctx.max_ctx_len)
+            if attention_decode_bf16(out, q, cache_layer, ctx.tok_pos, ctx.tok_seg, block_table, H, Hkv, hd, page,
+                                     window, scale, splits):
+                return
+        elif attention_prefill_bf16(out, q, cache_layer, ctx.seg_q_start, ctx.seg_pos0, block_table, ctx.num_segments,
+                                    ctx.max_q_len, H, Hkv, hd, page, window, scale):
+            return
     attention_generic(out, q, cache_layer, ctx.tok_pos, ctx.tok_seg, block_table, H, Hkv, hd, page, window, scale)
-
-
-# ------------------------------------------------------------------ sampling
-
-def argmax(out_ids, logits) -> None:
-    """out_ids[r] = index of the first maximum of logits[r] (float32)."""
-    _need_cuda(out_ids, logits)
-    _i32(out_ids, "out_ids")
-    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out_ids.numel() >= logits.shape[0]
-    rc = load_library("sampling").qv_argmax(_ptr(out_ids), _ptr(logits), c_int(logits.shape[0]),
-                                            c_int(logits.shape[1]), c_longlong(logits.stride(0)), _stream())
-    _check(rc, "argmax")
-
-
-def sample(out_ids, logits, temperature, top_k, top_p, min_p, uniform, recent=None, rep_pen=None,
-           freq_pen=None, pres_pen=None) -> None:
-    """One token per row of logits (float32; rewritten in place by the penalties).  Per-row
-    parameters are device tensors: temperature/top_p/min_p/uniform float32, top_k int32; recent is
-    int32 [rows, n] of the tokens the penalties look at (-1: empty)."""
-    _need_cuda(out_ids, logits, temperature, top_k, top_p, min_p, uniform, recent, rep_pen, freq_pen, pres_pen)
-    _i32(out_ids, "out_ids"); _i32(top_k, "top_k")
-    rows, V = logits.shape
-    assert logits.dtype == torch.float32 and logits.stride(1) == 1
-    for t in (temperature, top_p, min_p, uniform):
-        assert t.dtype == torch.float32 and t.is_contiguous() and t.numel() >= rows
-    recent_n = 0
-    if recent is not None:
-        _i32(recent, "recent")
-        recent_n = recent.shape[1]
-        for t in (rep_pen, freq_pen, pres_pen):
-            assert t is not None and t.dtype == torch.float32 and t.numel() >= rows
-    rc = load_library("sampling").qv_sample(
-        _ptr(out_ids), _ptr(logits), c_int(rows), c_int(V), c_longlong(logits.stride(0)), _ptr(temperature),
-        _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform), _ptr(recent), c_int(recent_n), _ptr(rep_pen),
-        _ptr(freq_pen), _ptr(pres_pen), _stream())
-    _check(rc, "sample")

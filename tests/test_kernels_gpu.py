@@ -241,3 +241,88 @@ def test_sampler_same_row_same_number_same_token_whatever_the_batch():
     batch = torch.cat([rnd(3, V, seed=55), a, rnd(2, V, seed=56)])
     us = [0.1, 0.9, 0.5, 0.4321, 0.7, 0.2]
     assert _sample(batch, 0.8, 40, 0.95, 0.05, us)[3] == alone
+
+
+# ------------------------------------------------------------------ tensor-core attention (bfloat16)
+
+def _segments(lens_ctx, H, Hkv, hd, page, seed, window=0):
+    """Several requests; request i has ctx tokens cached of which the last q are this step's
+    queries.  Pages are scattered.  Returns everything the kernels need and the plain reference."""
+    g = torch.Generator().manual_seed(seed)
+    S = len(lens_ctx)
+    n_blocks = [-(-c // page) for _, c in lens_ctx]
+    n_pages = sum(n_blocks) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max(n_blocks)
+    bt = torch.full((S, width), n_pages - 1, dtype=torch.int32)
+    cache = torch.zeros(n_pages, 2, Hkv, page, hd, dtype=torch.bfloat16)
+    qs, refs, pos, seg, qstart, pos0 = [], [], [], [], [0], []
+    for i, (qlen, c) in enumerate(lens_ctx):
+        pages = [perm.pop() for _ in range(n_blocks[i])]
+        bt[i, :len(pages)] = torch.tensor(pages, dtype=torch.int32)
+        k = (torch.randn(c, Hkv, hd, generator=g) * 1.5).to(torch.bfloat16)
+        v = torch.randn(c, Hkv, hd, generator=g).to(torch.bfloat16)
+        qfull = (torch.randn(c, H, hd, generator=g) * 1.5).to(torch.bfloat16)
+        for t in range(c):
+            cache[pages[t // page], 0, :, t % page] = k[t]
+            cache[pages[t // page], 1, :, t % page] = v[t]
+        ref = plain.attention(qfull.double(), k.double(), v.double(), window=window)[c - qlen:]
+        qs.append(qfull[c - qlen:].reshape(qlen, H * hd))
+        refs.append(ref.reshape(qlen, H * hd))
+        pos += list(range(c - qlen, c))
+        seg += [i] * qlen
+        qstart.append(qstart[-1] + qlen)
+        pos0.append(c - qlen)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return dict(q=torch.cat(qs).to(DEV), cache=cache.to(DEV), bt=bt.to(DEV), pos=i32(pos), seg=i32(seg), qstart=i32(qstart),
+                pos0=i32(pos0), ref=torch.cat(refs), S=S, max_q=max(q for q, _ in lens_ctx), max_ctx=max(c for _, c in lens_ctx))
+
+
+ATT_SHAPES = [(4, 4, 16, 16, 0), (6, 2, 32, 16, 0), (5, 1, 48, 32, 0), (8, 2, 64, 16, 0), (3, 3, 80, 16, 0),
+              (12, 4, 96, 64, 0), (14, 2, 112, 16, 0), (32, 8, 128, 16, 0), (16, 1, 128, 16, 0), (4, 2, 64, 16, 37)]
+
+
+@pytest.mark.parametrize("H,Hkv,hd,page,window", ATT_SHAPES)
+def test_attention_prefill_bf16(H, Hkv, hd, page, window):
+    d = _segments([(70, 70), (1, 33), (130, 200), (2, 2), (16, 48), (1, 1)], H, Hkv, hd, page, seed=61, window=window)
+    out = torch.full_like(d["q"], float("nan"))
+    assert ops.attention_prefill_bf16(out, d["q"], d["cache"], d["qstart"], d["pos0"], d["bt"], d["S"], d["max_q"], H, Hkv, hd,
+                                      page, window, 1.0 / math.sqrt(hd))
+    assert torch.allclose(out.double().cpu(), d["ref"], rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("splits", [1, 3, 16])
+@pytest.mark.parametrize("H,Hkv,hd,page,window", ATT_SHAPES)
+def test_attention_decode_bf16(H, Hkv, hd, page, window, splits):
+    d = _segments([(1, 70), (1, 1), (1, 333), (1, 16), (1, 17), (1, 1024), (1, 64)], H, Hkv, hd, page, seed=62, window=window)
+    out = torch.full_like(d["q"], float("nan"))
+    assert ops.attention_decode_bf16(out, d["q"], d["cache"], d["pos"], d["seg"], d["bt"], H, Hkv, hd, page, window,
+                                     1.0 / math.sqrt(hd), splits)
+    assert torch.allclose(out.double().cpu(), d["ref"], rtol=2e-2, atol=2e-2)
+
+
+def test_attention_bf16_finds_a_far_key_and_respects_page_edges():
+    """A key deep in the context is made to dominate; both kernels must see it, at a page's edge too."""
+    H, Hkv, hd, page = 8, 2, 128, 16
+    for far in (0, 15, 16, 511, 512):
+        d = _segments([(1, 900)], H, Hkv, hd, page, seed=70 + far)
+        pages = d["bt"][0].tolist()
+        q = d["q"].view(1, H, hd)
+        d["cache"][pages[far // page], 0, 0, far % page] = (q[0, 1].float() * 6.0).to(torch.bfloat16)   # kv head 0 serves heads 0..3
+        d["cache"][pages[far // page], 1, 0, far % page] = 50.0
+        for fn in ("decode", "prefill"):
+            out = torch.zeros_like(d["q"])
+            if fn == "decode":
+                assert ops.attention_decode_bf16(out, d["q"], d["cache"], d["pos"], d["seg"], d["bt"], H, Hkv, hd, page, 0, 1 / math.sqrt(hd), 4)
+            else:
+                assert ops.attention_prefill_bf16(out, d["q"], d["cache"], d["qstart"], d["pos0"], d["bt"], 1, 1, H, Hkv, hd, page, 0, 1 / math.sqrt(hd))
+            assert float(out.view(H, hd)[1].float().min()) > 49.0, f"{fn}: key {far} was not found"
+
+
+def test_attention_bf16_refuses_what_it_cannot_do():
+    d = _segments([(1, 20)], 4, 4, 16, 16, seed=80)
+    q = torch.zeros(1, 4 * 144, dtype=torch.bfloat16, device=DEV)
+    cache = torch.zeros(3, 2, 4, 16, 144, dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros_like(q)
+    assert not ops.attention_decode_bf16(out, q, cache, d["pos"], d["seg"], d["bt"], 4, 4, 144, 16, 0, 0.1, 1)    # head size 144
+    assert not ops.attention_prefill_bf16(out, q, cache, d["qstart"], d["pos0"], d["bt"], 1, 1, 4, 4, 144, 16, 0, 0.1)
