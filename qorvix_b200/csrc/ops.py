@@ -296,3 +296,39 @@ def attention(out, q, cache_layer, ctx, block_table, H, Hkv, hd, page, window, s
                                     ctx.max_q_len, H, Hkv, hd, page, window, scale):
             return
     attention_generic(out, q, cache_layer, ctx.tok_pos, ctx.tok_seg, block_table, H, Hkv, hd, page, window, scale)
+
+
+# ------------------------------------------------------------------ sampling
+
+def argmax(out_ids, logits) -> None:
+    """out_ids[r] = index of the first maximum of logits[r] (float32)."""
+    _need_cuda(out_ids, logits)
+    _i32(out_ids, "out_ids")
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out_ids.numel() >= logits.shape[0]
+    rc = load_library("sampling").qv_argmax(_ptr(out_ids), _ptr(logits), c_int(logits.shape[0]),
+                                            c_int(logits.shape[1]), c_longlong(logits.stride(0)), _stream())
+    _check(rc, "argmax")
+
+
+def sample(out_ids, logits, temperature, top_k, top_p, min_p, uniform, recent=None, rep_pen=None,
+           freq_pen=None, pres_pen=None) -> None:
+    """One token per row of logits (float32; rewritten in place by the penalties).  Per-row
+    parameters are device tensors: temperature/top_p/min_p/uniform float32, top_k int32; recent is
+    int32 [rows, n] of the tokens the penalties look at (-1: empty)."""
+    _need_cuda(out_ids, logits, temperature, top_k, top_p, min_p, uniform, recent, rep_pen, freq_pen, pres_pen)
+    _i32(out_ids, "out_ids"); _i32(top_k, "top_k")
+    rows, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    for t in (temperature, top_p, min_p, uniform):
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.numel() >= rows
+    recent_n = 0
+    if recent is not None:
+        _i32(recent, "recent")
+        recent_n = recent.shape[1]
+        for t in (rep_pen, freq_pen, pres_pen):
+            assert t is not None and t.dtype == torch.float32 and t.numel() >= rows
+    rc = load_library("sampling").qv_sample(
+        _ptr(out_ids), _ptr(logits), c_int(rows), c_int(V), c_longlong(logits.stride(0)), _ptr(temperature),
+        _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform), _ptr(recent), c_int(recent_n), _ptr(rep_pen),
+        _ptr(freq_pen), _ptr(pres_pen), _stream())
+    _check(rc, "sample")
