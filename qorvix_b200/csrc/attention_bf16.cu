@@ -413,3 +413,45 @@ extern "C" int qv_attn_decode_bf16(void* out, int ld_out, const void* q, int ld_
 #undef CASE
   return QV_ERR_UNSUPPORTED;
 }
+
+// ---------------------------------------------------------------- decode without allocation
+// See attention_noalloc.h.  The workspace of the key slices is this array; host code may not
+// use its name as a pointer (on the host the name stands for a shadow object, not for device
+// memory), so the device address is looked up once per device and handed to the kernel.
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float g_decode_scratch[QV_ATTN_STATIC_SCRATCH_FLOATS];
+
+#define QV_MAX_DEVICES 64
+static float* g_decode_scratch_addr[QV_MAX_DEVICES];     // per device, filled on that device's first call
+
+extern "C" int qv_attn_decode_bf16_static(void* out, int ld_out, const void* q, int ld_q, const void* cache, const int* tok_pos,
+                                          const int* tok_seg, const int* block_table, int max_blocks, int T, int H, int Hkv,
+                                          int hd, int page, int window, float scale, int splits, void* stream) {
+  if (T <= 0) return 0;
+  if (splits < 1) return QV_ERR_UNSUPPORTED;
+  if (splits > 1 && (long long)T * H * splits * (hd + 2) > (long long)QV_ATTN_STATIC_SCRATCH_FLOATS)
+    return QV_ERR_STATIC_SCRATCH_TOO_SMALL;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= QV_MAX_DEVICES) return QV_ERR_UNSUPPORTED;
+  if (g_decode_scratch_addr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_decode_scratch);    // the address on the current device
+    if (e != cudaSuccess) return (int)e;
+    g_decode_scratch_addr[dev] = p;
+  }
+  return qv_attn_decode_bf16(out, ld_out, q, ld_q, cache, tok_pos, tok_seg, block_table, max_blocks, T, H, Hkv, hd, page,
+                             window, scale, splits, g_decode_scratch_addr[dev], stream);
+}
+
+extern "C" const char* qv_attn_decode_static_strerror(int code) {
+  if (code == 0) return "ok";
+  if (code == QV_ERR_STATIC_SCRATCH_TOO_SMALL)
+    return "T * H * splits * (head_dim + 2) exceeds the library's built-in workspace (QV_ATTN_STATIC_SCRATCH_FLOATS); "
+           "use fewer slices or tokens per call, or qv_attn_decode_bf16 with a workspace of your own";
+  if (code == QV_ERR_UNSUPPORTED) return "sizes or alignment this kernel does not take";
+  if (code == QV_ERR_TOO_LARGE) return "too many tokens or heads for one launch";
+  return cudaGetErrorString((cudaError_t)code);
+}
