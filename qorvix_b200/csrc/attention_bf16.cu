@@ -92,23 +92,41 @@ template <int HD> struct RowState {
 // One block of 16 keys starting at absolute key index `base` (a multiple of 16).
 // kpage / vpage: this kv head's K and V rows of the page that holds the block, at the block's
 // first key.  Row r in {0,1} (tile rows g, g+8) sees keys in [lo[r], hi[r]] (inclusive).
-template <int HD>
+// EARLY_V: the V rows are requested together with the K rows, before the scores are formed,
+// so that both round trips to memory overlap (decode, where latency is what costs).
+template <int HD, bool EARLY_V>
 __device__ __forceinline__ void block16(RowState<HD>& st, const QFrag<HD>& q, const bf16* __restrict__ kblk,
                                         const bf16* __restrict__ vblk, int base, const int* lo, const int* hi,
                                         float scale_log2, int g, int tg) {
   constexpr int KW = Shape<HD>::KW, KCH = Shape<HD>::KCH, VW = Shape<HD>::VW, VCH = Shape<HD>::VCH;
   float s[2][4];
+  Words<KW> kw[2][KCH];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const bf16* krow = kblk + (size_t)(8 * j + g) * HD + tg * KW * 2;
+#pragma unroll
+    for (int c = 0; c < KCH; ++c) kw[j][c] = load_words<KW>(krow + c * KW * 8);
+  }
+  const bf16* v0 = vblk + (size_t)(2 * tg) * HD + g * VW * 2;
+  Words<VW> vw[VCH][4];
+  if (EARLY_V) {
+#pragma unroll
+    for (int c = 0; c < VCH; ++c) {
+      vw[c][0] = load_words<VW>(v0 + c * VW * 16);
+      vw[c][1] = load_words<VW>(v0 + HD + c * VW * 16);
+      vw[c][2] = load_words<VW>(v0 + 8 * HD + c * VW * 16);
+      vw[c][3] = load_words<VW>(v0 + 9 * HD + c * VW * 16);
+    }
+  }
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-    const bf16* krow = kblk + (size_t)(8 * j + g) * HD + tg * KW * 2;
 #pragma unroll
     for (int c = 0; c < KCH; ++c) {
-      const Words<KW> kw = load_words<KW>(krow + c * KW * 8);
 #pragma unroll
       for (int step = 0; step < KW / 2; ++step)
         mma_bf16(s[j], q.w[c][0][2 * step], q.w[c][1][2 * step], q.w[c][0][2 * step + 1], q.w[c][1][2 * step + 1],
-                 kw.w[2 * step], kw.w[2 * step + 1]);
+                 kw[j][c].w[2 * step], kw[j][c].w[2 * step + 1]);
     }
   }
   // mask, running maximum
@@ -157,19 +175,20 @@ __device__ __forceinline__ void block16(RowState<HD>& st, const QFrag<HD>& q, co
   }
   // P.V: this thread supplies keys 2tg, 2tg+1, 8+2tg, 9+2tg for output column n = g of each n-tile;
   // n-tile e of chunk c is head dim c*VW*16 + g*VW*2 + e.
-  const bf16* v0 = vblk + (size_t)(2 * tg) * HD + g * VW * 2;
 #pragma unroll
   for (int c = 0; c < VCH; ++c) {
-    const Words<VW> a = load_words<VW>(v0 + c * VW * 16);
-    const Words<VW> b = load_words<VW>(v0 + HD + c * VW * 16);
-    const Words<VW> cc = load_words<VW>(v0 + 8 * HD + c * VW * 16);
-    const Words<VW> d = load_words<VW>(v0 + 9 * HD + c * VW * 16);
+    if (!EARLY_V) {
+      vw[c][0] = load_words<VW>(v0 + c * VW * 16);
+      vw[c][1] = load_words<VW>(v0 + HD + c * VW * 16);
+      vw[c][2] = load_words<VW>(v0 + 8 * HD + c * VW * 16);
+      vw[c][3] = load_words<VW>(v0 + 9 * HD + c * VW * 16);
+    }
 #pragma unroll
     for (int e = 0; e < VW * 2; ++e) {
       const int w = e >> 1;
       const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
-      const uint32_t b0 = __byte_perm(a.w[w], b.w[w], sel);
-      const uint32_t b1 = __byte_perm(cc.w[w], d.w[w], sel);
+      const uint32_t b0 = __byte_perm(vw[c][0].w[w], vw[c][1].w[w], sel);
+      const uint32_t b1 = __byte_perm(vw[c][2].w[w], vw[c][3].w[w], sel);
       mma_bf16(st.o[c * VW * 2 + e], p[0], p[1], p[2], p[3], b0, b1);
     }
   }
@@ -219,7 +238,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(bf16* __restrict__ ou
   const size_t v_off = (size_t)Hkv * page * HD;
   for (int base = k_begin; base <= k_end; base += 16) {
     const bf16* kblk = cache + (size_t)bt[base / page] * page_elems + ((size_t)kvh * page + (base % page)) * HD;
-    block16<HD>(st, qf, kblk, kblk + v_off, base, lo, hi, scale_log2, g, tg);
+    block16<HD, false>(st, qf, kblk, kblk + v_off, base, lo, hi, scale_log2, g, tg);
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -272,7 +291,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(bf16* __restrict__ out
   const size_t v_off = (size_t)Hkv * page * HD;
   for (int base = k_begin + 16 * warp; base < k_stop; base += 64) {
     const bf16* kblk = cache + (size_t)bt[base / page] * page_elems + ((size_t)kvh * page + (base % page)) * HD;
-    block16<HD>(st, qf, kblk, kblk + v_off, base, lo, hi, scale_log2, g, tg);
+    block16<HD, true>(st, qf, kblk, kblk + v_off, base, lo, hi, scale_log2, g, tg);
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {

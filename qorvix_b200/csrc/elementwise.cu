@@ -32,30 +32,89 @@ extern "C" int qv_embed(float* out, const void* table, const int* ids, int T, in
 //   if write_residual: residual[s] = x              (only without row_idx)
 //   out[r] = (x * rsqrt(mean(x^2) + eps)) * w
 // One block per row; the row is staged in shared memory so it is read once.
-template <typename TD, typename TO>
-__global__ void add_rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ residual,
+template <typename TD> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *(const float4*)p; }
+};
+template <> struct Vec4<bf16> {
+  static __device__ __forceinline__ float4 load(const bf16* p) {
+    const uint2 v = *(const uint2*)p;
+    const __nv_bfloat162 a = *(const __nv_bfloat162*)&v.x, b = *(const __nv_bfloat162*)&v.y;
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  }
+};
+__device__ __forceinline__ void store4(float* p, float4 v) { *(float4*)p = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u; u.x = *(uint32_t*)&a; u.y = *(uint32_t*)&b;
+  *(uint2*)p = u;
+}
+
+// VEC: rows are read four elements at a time, all loads of a thread issued before any is used
+// (d a multiple of 4, at most 4 * 4 * blockDim elements); else one element at a time.
+template <typename TD, typename TO, bool VEC>
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ residual,
                                    const TD* __restrict__ delta, const float* __restrict__ w,
                                    const int* __restrict__ row_idx, int d, float eps,
                                    int write_residual) {
   extern __shared__ float smem[];
   float* xs = smem;            // d floats
-  float* red = smem + d;       // 33 floats
+  float* red = VEC ? smem : smem + d;       // 33 floats
   const int r = blockIdx.x;
   const int s = row_idx ? row_idx[r] : r;
   float* res = residual + (size_t)s * d;
   const TD* dl = delta ? delta + (size_t)s * d : nullptr;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float x = res[i];
-    if (dl) x += to_f(dl[i]);
-    xs[i] = x;
-    if (write_residual) res[i] = x;
-    ss += x * x;
-  }
-  const float total = block_sum(ss, red);
-  const float scale = 1.0f / sqrtf(total / (float)d + eps);
   TO* o = out + (size_t)r * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f<TO>(xs[i] * scale * w[i]);
+  float ss = 0.f;
+  if constexpr (VEC) {
+    constexpr int MAXV = 4;
+    float4 x[MAXV];
+    const int nvec = d >> 2;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int i = threadIdx.x + k * 256;
+      x[k] = i < nvec ? *(const float4*)(res + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (dl) {
+#pragma unroll
+      for (int k = 0; k < MAXV; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < nvec) {
+          const float4 dv = Vec4<TD>::load(dl + 4 * i);
+          x[k].x += dv.x; x[k].y += dv.y; x[k].z += dv.z; x[k].w += dv.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int i = threadIdx.x + k * 256;
+      if (i < nvec) {
+        if (write_residual) *(float4*)(res + 4 * i) = x[k];
+        ss += x[k].x * x[k].x + x[k].y * x[k].y + x[k].z * x[k].z + x[k].w * x[k].w;
+      }
+    }
+    const float total = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(total / (float)d + eps);
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int i = threadIdx.x + k * 256;
+      if (i < nvec) {
+        const float4 wv = *(const float4*)(w + 4 * i);
+        store4(o + 4 * i, make_float4(x[k].x * scale * wv.x, x[k].y * scale * wv.y, x[k].z * scale * wv.z, x[k].w * scale * wv.w));
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      float x = res[i];
+      if (dl) x += to_f(dl[i]);
+      xs[i] = x;
+      if (write_residual) res[i] = x;
+      ss += x * x;
+    }
+    const float total = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(total / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f<TO>(xs[i] * scale * w[i]);
+  }
 }
 
 extern "C" int qv_add_rmsnorm(void* out, float* residual, const void* delta, const float* w,
@@ -66,13 +125,20 @@ extern "C" int qv_add_rmsnorm(void* out, float* residual, const void* delta, con
   if (smem > 200 * 1024) return QV_ERR_TOO_LARGE;
   if (row_idx && write_residual) return QV_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
+  // the vector path keeps the row in registers: d a multiple of 4, at most 4096 elements, rows 16-byte aligned
+  const bool vec = (d % 4 == 0) && d <= 4 * 4 * 256 && (((uintptr_t)out | (uintptr_t)residual | (uintptr_t)delta | (uintptr_t)w) & 15) == 0;
 #define LAUNCH_NORM(TD, TO)                                                                          \
   do {                                                                                               \
-    if (smem > 48 * 1024)                                                                            \
-      cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
-                           (int)smem);                                                               \
-    add_rmsnorm_kernel<TD, TO><<<rows, 256, smem, st>>>((TO*)out, residual, (const TD*)delta, w,     \
-                                                        row_idx, d, eps, write_residual);            \
+    if (vec) {                                                                                       \
+      add_rmsnorm_kernel<TD, TO, true><<<rows, 256, 48 * sizeof(float), st>>>(                      \
+          (TO*)out, residual, (const TD*)delta, w, row_idx, d, eps, write_residual);                 \
+    } else {                                                                                         \
+      if (smem > 48 * 1024)                                                                          \
+        cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, false>,                                      \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
+      add_rmsnorm_kernel<TD, TO, false><<<rows, 256, smem, st>>>((TO*)out, residual,                 \
+                                                 (const TD*)delta, w, row_idx, d, eps, write_residual); \
+    }                                                                                                \
   } while (0)
   if (delta_dt == QV_DT_F32 && out_dt == QV_DT_F32) LAUNCH_NORM(float, float);
   else if (delta_dt == QV_DT_BF16 && out_dt == QV_DT_BF16) LAUNCH_NORM(bf16, bf16);
@@ -97,7 +163,9 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int ld, T* __restrict_
                                      const int* __restrict__ tok_pos, const int* __restrict__ tok_seg,
                                      const int* __restrict__ block_table, int max_blocks, int H,
                                      int Hkv, int hd, int rot, int page) {
+  // grid (token, head slot): slots 0..H-1 are q heads, H..H+Hkv-1 k heads, H+Hkv..H+2Hkv-1 v heads
   const int t = blockIdx.x;
+  const int head = blockIdx.y;
   const int pos = tok_pos[t];
   T* row = qkv + (size_t)t * ld;
   const int half = rot >> 1;
@@ -110,34 +178,23 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int ld, T* __restrict_
     kdst = cache + (size_t)pg * page_elems + (size_t)(pos % page) * hd;
     vdst = kdst + (size_t)Hkv * page * hd;
   }
-  // rotations: heads 0..H-1 are q, H..H+Hkv-1 are k
-  const int n_rot = (H + Hkv) * half;
-  for (int it = threadIdx.x; it < n_rot; it += blockDim.x) {
-    const int head = it / half, i = it - head * half;
+  if (head < H + Hkv) {
     T* v = row + (size_t)head * hd;
-    const float a = to_f(v[i]), b = to_f(v[i + half]);
-    const float2 c = cs[i];
-    const float ra = a * c.x - b * c.y;
-    const float rb = a * c.y + b * c.x;
-    if (head < H || !cache) {
-      v[i] = from_f<T>(ra);
-      v[i + half] = from_f<T>(rb);
-    } else {
-      T* kd = kdst + (size_t)(head - H) * page * hd;
-      kd[i] = from_f<T>(ra);
-      kd[i + half] = from_f<T>(rb);
+    const bool to_cache = head >= H && cache;
+    T* dst = to_cache ? kdst + (size_t)(head - H) * page * hd : v;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      const float a = to_f(v[i]), b = to_f(v[i + half]);
+      const float2 c = cs[i];
+      dst[i] = from_f<T>(a * c.x - b * c.y);
+      dst[i + half] = from_f<T>(a * c.y + b * c.x);
     }
-  }
-  if (!cache) return;
-  // pass-through dims of k (beyond rot) and all of v
-  const int tail = hd - rot;
-  for (int it = threadIdx.x; it < Hkv * tail; it += blockDim.x) {
-    const int head = it / tail, i = rot + (it - head * tail);
-    kdst[(size_t)head * page * hd + i] = row[(size_t)(H + head) * hd + i];
-  }
-  for (int it = threadIdx.x; it < Hkv * hd; it += blockDim.x) {
-    const int head = it / hd, i = it - head * hd;
-    vdst[(size_t)head * page * hd + i] = row[(size_t)(H + Hkv + head) * hd + i];
+    if (to_cache)      // dims beyond the rotated ones pass through
+      for (int i = rot + threadIdx.x; i < hd; i += blockDim.x) dst[i] = v[i];
+  } else if (cache) {
+    const int vh = head - H - Hkv;
+    const T* v = row + (size_t)head * hd;
+    T* dst = vdst + (size_t)vh * page * hd;
+    for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = v[i];
   }
 }
 
@@ -147,8 +204,9 @@ extern "C" int qv_rope_kv_write(void* qkv, int ld, void* cache, const float* cos
                                 int dt, void* stream) {
   if (T <= 0) return 0;
   if (rot < 0 || rot > hd || (rot & 1)) return QV_ERR_UNSUPPORTED;
+  if (H + 2 * Hkv > 65535) return QV_ERR_TOO_LARGE;
   QV_DISPATCH_DT(dt, TT,
-                 rope_kv_write_kernel<TT><<<T, 256, 0, (cudaStream_t)stream>>>(
+                 rope_kv_write_kernel<TT><<<dim3(T, H + 2 * Hkv), 64, 0, (cudaStream_t)stream>>>(
                      (TT*)qkv, ld, (TT*)cache, (const float2*)cos_sin, table_rows, tok_pos, tok_seg,
                      block_table, max_blocks, H, Hkv, hd, rot, page));
   return qv_launch_status();

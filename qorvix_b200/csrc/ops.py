@@ -252,9 +252,9 @@ def attention_prefill_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_tab
 
 
 def decode_splits(T: int, Hkv: int, max_ctx: int) -> int:
-    """How many slices of the keys each (token, kv head) is cut into, so that about two CTAs per
+    """How many slices of the keys each (token, kv head) is cut into, so that about three CTAs per
     SM are busy; a function of the step's shape only (a captured step keeps it)."""
-    want = -(-2 * 148 // max(1, T * Hkv))
+    want = -(-3 * 148 // max(1, T * Hkv))
     return max(1, min(16, want, -(-max_ctx // 64)))
 
 
