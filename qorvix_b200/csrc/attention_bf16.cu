@@ -207,6 +207,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(bf16* __restrict__ ou
                                                            const bf16* __restrict__ cache, const int* __restrict__ seg_q_start,
                                                            const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
                                                            int max_blocks, int H, int Hkv, int page, int window, float scale_log2) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int seg = blockIdx.z, h = blockIdx.y;
   const int q0 = seg_q_start[seg], qlen = seg_q_start[seg + 1] - q0;
   const int tile0 = blockIdx.x * 64;
@@ -267,6 +269,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(bf16* __restrict__ out
                                                           int max_blocks, int H, int Hkv, int page, int window, float scale_log2,
                                                           int splits, float* __restrict__ partial) {
   extern __shared__ float sm[];                 // [4 warps][16 rows][HD + 2]
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
   const int G = H / Hkv;
@@ -340,6 +344,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(bf16* __restrict__ out
 
 // merges the slices of one (token, head) in slice order
 __global__ void attn_combine_kernel(bf16* __restrict__ out, int ld_out, const float* __restrict__ partial, int H, int hd, int splits) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.y, h = blockIdx.x;
   const int row = hd + 2;
   const float* src = partial + ((size_t)t * H + h) * splits * row;
@@ -362,9 +368,8 @@ int launch_prefill(bf16* out, int ld_out, const bf16* q, int ld_q, const bf16* c
                    const int* bt, int max_blocks, int S, int max_q_len, int H, int Hkv, int page, int window, float scale_log2,
                    cudaStream_t st) {
   dim3 grid((max_q_len + 63) / 64, H, S);
-  attn_prefill_kernel<HD><<<grid, 128, 0, st>>>(out, ld_out, q, ld_q, cache, seg_q_start, seg_pos0, bt, max_blocks, H, Hkv, page,
-                                               window, scale_log2);
-  return qv_launch_status();
+  return qv_launch(attn_prefill_kernel<HD>, grid, dim3(128), 0, st, out, ld_out, q, ld_q, cache, seg_q_start, seg_pos0, bt,
+                   max_blocks, H, Hkv, page, window, scale_log2);
 }
 
 template <int HD>
@@ -379,12 +384,11 @@ int launch_decode(bf16* out, int ld_out, const bf16* q, int ld_q, const bf16* ca
     configured = true;
   }
   dim3 grid(splits, Hkv, T);
-  attn_decode_kernel<HD><<<grid, 128, smem, st>>>(out, ld_out, q, ld_q, cache, tok_pos, tok_seg, bt, max_blocks, H, Hkv, page,
-                                                  window, scale_log2, splits, partial);
-  int rc = qv_launch_status();
+  int rc = qv_launch(attn_decode_kernel<HD>, grid, dim3(128), smem, st, out, ld_out, q, ld_q, cache, tok_pos, tok_seg, bt,
+                     max_blocks, H, Hkv, page, window, scale_log2, splits, partial);
   if (rc || splits == 1) return rc;
-  attn_combine_kernel<<<dim3(H, T), HD < 128 ? 64 : 128, 0, st>>>(out, ld_out, partial, H, HD, splits);
-  return qv_launch_status();
+  return qv_launch(attn_combine_kernel, dim3(H, T), dim3(HD < 128 ? 64 : 128), 0, st, out, ld_out, (const float*)partial, H,
+                   (int)HD, splits);
 }
 
 }  // namespace

@@ -8,6 +8,9 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#include <utility>
 
 #define QV_DT_F32 0
 #define QV_DT_BF16 1
@@ -53,6 +56,40 @@ __device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats *
 }
 
 static inline int qv_launch_status() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch: a kernel launched through qv_launch may be scheduled while the
+// kernel before it in the stream is still running; it must call pdl_wait() before it reads or
+// writes anything the earlier kernel touches, and what it does before that call (setting up
+// barriers, fetching weights, which no kernel writes) overlaps the earlier kernel's tail.
+// pdl_launch_dependents() lets the kernel after this one be scheduled likewise.  In a kernel
+// launched the ordinary way both calls do nothing.  QORVIX_PDL=0 switches the attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool qv_pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("QORVIX_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int qv_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = qv_pdl_enabled() ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 #define QV_DISPATCH_DT(dt, T, ...)                                   \
   do {                                                               \

@@ -10,6 +10,8 @@
 template <typename TW>
 __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ table,
                              const int* __restrict__ ids, int d, int vocab) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;   // ids are validated on the host; never read out of bounds
@@ -22,8 +24,8 @@ extern "C" int qv_embed(float* out, const void* table, const int* ids, int T, in
                         int table_dt, void* stream) {
   if (T <= 0) return 0;
   QV_DISPATCH_DT(table_dt, TW,
-                 embed_kernel<TW><<<T, 256, 0, (cudaStream_t)stream>>>(out, (const TW*)table, ids, d, vocab));
-  return qv_launch_status();
+                 return qv_launch(embed_kernel<TW>, dim3(T), dim3(256), 0, (cudaStream_t)stream, out, (const TW*)table, ids, d, vocab));
+  return QV_ERR_UNSUPPORTED;
 }
 
 // ---------------------------------------------------------------- add + rmsnorm (+ gather)
@@ -58,6 +60,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(TO* __restrict__ out, 
                                    const int* __restrict__ row_idx, int d, float eps,
                                    int write_residual) {
   extern __shared__ float smem[];
+  pdl_wait();
+  pdl_launch_dependents();
   float* xs = smem;            // d floats
   float* red = VEC ? smem : smem + d;       // 33 floats
   const int r = blockIdx.x;
@@ -125,18 +129,19 @@ extern "C" int qv_add_rmsnorm(void* out, float* residual, const void* delta, con
   if (smem > 200 * 1024) return QV_ERR_TOO_LARGE;
   if (row_idx && write_residual) return QV_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
+  int rc = 0;
   // the vector path keeps the row in registers: d a multiple of 4, at most 4096 elements, rows 16-byte aligned
   const bool vec = (d % 4 == 0) && d <= 4 * 4 * 256 && (((uintptr_t)out | (uintptr_t)residual | (uintptr_t)delta | (uintptr_t)w) & 15) == 0;
 #define LAUNCH_NORM(TD, TO)                                                                          \
   do {                                                                                               \
     if (vec) {                                                                                       \
-      add_rmsnorm_kernel<TD, TO, true><<<rows, 256, 48 * sizeof(float), st>>>(                      \
+      rc = qv_launch(add_rmsnorm_kernel<TD, TO, true>, dim3(rows), dim3(256), 48 * sizeof(float), st, \
           (TO*)out, residual, (const TD*)delta, w, row_idx, d, eps, write_residual);                 \
     } else {                                                                                         \
       if (smem > 48 * 1024)                                                                          \
         cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, false>,                                      \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
-      add_rmsnorm_kernel<TD, TO, false><<<rows, 256, smem, st>>>((TO*)out, residual,                 \
+      rc = qv_launch(add_rmsnorm_kernel<TD, TO, false>, dim3(rows), dim3(256), smem, st, (TO*)out, residual, \
                                                  (const TD*)delta, w, row_idx, d, eps, write_residual); \
     }                                                                                                \
   } while (0)
@@ -146,7 +151,7 @@ extern "C" int qv_add_rmsnorm(void* out, float* residual, const void* delta, con
   else if (delta_dt == QV_DT_BF16 && out_dt == QV_DT_F32) LAUNCH_NORM(bf16, float);
   else return QV_ERR_UNSUPPORTED;
 #undef LAUNCH_NORM
-  return qv_launch_status();
+  return rc;
 }
 
 // ---------------------------------------------------------------- rotary + paged KV write
@@ -164,6 +169,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int ld, T* __restrict_
                                      const int* __restrict__ block_table, int max_blocks, int H,
                                      int Hkv, int hd, int rot, int page) {
   // grid (token, head slot): slots 0..H-1 are q heads, H..H+Hkv-1 k heads, H+Hkv..H+2Hkv-1 v heads
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int head = blockIdx.y;
   const int pos = tok_pos[t];
@@ -206,32 +213,39 @@ extern "C" int qv_rope_kv_write(void* qkv, int ld, void* cache, const float* cos
   if (rot < 0 || rot > hd || (rot & 1)) return QV_ERR_UNSUPPORTED;
   if (H + 2 * Hkv > 65535) return QV_ERR_TOO_LARGE;
   QV_DISPATCH_DT(dt, TT,
-                 rope_kv_write_kernel<TT><<<dim3(T, H + 2 * Hkv), 64, 0, (cudaStream_t)stream>>>(
+                 return qv_launch(rope_kv_write_kernel<TT>, dim3(T, H + 2 * Hkv), dim3(64), 0, (cudaStream_t)stream,
                      (TT*)qkv, ld, (TT*)cache, (const float2*)cos_sin, table_rows, tok_pos, tok_seg,
                      block_table, max_blocks, H, Hkv, hd, rot, page));
-  return qv_launch_status();
+  return QV_ERR_UNSUPPORTED;
 }
 
 // ---------------------------------------------------------------- swiglu
-// gu[t] = [gate: f | up: f] (row stride 2f); out[t, i] = gate/(1+exp(-gate)) * up.
+// out[t, i] = gate/(1+exp(-gate)) * up, with gu[t] (row stride 2f) either [gate: f | up: f] or, when
+// `interleaved`, groups of 32 columns holding 16 gate values and then the 16 up values of the same
+// features (the layout the fused tensor-core epilogue uses; f a multiple of 16).
 template <typename T>
-__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, size_t n, int f) {
+__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, size_t n, int f, int interleaved) {
+  pdl_wait();
+  pdl_launch_dependents();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / f;
     const int i = (int)(idx - t * f);
-    const float g = to_f(gu[t * 2 * f + i]);
-    const float u = to_f(gu[t * 2 * f + f + i]);
+    const int gi = interleaved ? ((i >> 4) << 5) + (i & 15) : i;
+    const int ui = interleaved ? gi + 16 : f + i;
+    const float g = to_f(gu[t * 2 * f + gi]);
+    const float u = to_f(gu[t * 2 * f + ui]);
     out[idx] = from_f<T>(g / (1.0f + expf(-g)) * u);
   }
 }
 
-extern "C" int qv_swiglu(void* out, const void* gu, int T, int f, int dt, void* stream) {
+extern "C" int qv_swiglu(void* out, const void* gu, int T, int f, int interleaved, int dt, void* stream) {
   const size_t n = (size_t)T * f;
   if (n == 0) return 0;
+  if (interleaved && (f & 15)) return QV_ERR_UNSUPPORTED;
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-  QV_DISPATCH_DT(dt, TT, swiglu_kernel<TT><<<blocks, 256, 0, (cudaStream_t)stream>>>((TT*)out, (const TT*)gu, n, f));
-  return qv_launch_status();
+  QV_DISPATCH_DT(dt, TT, return qv_launch(swiglu_kernel<TT>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (TT*)out, (const TT*)gu, n, f, interleaved));
+  return QV_ERR_UNSUPPORTED;
 }
 
 // ---------------------------------------------------------------- casts

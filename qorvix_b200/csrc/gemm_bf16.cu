@@ -125,7 +125,12 @@ struct GemmArgs {
 
 // BN: columns of the accumulator (rows of the narrow operand per tile).  SWAP: the wide operand
 // is the weight matrix (features) and the narrow one the tokens, so the tile is C^T.
-template <int BN, int STAGES, bool SWAP, typename TC>
+// SWIGLU: the weight rows come in groups of 32 (16 gate rows, then the 16 up rows of the same
+// features); the epilogue writes silu(gate) * up, so C has half as many features as W has rows.
+// bfloat16 output: the fast exponential's error (a few float32 ulp) vanishes in the rounding
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
+template <int BN, int STAGES, bool SWAP, typename TC, bool SWIGLU>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_wide,
                                                       const __grid_constant__ CUtensorMap map_narrow,
                                                       const GemmArgs args) {
@@ -166,10 +171,25 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
+      // Weights are never written by a kernel, so the first stages' weight tiles are requested
+      // before waiting for the kernel ahead in the stream; the activation tiles after.
+      const CUtensorMap* w_map = SWAP ? &map_wide : &map_narrow;
+      const CUtensorMap* x_map = SWAP ? &map_narrow : &map_wide;
+      const int w_row0 = SWAP ? wide0 : narrow0, x_row0 = SWAP ? narrow0 : wide0;
+      const int w_off = SWAP ? 0 : A_BYTES, x_off = SWAP ? A_BYTES : 0;
+      const int pre = num_kb < STAGES ? num_kb : STAGES;
+      for (int kb = 0; kb < pre; ++kb) {
+        mbar_expect_tx(&full[kb], STAGE_BYTES);
+        tma_load_2d(tiles + kb * STAGE_BYTES + w_off, w_map, &full[kb], (kb0 + kb) * BK, w_row0);
+      }
+      pdl_wait();
+      for (int kb = 0; kb < pre; ++kb)
+        tma_load_2d(tiles + kb * STAGE_BYTES + x_off, x_map, &full[kb], (kb0 + kb) * BK, x_row0);
+      for (int kb = pre; kb < num_kb; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = (kb / STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, args.err, 1)) break;
@@ -200,6 +220,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     }
   } else {
     // epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31
+    pdl_wait();                 // C, the workspace and the counters may still be in use by the kernel ahead
     const int q = warp & 3;
     // one lane per warp polls; the four warps then agree, so that either all of them take the
     // barriers below or none does
@@ -222,7 +243,28 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
           uint32_t r[32];
           tmem_ld32(taddr + c0, r);
           tmem_wait_ld();
-          if (wide_row < args.rows_wide) {
+          if (SWIGLU) {
+            if (wide_row < args.rows_wide && narrow0 + c0 < args.rows_narrow) {
+              // columns 0..15 of this chunk are gate, 16..31 up, of features (narrow0 + c0)/2 + j
+              TC* dst = C + (size_t)wide_row * args.ldc + ((narrow0 + c0) >> 1);
+              float a[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) a[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r[16 + j]));
+              if (sizeof(TC) == 2 && (((uintptr_t)dst) & 15) == 0) {
+                uint32_t w[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(a[2 * j], a[2 * j + 1]);
+                  w[j] = *(uint32_t*)&h;
+                }
+                ((uint4*)dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                ((uint4*)dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) store_out<TC>(dst + j, a[j]);
+              }
+            }
+          } else if (wide_row < args.rows_wide) {
             TC* dst = C + (size_t)wide_row * args.ldc + narrow0 + c0;
             const int ncols = args.rows_narrow - (narrow0 + c0);
             if (sizeof(TC) == 2 && ncols >= 32 && (((uintptr_t)dst) & 15) == 0) {
@@ -257,7 +299,17 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
             uint32_t r[16];
             tmem_ld16(taddr + c0, r);
             tmem_wait_ld();
-            if (frow) {
+            if (SWIGLU) {
+              // lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same features
+              const int feat = ((wide0 + q * 32) >> 1) + (lane & 15);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float mine = __uint_as_float(r[j]);
+                const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+                const int t = narrow0 + c0 + j;
+                if (lane < 16 && frow && t < ntok) store_out<TC>(C + (size_t)t * args.ldc + feat, silu_mul(mine, other));
+              }
+            } else if (frow) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const int t = narrow0 + c0 + j;
@@ -343,17 +395,16 @@ bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int bo
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES, bool SWAP, typename TC>
+template <int BN, int STAGES, bool SWAP, typename TC, bool SWIGLU = false>
 int launch(const CUtensorMap& mw, const CUtensorMap& mn, const GemmArgs& args, dim3 grid, cudaStream_t st) {
   constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  gemm_tc_kernel<BN, STAGES, SWAP, TC><<<grid, 192, smem, st>>>(mw, mn, args);
-  return qv_launch_status();
+  return qv_launch(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, grid, dim3(192), (size_t)smem, st, mw, mn, args);
 }
 
 }  // namespace
@@ -366,8 +417,11 @@ extern "C" long long qv_gemm_bf16_workspace_bytes(int max_features) { return (lo
 // K not a multiple of 8 elements, or operands whose rows do not start on 16-byte boundaries.
 extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
                                int c_dt, float* workspace, long long workspace_bytes, int* counters, int n_counters,
-                               int* err, int force_splits, void* stream) {
+                               int* err, int force_splits, int epilogue, void* stream) {
+  // epilogue 0: C[M,N] = A W^T.  epilogue 1: W's rows are 16 gate rows / 16 up rows interleaved and
+  // C[M,N/2] = silu(gate) * up (bfloat16 out, N a multiple of 32).
   if (M <= 0 || N <= 0) return 0;
+  if (epilogue != 0 && (epilogue != 1 || c_dt != QV_DT_BF16 || (N & 31))) return QV_ERR_UNSUPPORTED;
   if (K < 8 || (K & 7) || (lda & 7) || (ldw & 7)) return QV_ERR_UNSUPPORTED;
   if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return QV_ERR_UNSUPPORTED;
   if (c_dt != QV_DT_BF16 && c_dt != QV_DT_F32) return QV_ERR_UNSUPPORTED;
@@ -382,9 +436,11 @@ extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     const int tiles = (N + BM - 1) / BM;
     int splits = 1;
-    if (force_splits > 0) splits = force_splits;
+    if (epilogue == 1) splits = 1;                  // the fused activation needs whole sums
+    else if (force_splits > 0) splits = force_splits;
     else if (tiles < 96) {                          // too few CTAs to pull full bandwidth: split along K
-      splits = (148 + tiles - 1) / tiles;
+      splits = 148 / tiles;                         // as many CTAs as fit in one wave
+      if (splits < 1) splits = 1;
       if (splits > 8) splits = 8;
     }
     if (splits > total_kb) splits = total_kb;
@@ -397,9 +453,15 @@ extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int
     dim3 grid(tiles, 1, splits);
 #define SWAP_LAUNCH(BN_, ST_)                                                                     \
   (c_dt == QV_DT_BF16 ? launch<BN_, ST_, true, bf16>(mw, mn, args, grid, st) : launch<BN_, ST_, true, float>(mw, mn, args, grid, st))
-    if (bn == 16) return SWAP_LAUNCH(16, 6);
-    if (bn == 32) return SWAP_LAUNCH(32, 5);
-    return SWAP_LAUNCH(64, 4);
+    if (epilogue == 1) {
+      if (bn == 16) return launch<16, 6, true, bf16, true>(mw, mn, args, grid, st);
+      if (bn == 32) return launch<32, 5, true, bf16, true>(mw, mn, args, grid, st);
+      return launch<64, 4, true, bf16, true>(mw, mn, args, grid, st);
+    }
+    const bool one_wave = tiles * splits <= 148;     // every CTA resident at once, one per SM: deeper rings
+    if (bn == 16) return one_wave ? SWAP_LAUNCH(16, 12) : SWAP_LAUNCH(16, 6);
+    if (bn == 32) return one_wave ? SWAP_LAUNCH(32, 10) : SWAP_LAUNCH(32, 5);
+    return one_wave ? SWAP_LAUNCH(64, 8) : SWAP_LAUNCH(64, 4);
 #undef SWAP_LAUNCH
   }
   // many tokens: tokens on the 128-row side, 128 weight rows per tile
@@ -407,6 +469,7 @@ extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int
   if (!make_map(&mw, A, M, K, lda, BM) || !make_map(&mn, W, N, K, ldw, 128)) return QV_ERR_UNSUPPORTED;
   dim3 grid((M + BM - 1) / BM, (N + 127) / 128, 1);
   if (grid.y > 65535) return QV_ERR_TOO_LARGE;
+  if (epilogue == 1) return launch<128, 3, false, bf16, true>(mw, mn, args, grid, st);
   if (c_dt == QV_DT_BF16) return launch<128, 3, false, bf16>(mw, mn, args, grid, st);
   return launch<128, 3, false, float>(mw, mn, args, grid, st);
 }

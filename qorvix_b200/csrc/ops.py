@@ -127,12 +127,13 @@ def rope_kv_write(qkv, cache_layer, cos_sin, tok_pos, tok_seg, block_table, H, H
     _check(rc, "rope_kv_write")
 
 
-def swiglu(out, gu) -> None:
-    """gu [T, 2f] = [gate | up] -> out [T, f] = silu(gate) * up."""
+def swiglu(out, gu, interleaved: bool = False) -> None:
+    """gu [T, 2f] -> out [T, f] = silu(gate) * up.  gu is [gate | up], or with `interleaved` groups of
+    32 columns: 16 gate values, then the 16 up values of the same features."""
     _need_cuda(out, gu)
     T, f = out.shape
     assert gu.shape == (T, 2 * f) and gu.is_contiguous() and out.is_contiguous() and gu.dtype == out.dtype
-    rc = load_library("elementwise").qv_swiglu(_ptr(out), _ptr(gu), c_int(T), c_int(f),
+    rc = load_library("elementwise").qv_swiglu(_ptr(out), _ptr(gu), c_int(T), c_int(f), c_int(1 if interleaved else 0),
                                                c_int(dt_code(out.dtype)), _stream())
     _check(rc, "swiglu")
 
@@ -177,19 +178,22 @@ def _tc_buffers(device):
     return st
 
 
-def gemm_bf16_tc(c, a, w, force_splits: int = 0) -> bool:
-    """c[M,N] (bf16 or f32) = a[M,K] @ w[N,K]^T on the tcgen05 tensor cores.  False when the
+def gemm_bf16_tc(c, a, w, force_splits: int = 0, swiglu: bool = False) -> bool:
+    """c[M,N] (bf16 or f32) = a[M,K] @ w[N,K]^T on the tcgen05 tensor cores.  With `swiglu`, w holds
+    gate and up rows interleaved in groups of 16 and c[M,N/2] = silu(gate) * up.  False when the
     shape is one the kernel refuses (K not a multiple of 8, unaligned rows); nothing is written then."""
     _need_cuda(c, a, w)
     M, K = a.shape
     N = w.shape[0]
-    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K and c.shape == (M, N)
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+    assert c.shape == ((M, N // 2) if swiglu else (M, N))
     assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
     st = _tc_buffers(a.device)
     rc = load_library("gemm_bf16").qv_gemm_bf16_tc(
         _ptr(c), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(w.stride(0)),
         c_int(c.stride(0)), c_int(dt_code(c.dtype)), _ptr(st["workspace"]), c_longlong(st["workspace"].numel()),
-        _ptr(st["counters"]), c_int(st["counters"].numel()), _ptr(st["err"]), c_int(force_splits), _stream())
+        _ptr(st["counters"]), c_int(st["counters"].numel()), _ptr(st["err"]), c_int(force_splits),
+        c_int(1 if swiglu else 0), _stream())
     if rc == -2:
         return False
     _check(rc, "gemm_bf16_tc")
@@ -230,6 +234,18 @@ def gemm(out, x, w) -> None:
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and gemm_bf16_tc(out, x, w):
         return
     gemm_simt(out, x, w)
+
+
+def gemm_swiglu(out, x, w_interleaved) -> None:
+    """out[M,f] = silu(x Wg^T) * (x Wu^T) with gate and up rows interleaved in groups of 16 in
+    w_interleaved [2f, K]: one tensor-core kernel when it takes the shape, else the product followed
+    by the activation kernel."""
+    if (x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+            and gemm_bf16_tc(out, x, w_interleaved, swiglu=True)):
+        return
+    gu = torch.empty((x.shape[0], w_interleaved.shape[0]), device=x.device, dtype=out.dtype)
+    gemm(gu, x, w_interleaved)
+    swiglu(out, gu, interleaved=True)
 
 
 def attention_prefill_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, Hkv, hd, page,

@@ -29,12 +29,40 @@ __device__ __forceinline__ u64 fixed_weight(float x, float xmax) {
 
 // ---------------------------------------------------------------- argmax (first maximum wins)
 __global__ void argmax_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, long long ld) {
+  pdl_wait();
+  pdl_launch_dependents();
   const float* row = logits + (size_t)blockIdx.x * ld;
   float best = -INFINITY;
   int besti = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best || (v == best && i < besti)) { best = v; besti = i; }
+  if ((((uintptr_t)row) & 15) == 0) {
+    // four independent 16-byte loads in flight per thread
+    const int nvec = V >> 2;
+    const float4* row4 = (const float4*)row;
+    for (int i0 = threadIdx.x; i0 < nvec; i0 += 4 * blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = i0 + k * blockDim.x;
+        v[k] = i < nvec ? row4[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = 4 * (i0 + k * blockDim.x);
+        const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (e[j] > best || (e[j] == best && i + j < besti)) { best = e[j]; besti = i + j; }
+      }
+    }
+    for (int i = (nvec << 2) + threadIdx.x; i < V; i += blockDim.x) {
+      const float v = row[i];
+      if (v > best || (v == best && i < besti)) { best = v; besti = i; }
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = row[i];
+      if (v > best || (v == best && i < besti)) { best = v; besti = i; }
+    }
   }
   __shared__ float sv[32];
   __shared__ int si[32];
@@ -62,8 +90,7 @@ __global__ void argmax_kernel(int* __restrict__ out, const float* __restrict__ l
 
 extern "C" int qv_argmax(int* out, const float* logits, int rows, int V, long long ld, void* stream) {
   if (rows <= 0) return 0;
-  argmax_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(out, logits, V, ld);
-  return qv_launch_status();
+  return qv_launch(argmax_kernel, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, out, logits, V, ld);
 }
 
 // ---------------------------------------------------------------- sampler

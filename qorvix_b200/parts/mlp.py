@@ -17,14 +17,27 @@ class SwiGLU(FeedForward):
         self.f = int(spec.intermediate_size)
         g, u = source.get(spec.gate_proj), source.get(spec.up_proj)
         dt = torch.float32 if (g.dtype == torch.float32 or u.dtype == torch.float32) else g.dtype
-        self.gate_up = Linear(torch.cat([g.to(dt), u.to(dt)], dim=0))
+        # When the width allows, gate and up rows are interleaved in groups of 16 (16 gate rows, the 16
+        # up rows of the same features, ...), so that one tile of the product holds both halves of a
+        # feature and the activation is applied in the product's epilogue.
+        self.interleaved = self.f % 16 == 0
+        if self.interleaved:
+            k = g.shape[1]
+            fused = torch.stack([g.to(dt).view(self.f // 16, 16, k), u.to(dt).view(self.f // 16, 16, k)], dim=1)
+            self.gate_up = Linear(fused.reshape(2 * self.f, k))
+            del fused
+        else:
+            self.gate_up = Linear(torch.cat([g.to(dt), u.to(dt)], dim=0))
         del g, u
         self.down = Linear(source.get(spec.down_proj))
 
     def forward(self, x, ctx):
-        gu = self.gate_up(x, out_dtype=self.rt.dtype)
         act = torch.empty((x.shape[0], self.f), device=x.device, dtype=self.rt.dtype)
-        ops.swiglu(act, gu)
+        if self.interleaved:
+            ops.gemm_swiglu(act, x, self.gate_up.weight)
+        else:
+            gu = self.gate_up(x, out_dtype=self.rt.dtype)
+            ops.swiglu(act, gu)
         return self.down(act, out_dtype=self.rt.dtype)
 
 

@@ -66,3 +66,24 @@ def test_strided_activations_and_refused_shapes():
     ops.gemm(c, a, w)                                       # the dispatcher falls back to the CUDA cores
     ref = a.double() @ w.double().t()
     assert (c.double() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("M,f,K", [(8, 256, 128), (3, 14336, 256), (40, 512, 4096), (64, 1008, 72), (128, 64, 64),
+                                   (300, 1008, 328), (2048, 1024, 512)])
+def test_fused_swiglu_epilogue(M, f, K):
+    g, u = rnd(f, K, seed=5, scale=0.1), rnd(f, K, seed=6, scale=0.1)
+    w = torch.stack([g.view(f // 16, 16, K), u.view(f // 16, 16, K)], dim=1).reshape(2 * f, K).contiguous()
+    a = rnd(M, K, seed=7)
+    out = torch.full((M, f), float("nan"), device=DEV, dtype=torch.bfloat16)
+    assert ops.gemm_bf16_tc(out, a, w, swiglu=True)
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    gg, uu = a.double() @ g.double().t(), a.double() @ u.double().t()
+    ref = gg / (1 + torch.exp(-gg)) * uu
+    assert (out.double() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    # the unfused route over the same interleaved weight agrees
+    gu = torch.empty(M, 2 * f, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(gu, a, w)
+    out2 = torch.empty_like(out)
+    ops.swiglu(out2, gu, interleaved=True)
+    assert (out2.double() - ref).abs().max().item() <= 3e-2 * max(1.0, ref.abs().max().item())
