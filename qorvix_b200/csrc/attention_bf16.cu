@@ -260,6 +260,216 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(bf16* __restrict__ ou
   }
 }
 
+// ---------------------------------------------------------------- prefill, shared-memory tiles
+// For head sizes 64 and 128: 64 query rows and 64-key tiles of K and V staged in shared memory
+// with cp.async (two stages, XOR-swizzled 16-byte chunks), shared by the CTA's four warps and
+// read with ldmatrix (transposed for V).  Same arithmetic as the register-direct kernel above;
+// it moves each key and value once per 64 queries instead of once per 16.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t* r, const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
+template <int HD>
+__global__ void __launch_bounds__(128) attn_prefill_tile_kernel(bf16* __restrict__ out, int ld_out, const bf16* __restrict__ q, int ld_q,
+                                                                const bf16* __restrict__ cache, const int* __restrict__ seg_q_start,
+                                                                const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
+                                                                int max_blocks, int H, int Hkv, int page, int window, float scale_log2) {
+  extern __shared__ __align__(128) uint8_t smem_bytes[];
+  constexpr int CH = HD / 8;                        // 16-byte chunks per row
+  constexpr int KS = HD / 16;                       // k steps of a dot product over the head
+  bf16* sQ = (bf16*)smem_bytes;                     // [64][HD]
+  bf16* sK = sQ + 64 * HD;                          // [2][64][HD]
+  bf16* sV = sK + 2 * 64 * HD;                      // [2][64][HD]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int seg = blockIdx.z, h = blockIdx.y;
+  const int q0 = seg_q_start[seg], qlen = seg_q_start[seg + 1] - q0;
+  const int tile0 = blockIdx.x * 64;
+  if (tile0 >= qlen) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
+  const int pos0 = seg_pos0[seg];
+  const int kvh = h / (H / Hkv);
+  const int* bt = block_table + (size_t)seg * max_blocks;
+  const int rows_here = qlen - tile0 < 64 ? qlen - tile0 : 64;
+  const int k_last = pos0 + tile0 + rows_here - 1;                 // last key any row of the tile sees
+  int k_first = 0;
+  if (window > 0) { const int f = pos0 + tile0 - window + 1; k_first = f > 0 ? f : 0; }
+  const int tile_begin = k_first >> 6, tile_end = k_last >> 6;     // inclusive range of 64-key tiles
+  const size_t page_elems = (size_t)2 * Hkv * page * HD;
+  const size_t v_off = (size_t)Hkv * page * HD;
+
+  // Q tile (rows beyond the segment are zero)
+  for (int c = tid; c < 64 * CH; c += 128) {
+    const int r = c / CH, ch = c - r * CH;
+    bf16* dst = sQ + r * HD + ((ch ^ (r & 7)) << 3);
+    if (r < rows_here) cp_async16(dst, q + (size_t)(q0 + tile0 + r) * ld_q + (size_t)h * HD + ch * 8);
+    else *(uint4*)dst = make_uint4(0, 0, 0, 0);
+  }
+  auto load_kv = [&](int tile, int stage) {
+    bf16* dk = sK + stage * 64 * HD;
+    bf16* dv = sV + stage * 64 * HD;
+    for (int c = tid; c < 64 * CH; c += 128) {
+      const int r = c / CH, ch = c - r * CH;
+      const int key = tile * 64 + r;
+      const int off = r * HD + ((ch ^ (r & 7)) << 3);
+      if (key <= k_last) {
+        const bf16* src = cache + (size_t)bt[key / page] * page_elems + ((size_t)kvh * page + (key % page)) * HD + ch * 8;
+        cp_async16(dk + off, src);
+        cp_async16(dv + off, src + v_off);
+      } else {                                       // keys nobody sees: zeros, so that 0 * x stays 0
+        *(uint4*)(dk + off) = make_uint4(0, 0, 0, 0);
+        *(uint4*)(dv + off) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  load_kv(tile_begin, 0);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // Q fragments of this warp's 16 rows stay in registers
+  uint32_t qa[KS][4];
+  {
+    const int r = warp * 16 + (lane & 15);
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int ch = ks * 2 + (lane >> 4);
+      ldsm_x4(qa[ks], sQ + r * HD + ((ch ^ (r & 7)) << 3));
+    }
+  }
+  const int row_lo = tile0 + warp * 16 + g, row_hi = row_lo + 8;
+  int hi[2] = {row_lo < qlen ? pos0 + row_lo : -1, row_hi < qlen ? pos0 + row_hi : -1};
+  int lo[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) lo[r] = (window > 0 && hi[r] - window + 1 > 0) ? hi[r] - window + 1 : 0;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const int warp_last = pos0 + tile0 + warp * 16 + 15;             // keys beyond this are masked for the whole warp
+
+  for (int tile = tile_begin; tile <= tile_end; ++tile) {
+    const int stage = (tile - tile_begin) & 1;
+    if (tile + 1 <= tile_end) load_kv(tile + 1, stage ^ 1);        // the other stage was released by the barrier below
+    cp_async_commit();
+    const bf16* tK = sK + stage * 64 * HD;
+    const bf16* tV = sV + stage * 64 * HD;
+    const int base = tile * 64;
+    if (base <= warp_last) {
+      float s[8][4];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+          uint32_t kb[4];
+          const int r = np * 16 + (lane & 7) + ((lane >> 4) << 3);
+          const int ch = ks * 2 + ((lane >> 3) & 1);
+          ldsm_x4(kb, tK + r * HD + ((ch ^ (r & 7)) << 3));
+          mma_bf16(s[2 * np], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[0], kb[1]);
+          mma_bf16(s[2 * np + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[2], kb[3]);
+        }
+      }
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          const int key = base + 8 * j + 2 * tg + (e & 1);
+          const float v = (key >= lo[r] && key <= hi[r]) ? s[j][e] * scale_log2 : -INFINITY;
+          s[j][e] = v;
+          mx[r] = fmaxf(mx[r], v);
+        }
+      float corr[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m[r], mx[r]);
+        corr[r] = (m_new == -INFINITY) ? 1.f : exp2f(m[r] - m_new);
+        m[r] = m_new;
+        l[r] *= corr[r];
+      }
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) {
+        o[i][0] *= corr[0]; o[i][1] *= corr[0];
+        o[i][2] *= corr[1]; o[i][3] *= corr[1];
+      }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        uint32_t pa[4];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float e[4];
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const float sv = s[2 * kk + half][x];
+            e[x] = (sv == -INFINITY) ? 0.f : exp2f(sv - m[x >> 1]);
+            l[x >> 1] += e[x];
+          }
+          pa[2 * half] = pack_bf16(e[0], e[1]);
+          pa[2 * half + 1] = pack_bf16(e[2], e[3]);
+        }
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; ++dp) {
+          uint32_t vb[4];
+          const int r = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+          const int ch = dp * 2 + (lane >> 4);
+          ldsm_x4_trans(vb, tV + r * HD + ((ch ^ (r & 7)) << 3));
+          mma_bf16(o[2 * dp], pa[0], pa[1], pa[2], pa[3], vb[0], vb[1]);
+          mma_bf16(o[2 * dp + 1], pa[0], pa[1], pa[2], pa[3], vb[2], vb[3]);
+        }
+      }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = r ? row_hi : row_lo;
+    if (row >= qlen) continue;
+    const float inv = 1.f / l[r];
+    bf16* orow = out + (size_t)(q0 + row) * ld_out + (size_t)h * HD;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i)
+      *(uint32_t*)(orow + i * 8 + 2 * tg) = pack_bf16(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+  }
+}
+
+template <int HD>
+int launch_prefill_tile(bf16* out, int ld_out, const bf16* q, int ld_q, const bf16* cache, const int* seg_q_start, const int* seg_pos0,
+                        const int* bt, int max_blocks, int S, int max_q_len, int H, int Hkv, int page, int window, float scale_log2,
+                        cudaStream_t st) {
+  constexpr int smem = (64 + 4 * 64) * HD * 2;
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tile_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((max_q_len + 63) / 64, H, S);
+  return qv_launch(attn_prefill_tile_kernel<HD>, grid, dim3(128), (size_t)smem, st, out, ld_out, q, ld_q, cache, seg_q_start, seg_pos0,
+                   bt, max_blocks, H, Hkv, page, window, scale_log2);
+}
+
 // ---------------------------------------------------------------- decode
 // partial results of a slice: [token][head][slice][HD + 2] floats (out unnormalised, then m, l)
 template <int HD>
@@ -404,11 +614,20 @@ extern "C" long long qv_attn_decode_workspace_floats(int T, int H, int hd, int s
 // pages that are no multiple of 16, and operands that are not 16-byte aligned row by row.
 extern "C" int qv_attn_prefill_bf16(void* out, int ld_out, const void* q, int ld_q, const void* cache, const int* seg_q_start,
                                     const int* seg_pos0, const int* block_table, int max_blocks, int S, int max_q_len, int H,
-                                    int Hkv, int hd, int page, int window, float scale, void* stream) {
+                                    int Hkv, int hd, int page, int window, float scale, int variant, void* stream) {
+  // variant 0: the shared-memory kernel where it exists (head sizes 64 and 128), else the
+  // register-direct one; variant 1: always the register-direct kernel.
   if (S <= 0 || max_q_len <= 0) return 0;
   if (Hkv <= 0 || H % Hkv || page % 16 || (ld_q & 7) || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15)) return QV_ERR_UNSUPPORTED;
   if (S > 65535 || H > 65535) return QV_ERR_TOO_LARGE;
   const float sl2 = scale * 1.4426950408889634f;
+  if ((hd == 64 || hd == 128) && (ld_out & 1) == 0 && variant == 0) {
+    if (hd == 64)
+      return launch_prefill_tile<64>((bf16*)out, ld_out, (const bf16*)q, ld_q, (const bf16*)cache, seg_q_start, seg_pos0,
+                                     block_table, max_blocks, S, max_q_len, H, Hkv, page, window, sl2, (cudaStream_t)stream);
+    return launch_prefill_tile<128>((bf16*)out, ld_out, (const bf16*)q, ld_q, (const bf16*)cache, seg_q_start, seg_pos0,
+                                    block_table, max_blocks, S, max_q_len, H, Hkv, page, window, sl2, (cudaStream_t)stream);
+  }
 #define CASE(D)                                                                                                          \
   if (hd == D)                                                                                                           \
     return launch_prefill<D>((bf16*)out, ld_out, (const bf16*)q, ld_q, (const bf16*)cache, seg_q_start, seg_pos0, block_table, \

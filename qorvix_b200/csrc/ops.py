@@ -249,7 +249,7 @@ def gemm_swiglu(out, x, w_interleaved) -> None:
 
 
 def attention_prefill_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, Hkv, hd, page,
-                           window, scale) -> bool:
+                           window, scale, variant: int = 0) -> bool:
     """Flash attention of prompt portions (any mix of segments) over the paged bfloat16 cache.
     False when the kernel refuses the sizes."""
     _need_cuda(out, q, cache_layer, seg_q_start, seg_pos0, block_table)
@@ -260,7 +260,7 @@ def attention_prefill_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_tab
     rc = load_library("attention_bf16").qv_attn_prefill_bf16(
         _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(cache_layer), _ptr(seg_q_start), _ptr(seg_pos0),
         _ptr(block_table), c_int(block_table.shape[-1]), c_int(S), c_int(max_q_len), c_int(H), c_int(Hkv), c_int(hd),
-        c_int(page), c_int(window), c_float(scale), _stream())
+        c_int(page), c_int(window), c_float(scale), c_int(variant), _stream())
     if rc == -2:
         return False
     _check(rc, "attention_prefill_bf16")

@@ -282,12 +282,13 @@ ATT_SHAPES = [(4, 4, 16, 16, 0), (6, 2, 32, 16, 0), (5, 1, 48, 32, 0), (8, 2, 64
               (12, 4, 96, 64, 0), (14, 2, 112, 16, 0), (32, 8, 128, 16, 0), (16, 1, 128, 16, 0), (4, 2, 64, 16, 37)]
 
 
+@pytest.mark.parametrize("variant", [0, 1])        # 0: shared-memory tiles where they exist; 1: register-direct
 @pytest.mark.parametrize("H,Hkv,hd,page,window", ATT_SHAPES)
-def test_attention_prefill_bf16(H, Hkv, hd, page, window):
-    d = _segments([(70, 70), (1, 33), (130, 200), (2, 2), (16, 48), (1, 1)], H, Hkv, hd, page, seed=61, window=window)
+def test_attention_prefill_bf16(H, Hkv, hd, page, window, variant):
+    d = _segments([(70, 70), (1, 33), (130, 200), (2, 2), (16, 48), (1, 1), (64, 64), (65, 129)], H, Hkv, hd, page, seed=61, window=window)
     out = torch.full_like(d["q"], float("nan"))
     assert ops.attention_prefill_bf16(out, d["q"], d["cache"], d["qstart"], d["pos0"], d["bt"], d["S"], d["max_q"], H, Hkv, hd,
-                                      page, window, 1.0 / math.sqrt(hd))
+                                      page, window, 1.0 / math.sqrt(hd), variant)
     assert torch.allclose(out.double().cpu(), d["ref"], rtol=2e-2, atol=2e-2)
 
 
