@@ -168,11 +168,14 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int ld, T* __restrict_
                                      const int* __restrict__ tok_pos, const int* __restrict__ tok_seg,
                                      const int* __restrict__ block_table, int max_blocks, int H,
                                      int Hkv, int hd, int rot, int page) {
-  // grid (token, head slot): slots 0..H-1 are q heads, H..H+Hkv-1 k heads, H+Hkv..H+2Hkv-1 v heads
+  // grid (token, groups of 8 head slots), one warp per slot: slots 0..H-1 are q heads,
+  // H..H+Hkv-1 k heads, H+Hkv..H+2Hkv-1 v heads
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
-  const int head = blockIdx.y;
+  const int head = blockIdx.y * 8 + (threadIdx.x >> 5);
+  if (head >= H + 2 * Hkv) return;
+  const int lane = threadIdx.x & 31;
   const int pos = tok_pos[t];
   T* row = qkv + (size_t)t * ld;
   const int half = rot >> 1;
@@ -189,19 +192,19 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int ld, T* __restrict_
     T* v = row + (size_t)head * hd;
     const bool to_cache = head >= H && cache;
     T* dst = to_cache ? kdst + (size_t)(head - H) * page * hd : v;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    for (int i = lane; i < half; i += 32) {
       const float a = to_f(v[i]), b = to_f(v[i + half]);
       const float2 c = cs[i];
       dst[i] = from_f<T>(a * c.x - b * c.y);
       dst[i + half] = from_f<T>(a * c.y + b * c.x);
     }
     if (to_cache)      // dims beyond the rotated ones pass through
-      for (int i = rot + threadIdx.x; i < hd; i += blockDim.x) dst[i] = v[i];
+      for (int i = rot + lane; i < hd; i += 32) dst[i] = v[i];
   } else if (cache) {
     const int vh = head - H - Hkv;
     const T* v = row + (size_t)head * hd;
     T* dst = vdst + (size_t)vh * page * hd;
-    for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = v[i];
+    for (int i = lane; i < hd; i += 32) dst[i] = v[i];
   }
 }
 
@@ -211,9 +214,9 @@ extern "C" int qv_rope_kv_write(void* qkv, int ld, void* cache, const float* cos
                                 int dt, void* stream) {
   if (T <= 0) return 0;
   if (rot < 0 || rot > hd || (rot & 1)) return QV_ERR_UNSUPPORTED;
-  if (H + 2 * Hkv > 65535) return QV_ERR_TOO_LARGE;
+  if ((H + 2 * Hkv + 7) / 8 > 65535) return QV_ERR_TOO_LARGE;
   QV_DISPATCH_DT(dt, TT,
-                 return qv_launch(rope_kv_write_kernel<TT>, dim3(T, H + 2 * Hkv), dim3(64), 0, (cudaStream_t)stream,
+                 return qv_launch(rope_kv_write_kernel<TT>, dim3(T, (H + 2 * Hkv + 7) / 8), dim3(256), 0, (cudaStream_t)stream,
                      (TT*)qkv, ld, (TT*)cache, (const float2*)cos_sin, table_rows, tok_pos, tok_seg,
                      block_table, max_blocks, H, Hkv, hd, rot, page));
   return QV_ERR_UNSUPPORTED;

@@ -345,13 +345,23 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
           if (*flag_slot) {
             __threadfence();
             if (frow) {
-              for (int j = 0; j < BN; ++j) {
-                const int t = narrow0 + j;
-                if (t >= ntok) break;
-                float acc = 0.f;
-                for (int s = 0; s < args.splits; ++s)
-                  acc += __ldcg(args.workspace + ((size_t)s * ntok + t) * args.rows_wide + wide_row);
-                store_out<TC>(C + (size_t)t * args.ldc + wide_row, acc);
+              // 16 tokens at a time: the loads of one split are independent and in flight together;
+              // splits are added in order 0, 1, 2, ...
+              for (int j0 = 0; j0 < BN && narrow0 + j0 < ntok; j0 += 16) {
+                float acc[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+                for (int s = 0; s < args.splits; ++s) {
+                  const float* src = args.workspace + ((size_t)s * ntok + narrow0 + j0) * args.rows_wide + wide_row;
+                  float v[16];
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) v[j] = (narrow0 + j0 + j < ntok) ? __ldcg(src + (size_t)j * args.rows_wide) : 0.f;
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) acc[j] += v[j];
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  if (narrow0 + j0 + j < ntok) store_out<TC>(C + (size_t)(narrow0 + j0 + j) * args.ldc + wide_row, acc[j]);
               }
             }
           }

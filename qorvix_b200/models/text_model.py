@@ -26,13 +26,24 @@ class TextModel:
         self.lm_head = Linear(source.get(spec.lm_head)) if spec.lm_head is not None else Linear(self.embedding)
         self.order: List[int] = list(spec.order)
 
-    # what each layer wants of the cache manager: (cache_spec | None, layer it reads from | None)
     def cache_needs(self):
+        """What each RUN of the execution order wants of the cache manager: (cache spec or None, index
+        of the run whose cache it reads or None).  A layer that the order names twice keeps a cache per
+        run: in a later step its first run must find the keys its first run wrote, not its second's.
+        A mixer that reads another layer's cache reads that layer's latest run before its own."""
         needs = []
-        for b in self.blocks:
-            m = getattr(b, "mixer", None)
-            needs.append((m.cache_spec() if m is not None else None,
-                          m.reads_cache_of() if m is not None else None))
+        last_run_of = {}
+        for run, li in enumerate(self.order):
+            m = getattr(self.blocks[li], "mixer", None)
+            spec = m.cache_spec() if m is not None else None
+            src = m.reads_cache_of() if m is not None else None
+            src_run = None
+            if src is not None:
+                if src not in last_run_of:
+                    raise ValueError(f"layer {li} reads the cache of layer {src}, which has not run before it")
+                src_run = last_run_of[src]
+            needs.append((spec, src_run))
+            last_run_of[li] = run
         return needs
 
     def forward(self, ctx, cache) -> Optional[torch.Tensor]:
@@ -41,8 +52,8 @@ class TextModel:
         residual = torch.empty((T, self.spec.hidden_size), device=self.rt.device, dtype=torch.float32)
         ops.embed(residual, self.embedding, ctx.token_ids)
         pending = None
-        for li in self.order:
-            residual, pending = self.blocks[li].forward(residual, pending, ctx, cache.layer_view(li))
+        for run, li in enumerate(self.order):
+            residual, pending = self.blocks[li].forward(residual, pending, ctx, cache.layer_view(run))
         if ctx.num_wanted == 0:
             return None
         h = self.final_norm.add_norm(residual, pending, rows=ctx.want_rows)
