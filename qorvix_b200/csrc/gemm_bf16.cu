@@ -10,9 +10,9 @@
 //   * few tokens (decode, M <= 64): operands are swapped.  128 weight rows are the 128-row MMA
 //     operand and the tokens (padded to 16/32/64) the narrow one, so every weight byte is
 //     streamed from HBM exactly once through a deep TMA ring.  Matrices with few row tiles are
-//     also split along K so that enough CTAs pull from HBM at once; the partial sums go to a
-//     float32 workspace and the last CTA of a tile to arrive adds them in a fixed order
-//     (split 0, 1, 2, ...), so the result does not depend on which CTA came last.
+//     also split along K so that enough CTAs pull from HBM at once; the CTAs of one tile form a
+//     thread-block cluster, leave their partial sums in shared memory, and the first CTA adds
+//     them through distributed shared memory in a fixed order (split 0, 1, 2, ...).
 //
 // Every wait on an mbarrier is bounded; when one gives up it records a code in *err and the
 // CTA winds down (tensor memory is freed) instead of hanging the device.
@@ -112,8 +112,6 @@ template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { 
 
 struct GemmArgs {
   void* C;             // output [tokens, features], row stride ldc
-  float* workspace;    // split-K partial sums [splits][tokens][features] (swap mode only)
-  int* counters;       // one per (row tile, col tile), zero between launches
   int* err;
   int rows_wide;       // rows of the operand that feeds the 128-row side
   int rows_narrow;     // rows of the other operand
@@ -144,8 +142,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
   uint64_t* empty = full + STAGES;
   uint64_t* accum = empty + STAGES;
   uint32_t* tmem_slot = (uint32_t*)(accum + 1);
-  int* flag_slot = (int*)(tmem_slot + 1);
-  int* ok_slots = flag_slot + 1;          // one per epilogue warp
+  int* ok_slots = (int*)(tmem_slot + 1);  // one per epilogue warp
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wide0 = blockIdx.x * BM;
@@ -220,7 +217,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     }
   } else {
     // epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31
-    pdl_wait();                 // C, the workspace and the counters may still be in use by the kernel ahead
+    pdl_wait();                 // C may still be in use by the kernel ahead
     const int q = warp & 3;
     // one lane per warp polls; the four warps then agree, so that either all of them take the
     // barriers below or none does
@@ -318,52 +315,17 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
             }
           }
         } else {
-          float* ws = args.workspace + (size_t)split * ntok * args.rows_wide;
+          // split-K: this CTA's partial sums go to its own shared memory (the stage ring is free
+          // now), column-major so that a warp's 32 rows are 32 consecutive floats; the cluster's
+          // first CTA adds them up below
+          float* red = (float*)tiles;
 #pragma unroll 1
           for (int c0 = 0; c0 < BN; c0 += 16) {
             uint32_t r[16];
             tmem_ld16(taddr + c0, r);
             tmem_wait_ld();
-            if (frow) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int t = narrow0 + c0 + j;
-                if (t < ntok) ws[(size_t)t * args.rows_wide + wide_row] = __uint_as_float(r[j]);
-              }
-            }
-          }
-          // the last CTA of this tile to arrive adds the partial sums in split order
-          __threadfence();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (threadIdx.x == 64) {
-            const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-            const int prev = atomicAdd(&args.counters[tile], 1);
-            *flag_slot = (prev == args.splits - 1) ? 1 : 0;
-            if (prev == args.splits - 1) args.counters[tile] = 0;     // ready for the next launch
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (*flag_slot) {
-            __threadfence();
-            if (frow) {
-              // 16 tokens at a time: the loads of one split are independent and in flight together;
-              // splits are added in order 0, 1, 2, ...
-              for (int j0 = 0; j0 < BN && narrow0 + j0 < ntok; j0 += 16) {
-                float acc[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-                for (int s = 0; s < args.splits; ++s) {
-                  const float* src = args.workspace + ((size_t)s * ntok + narrow0 + j0) * args.rows_wide + wide_row;
-                  float v[16];
-#pragma unroll
-                  for (int j = 0; j < 16; ++j) v[j] = (narrow0 + j0 + j < ntok) ? __ldcg(src + (size_t)j * args.rows_wide) : 0.f;
-#pragma unroll
-                  for (int j = 0; j < 16; ++j) acc[j] += v[j];
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                  if (narrow0 + j0 + j < ntok) store_out<TC>(C + (size_t)(narrow0 + j0 + j) * args.ldc + wide_row, acc[j]);
-              }
-            }
+            for (int j = 0; j < 16; ++j) red[(c0 + j) * BM + q * 32 + lane] = __uint_as_float(r[j]);
           }
         }
       }
@@ -371,6 +333,45 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     tc_fence_before();
   }
   __syncthreads();
+  if (SWAP && args.splits > 1) {
+    // The CTAs of one tile (one per split) form a cluster.  After the cluster barrier every
+    // partial tile is visible through distributed shared memory; the first CTA adds them in
+    // split order 0, 1, 2, ... and stores the result, and a second barrier keeps the others'
+    // shared memory alive until it has.
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+    if (split == 0 && warp >= 2) {
+      const int row = (warp & 3) * 32 + lane;
+      const int wide_row = wide0 + row;
+      const int ntok = args.rows_narrow;
+      const float* red = (const float*)tiles;
+      const uint32_t red_addr = smem_u32(red);
+      TC* C = (TC*)args.C;
+      if (wide_row < args.rows_wide) {
+        for (int j0 = 0; j0 < BN && narrow0 + j0 < ntok; j0 += 16) {
+          float acc[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[j] = red[(j0 + j) * BM + row];
+          for (int sidx = 1; sidx < args.splits; ++sidx) {
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              uint32_t remote;
+              asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr + (uint32_t)(((j0 + j) * BM + row) * 4)), "r"(sidx));
+              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[j]) : "r"(remote) : "memory");
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] += v[j];
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (narrow0 + j0 + j < ntok) store_out<TC>(C + (size_t)(narrow0 + j0 + j) * args.ldc + wide_row, acc[j]);
+        }
+      }
+    }
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+  }
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -414,20 +415,17 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mn, const GemmArgs& args, d
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return qv_launch(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, grid, dim3(192), (size_t)smem, st, mw, mn, args);
+  // split-K CTAs of a tile (grid.z of them) are one cluster
+  return qv_launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, grid, dim3(192), (size_t)smem, st, (int)grid.z, mw, mn, args);
 }
 
 }  // namespace
-
-// Smallest workspace (bytes) and number of counters that any call with M <= 64 may need.
-extern "C" long long qv_gemm_bf16_workspace_bytes(int max_features) { return (long long)8 * 64 * (long long)max_features * 4; }
 
 // C (bf16 or f32) [M,N] = A (bf16) [M,K] * W (bf16) [N,K]^T.  Returns QV_ERR_UNSUPPORTED for shapes
 // the tensor-core path does not take (the caller then uses the CUDA-core kernel):
 // K not a multiple of 8 elements, or operands whose rows do not start on 16-byte boundaries.
 extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
-                               int c_dt, float* workspace, long long workspace_bytes, int* counters, int n_counters,
-                               int* err, int force_splits, int epilogue, void* stream) {
+                               int c_dt, int* err, int force_splits, int epilogue, void* stream) {
   // epilogue 0: C[M,N] = A W^T.  epilogue 1: W's rows are 16 gate rows / 16 up rows interleaved and
   // C[M,N/2] = silu(gate) * up (bfloat16 out, N a multiple of 32).
   if (M <= 0 || N <= 0) return 0;
@@ -437,7 +435,7 @@ extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int
   if (c_dt != QV_DT_BF16 && c_dt != QV_DT_F32) return QV_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   GemmArgs args;
-  args.C = C; args.workspace = workspace; args.counters = counters; args.err = err;
+  args.C = C; args.err = err;
   args.K = K; args.ldc = ldc;
   const int total_kb = (K + BK - 1) / BK;
   CUtensorMap mw, mn;
@@ -449,13 +447,10 @@ extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int
     if (epilogue == 1) splits = 1;                  // the fused activation needs whole sums
     else if (force_splits > 0) splits = force_splits;
     else if (tiles < 96) {                          // too few CTAs to pull full bandwidth: split along K
-      splits = 148 / tiles;                         // as many CTAs as fit in one wave
-      if (splits < 1) splits = 1;
-      if (splits > 8) splits = 8;
+      // a power of two (clusters of 2, 4 or 8 CTAs place well), at most ~200 CTAs in all
+      while (splits < 8 && tiles * splits * 2 <= 200 && total_kb / (splits * 2) >= 4) splits *= 2;
     }
     if (splits > total_kb) splits = total_kb;
-    if (splits > 1 && (workspace == nullptr || counters == nullptr || tiles > n_counters ||
-                       (long long)splits * M * N * 4 > workspace_bytes)) splits = 1;
     int per = (total_kb + splits - 1) / splits;
     splits = (total_kb + per - 1) / per;            // no empty split
     args.rows_wide = N; args.rows_narrow = M; args.kblocks_per_split = per; args.splits = splits;

@@ -166,14 +166,11 @@ _tc_state = {}
 
 
 def _tc_buffers(device):
-    """Per device: split-K workspace, tile counters and the error word of the tensor-core kernels.
-    Calls on one stream run one after another, so they can share these."""
+    """Per device: the error word of the tensor-core kernels."""
     key = device.index if device.index is not None else torch.cuda.current_device()
     st = _tc_state.get(key)
     if st is None:
-        st = dict(workspace=torch.empty(32 << 20, dtype=torch.uint8, device=device),
-                  counters=torch.zeros(4096, dtype=torch.int32, device=device),
-                  err=torch.zeros(1, dtype=torch.int32, device=device))
+        st = dict(err=torch.zeros(1, dtype=torch.int32, device=device))
         _tc_state[key] = st
     return st
 
@@ -191,8 +188,7 @@ def gemm_bf16_tc(c, a, w, force_splits: int = 0, swiglu: bool = False) -> bool:
     st = _tc_buffers(a.device)
     rc = load_library("gemm_bf16").qv_gemm_bf16_tc(
         _ptr(c), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(w.stride(0)),
-        c_int(c.stride(0)), c_int(dt_code(c.dtype)), _ptr(st["workspace"]), c_longlong(st["workspace"].numel()),
-        _ptr(st["counters"]), c_int(st["counters"].numel()), _ptr(st["err"]), c_int(force_splits),
+        c_int(c.stride(0)), c_int(dt_code(c.dtype)), _ptr(st["err"]), c_int(force_splits),
         c_int(1 if swiglu else 0), _stream())
     if rc == -2:
         return False

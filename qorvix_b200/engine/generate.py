@@ -12,6 +12,7 @@ from typing import List, Optional, Sequence, Union
 
 import torch
 
+from ..csrc import ops
 from ..sampling import Sampler, SamplingParams
 from .runner import ModelRunner
 from .scheduler import RequestResult, Scheduler, SchedulerConfig
@@ -48,6 +49,7 @@ class LLM:
         results = {r.id: r for r in sched.run_to_completion()}
         torch.cuda.synchronize(self.runner.device)
         dt = time.perf_counter() - t0
+        ops.check_kernel_errors()
         self.last_stats = dict(sched.stats, seconds=dt,
                                generated=sum(len(r.tokens) for r in results.values()))
         return [results[i] for i in ids]

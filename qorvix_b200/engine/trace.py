@@ -20,6 +20,7 @@ from pathlib import Path
 
 import numpy as np
 
+from ..csrc import ops
 from .batch import StepEntry
 from .runner import ModelRunner
 
@@ -60,6 +61,7 @@ def run(args, stdin=None, stdout=None) -> int:
             tmp = out_dir / f".{step}.f32.tmp"
             arr.tofile(tmp)
             tmp.replace(out_dir / f"{step}.f32")
+            ops.check_kernel_errors()              # a kernel that gave up on a barrier must not pass silently
         print(f"done {step}", file=stdout, flush=True)
     return 0
 
