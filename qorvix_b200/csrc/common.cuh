@@ -75,9 +75,9 @@ static inline bool qv_pdl_enabled() {
   return v != 0;
 }
 
-// As qv_launch, with the grid's z dimension grouped into thread-block clusters of cluster_z CTAs.
+// As qv_launch, with the grid grouped into thread-block clusters of the given shape.
 template <typename... KArgs, typename... Args>
-static inline int qv_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, int cluster_z,
+static inline int qv_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, dim3 cluster,
                                     Args&&... args) {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -87,11 +87,11 @@ static inline int qv_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 bl
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
   int n = 0;
-  if (cluster_z > 1) {
+  if (cluster.x * cluster.y * cluster.z > 1) {
     attr[n].id = cudaLaunchAttributeClusterDimension;
-    attr[n].val.clusterDim.x = 1;
-    attr[n].val.clusterDim.y = 1;
-    attr[n].val.clusterDim.z = (unsigned)cluster_z;
+    attr[n].val.clusterDim.x = cluster.x;
+    attr[n].val.clusterDim.y = cluster.y;
+    attr[n].val.clusterDim.z = cluster.z;
     ++n;
   }
   if (qv_pdl_enabled()) {

@@ -416,7 +416,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mn, const GemmArgs& args, d
     configured = true;
   }
   // split-K CTAs of a tile (grid.z of them) are one cluster
-  return qv_launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, grid, dim3(192), (size_t)smem, st, (int)grid.z, mw, mn, args);
+  return qv_launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, grid, dim3(192), (size_t)smem, st, dim3(1, 1, grid.z), mw, mn, args);
 }
 
 }  // namespace
