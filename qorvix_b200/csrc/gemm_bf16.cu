@@ -106,6 +106,10 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *(uint32_t*)&h;
+}
 template <typename TC> __device__ __forceinline__ void store_out(TC* p, float v);
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
@@ -378,6 +382,182 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
   }
 }
 
+// ---------------------------------------------------------------- many tokens: persistent kernel
+// One CTA per SM walks over 128 x BN output tiles (tile = blockIdx.x, + gridDim.x, ...; token tiles
+// fastest, so that CTAs running at the same time share a weight tile in L2).  The accumulator is
+// double-buffered in tensor memory (2 x BN columns): while the four epilogue warps drain tile i,
+// the MMA warp already accumulates tile i+1, and the TMA warp runs ahead of both through the
+// shared-memory ring.
+template <int BN, int STAGES, typename TC, bool SWIGLU>
+__global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                                 const __grid_constant__ CUtensorMap map_w,
+                                                                 const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = 2 * BN;                  // 256 or 512: a power of two
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;               // [2]
+  uint64_t* acc_empty = acc_full + 2;                // [2]
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int M = args.rows_wide, N = args.rows_narrow;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int total_tiles = tiles_m * tiles_n;
+  const int num_kb = (args.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // the first stages' weight tiles do not depend on the kernel ahead
+      int it = 0;
+      bool first = true;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        int kb = 0;
+        if (first) {
+          const int pre = num_kb < STAGES ? num_kb : STAGES;
+          for (int k = 0; k < pre; ++k) {
+            mbar_expect_tx(&full[k], STAGE_BYTES);
+            tma_load_2d(tiles + k * STAGE_BYTES + A_BYTES, &map_w, &full[k], k * BK, n0);
+          }
+          pdl_wait();
+          for (int k = 0; k < pre; ++k) tma_load_2d(tiles + k * STAGE_BYTES, &map_x, &full[k], k * BK, m0);
+          kb = pre;
+          it = pre;
+          first = false;
+        }
+        bool ok = true;
+        for (; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, args.err, 1)) { ok = false; break; }
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          uint8_t* a = tiles + s * STAGE_BYTES;
+          tma_load_2d(a, &map_x, &full[s], kb * BK, m0);
+          tma_load_2d(a + A_BYTES, &map_w, &full[s], kb * BK, n0);
+        }
+        if (!ok) break;
+      }
+      if (first) pdl_wait();
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BM, BN);
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        const int b = local & 1;
+        // the epilogue must have drained this accumulator (two tiles ago)
+        ok = mbar_wait(&acc_empty[b], ((local >> 1) & 1) ^ 1, args.err, 4);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&full[s], ph, args.err, 2);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
+          const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk)
+            umma_f16(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(&empty[s]);
+        }
+        umma_commit(&acc_full[b]);
+      }
+    }
+  } else {
+    pdl_wait();                                      // C may still be in use by the kernel ahead
+    const int q = warp & 3;
+    TC* C = (TC*)args.C;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+      const int b = local & 1;
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      // every thread polls: the arrivals below need all 128 of them, timed out or not
+      const bool ok = mbar_wait(&acc_full[b], (local >> 1) & 1, args.err, 3);
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN);
+      if (ok) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c0, r);
+          tmem_wait_ld();
+          if (row >= M || n0 + c0 >= N) continue;
+          if (SWIGLU) {
+            TC* dst = C + (size_t)row * args.ldc + ((n0 + c0) >> 1);
+            float a[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) a[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r[16 + j]));
+            if (sizeof(TC) == 2 && (((uintptr_t)dst) & 15) == 0) {
+              uint32_t w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) w[j] = pack2_bf16(a[2 * j], a[2 * j + 1]);
+              ((uint4*)dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              ((uint4*)dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) store_out<TC>(dst + j, a[j]);
+            }
+          } else {
+            TC* dst = C + (size_t)row * args.ldc + n0 + c0;
+            const int ncols = N - (n0 + c0);
+            if (sizeof(TC) == 2 && ncols >= 32 && (((uintptr_t)dst) & 15) == 0) {
+              uint4* d4 = (uint4*)dst;
+#pragma unroll
+              for (int v = 0; v < 4; ++v)
+                d4[v] = make_uint4(pack2_bf16(__uint_as_float(r[v * 8]), __uint_as_float(r[v * 8 + 1])),
+                                   pack2_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3])),
+                                   pack2_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5])),
+                                   pack2_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7])));
+            } else if (sizeof(TC) == 4 && ncols >= 32 && (((uintptr_t)dst) & 15) == 0) {
+              float4* d4 = (float4*)dst;
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                d4[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+            } else {
+              for (int j = 0; j < 32 && j < ncols; ++j) store_out<TC>(dst + j, __uint_as_float(r[j]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[b])) : "memory");
+      if (!ok) break;
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -419,7 +599,30 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mn, const GemmArgs& args, d
   return qv_launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, grid, dim3(192), (size_t)smem, st, dim3(1, 1, grid.z), mw, mn, args);
 }
 
+template <int BN, int STAGES, typename TC, bool SWIGLU>
+int launch_persistent(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& args, int total_tiles, cudaStream_t st) {
+  constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  static bool configured = false;
+  static int sms = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, TC, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+    configured = true;
+  }
+  const int ctas = total_tiles < sms ? total_tiles : sms;
+  return qv_launch(gemm_tc_persistent_kernel<BN, STAGES, TC, SWIGLU>, dim3(ctas), dim3(192), (size_t)smem, st, mx, mw, args);
+}
+
 }  // namespace
+
+// Which kernel serves more than 64 tokens: 0 (default) the persistent one with 128 x 256 tiles,
+// 1 the one-tile-per-CTA kernel with 128 x 128 tiles (kept for comparison and tests).
+static int g_prefill_variant = 0;
+extern "C" void qv_gemm_bf16_set_prefill_variant(int v) { g_prefill_variant = v; }
 
 // C (bf16 or f32) [M,N] = A (bf16) [M,K] * W (bf16) [N,K]^T.  Returns QV_ERR_UNSUPPORTED for shapes
 // the tensor-core path does not take (the caller then uses the CUDA-core kernel):
@@ -471,6 +674,14 @@ extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int
   }
   // many tokens: tokens on the 128-row side, 128 weight rows per tile
   args.rows_wide = M; args.rows_narrow = N; args.kblocks_per_split = total_kb; args.splits = 1;
+  if (g_prefill_variant == 0) {
+    // persistent kernel, 128 x 256 tiles, accumulator double-buffered in tensor memory
+    if (!make_map(&mw, A, M, K, lda, BM) || !make_map(&mn, W, N, K, ldw, 256)) return QV_ERR_UNSUPPORTED;
+    const int total_tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
+    if (epilogue == 1) return launch_persistent<256, 4, bf16, true>(mw, mn, args, total_tiles, st);
+    if (c_dt == QV_DT_BF16) return launch_persistent<256, 4, bf16, false>(mw, mn, args, total_tiles, st);
+    return launch_persistent<256, 4, float, false>(mw, mn, args, total_tiles, st);
+  }
   if (!make_map(&mw, A, M, K, lda, BM) || !make_map(&mn, W, N, K, ldw, 128)) return QV_ERR_UNSUPPORTED;
   dim3 grid((M + BM - 1) / BM, (N + 127) / 128, 1);
   if (grid.y > 65535) return QV_ERR_TOO_LARGE;

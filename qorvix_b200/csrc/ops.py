@@ -196,6 +196,12 @@ def gemm_bf16_tc(c, a, w, force_splits: int = 0, swiglu: bool = False) -> bool:
     return True
 
 
+def gemm_bf16_set_prefill_variant(variant: int) -> None:
+    """0 (default): more than 64 tokens run on the persistent kernel (128 x 256 tiles, double-buffered
+    accumulator); 1: on the one-tile-per-CTA kernel (128 x 128 tiles)."""
+    load_library("gemm_bf16").qv_gemm_bf16_set_prefill_variant(c_int(variant))
+
+
 def check_kernel_errors() -> None:
     """Raises if a kernel gave up on a bounded wait since the last check (synchronises)."""
     for key, st in _tc_state.items():

@@ -27,11 +27,16 @@ def check(M, N, K, out_dtype, force_splits=0, lda=None):
     assert err <= tol * max(1.0, ref.abs().max().item()), f"M={M} N={N} K={K}: max err {err}"
 
 
+@pytest.mark.parametrize("variant", [0, 1])        # 0: persistent 128x256 kernel; 1: one 128x128 tile per CTA
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 256), (256, 384, 4096), (200, 1000, 328),
-                                   (2048, 6144, 4096), (65, 136, 72), (300, 331, 1000)])
-def test_many_tokens(M, N, K, out_dtype):
-    check(M, N, K, out_dtype)
+                                   (2048, 6144, 4096), (65, 136, 72), (300, 331, 1000), (4000, 2000, 136)])
+def test_many_tokens(M, N, K, out_dtype, variant):
+    ops.gemm_bf16_set_prefill_variant(variant)
+    try:
+        check(M, N, K, out_dtype)
+    finally:
+        ops.gemm_bf16_set_prefill_variant(0)
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
