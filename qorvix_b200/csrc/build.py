@@ -35,6 +35,7 @@ LIBRARIES = {
     "sampling": "sampling.cu",
     "gemm_bf16": "gemm_bf16.cu",
     "attention_bf16": "attention_bf16.cu",
+    "attention_tc": "attention_tc.cu",
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -269,6 +269,27 @@ def attention_prefill_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_tab
     return True
 
 
+def attention_prefill_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, Hkv, hd, page,
+                         window, scale) -> bool:
+    """Flash attention of prompt portions with tcgen05 tensor-core products (head sizes 64 and 128).
+    False when the kernel refuses the sizes."""
+    _need_cuda(out, q, cache_layer, seg_q_start, seg_pos0, block_table)
+    assert q.dtype == out.dtype == cache_layer.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and cache_layer.is_contiguous()
+    assert tuple(cache_layer.shape[1:]) == (2, Hkv, page, hd)
+    _i32(seg_q_start, "seg_q_start"); _i32(seg_pos0, "seg_pos0"); _i32(block_table, "block_table")
+    st = _tc_buffers(q.device)
+    rc = load_library("attention_tc").qv_attn_prefill_tc(
+        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), c_int(q.shape[0]), _ptr(cache_layer),
+        c_longlong(cache_layer.shape[0]), _ptr(seg_q_start), _ptr(seg_pos0), _ptr(block_table),
+        c_int(block_table.shape[-1]), c_int(S), c_int(max_q_len), c_int(H), c_int(Hkv), c_int(hd), c_int(page),
+        c_int(window), c_float(scale), _ptr(st["err"]), _stream())
+    if rc == -2:
+        return False
+    _check(rc, "attention_prefill_tc")
+    return True
+
+
 def decode_splits(T: int, Hkv: int, max_ctx: int) -> int:
     """How many slices of the keys each (token, kv head) is cut into, so that about three CTAs per
     SM are busy; a function of the step's shape only (a captured step keeps it)."""
@@ -310,6 +331,9 @@ def attention(out, q, cache_layer, ctx, block_table, H, Hkv, hd, page, window, s
             if attention_decode_bf16(out, q, cache_layer, ctx.tok_pos, ctx.tok_seg, block_table, H, Hkv, hd, page,
                                      window, scale, splits):
                 return
+        elif ctx.max_q_len >= 32 and attention_prefill_tc(out, q, cache_layer, ctx.seg_q_start, ctx.seg_pos0, block_table,
+                                                          ctx.num_segments, ctx.max_q_len, H, Hkv, hd, page, window, scale):
+            return                                    # long portions at head sizes 64/128: tcgen05
         elif attention_prefill_bf16(out, q, cache_layer, ctx.seg_q_start, ctx.seg_pos0, block_table, ctx.num_segments,
                                     ctx.max_q_len, H, Hkv, hd, page, window, scale):
             return

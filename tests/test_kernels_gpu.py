@@ -327,3 +327,30 @@ def test_attention_bf16_refuses_what_it_cannot_do():
     out = torch.zeros_like(q)
     assert not ops.attention_decode_bf16(out, q, cache, d["pos"], d["seg"], d["bt"], 4, 4, 144, 16, 0, 0.1, 1)    # head size 144
     assert not ops.attention_prefill_bf16(out, q, cache, d["qstart"], d["pos0"], d["bt"], 1, 1, 4, 4, 144, 16, 0, 0.1)
+
+
+@pytest.mark.parametrize("H,Hkv,hd,page,window", [(8, 2, 64, 16, 0), (32, 8, 128, 16, 0), (16, 1, 128, 16, 0), (4, 2, 64, 16, 37),
+                                                  (12, 4, 128, 64, 0), (6, 3, 128, 32, 150)])
+def test_attention_prefill_tcgen05(H, Hkv, hd, page, window):
+    d = _segments([(70, 70), (1, 33), (300, 420), (2, 2), (128, 128), (129, 257), (16, 48), (1, 1)], H, Hkv, hd, page, seed=91, window=window)
+    out = torch.full_like(d["q"], float("nan"))
+    assert ops.attention_prefill_tc(out, d["q"], d["cache"], d["qstart"], d["pos0"], d["bt"], d["S"], d["max_q"], H, Hkv, hd,
+                                    page, window, 1.0 / math.sqrt(hd))
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    assert torch.allclose(out.double().cpu(), d["ref"], rtol=2e-2, atol=2e-2)
+
+
+def test_attention_prefill_tcgen05_finds_a_far_key():
+    H, Hkv, hd, page = 8, 2, 128, 16
+    for far in (0, 15, 16, 127, 128, 511, 600):
+        d = _segments([(140, 900)], H, Hkv, hd, page, seed=170 + far)
+        pages = d["bt"][0].tolist()
+        q = d["q"].view(140, H, hd)
+        d["cache"][pages[far // page], 0, 0, far % page] = (q[139, 1].float() * 6.0).to(torch.bfloat16)
+        d["cache"][pages[far // page], 1, 0, far % page] = 50.0
+        out = torch.zeros_like(d["q"])
+        assert ops.attention_prefill_tc(out, d["q"], d["cache"], d["qstart"], d["pos0"], d["bt"], 1, 140, H, Hkv, hd, page, 0, 1 / math.sqrt(hd))
+        torch.cuda.synchronize()
+        ops.check_kernel_errors()
+        assert float(out.view(140, H, hd)[139, 1].float().min()) > 49.0, f"key {far} was not found"
