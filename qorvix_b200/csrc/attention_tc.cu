@@ -91,6 +91,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// 2^x for x <= 0 on the special-function unit (results below the normal range flush to zero; P is
+// rounded to bfloat16 right after, so the approximation's last bits do not matter)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *(uint32_t*)&h;
@@ -137,7 +144,8 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
   pdl_wait();
   pdl_launch_dependents();
   const int q0 = a.seg_q_start[seg], qlen = a.seg_q_start[seg + 1] - q0;
-  const int tile0 = blockIdx.x * QT;
+  // the last query tiles see the most keys: they are scheduled first
+  const int tile0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * QT;
   if (tile0 >= qlen) return;
   const int pos0 = a.seg_pos0[seg];
   const int kvh = h / (a.H / a.Hkv);
@@ -251,17 +259,25 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
       const uint32_t s_addr = tmem + lane_base + (uint32_t)(s * KT);
       // pass 1: row maximum of the visible, scaled scores
       float mx = -INFINITY;
+      const bool all_visible = key_base >= lo && key_base + KT - 1 <= hi;   // no mask needed in this tile
 #pragma unroll 1
-      for (int c = 0; c < KT; c += 32) {
-        uint32_t v[32];
+      for (int c = 0; c < KT; c += 64) {
+        uint32_t v[64];
         tmem_ld32(s_addr + c, v);
+        tmem_ld32(s_addr + c + 32, v + 32);
         tmem_wait_ld();
+        if (all_visible) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key_base + c + i;
-          if (key >= lo && key <= hi) mx = fmaxf(mx, __uint_as_float(v[i]) * a.scale_log2);
+          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const int key = key_base + c + i;
+            if (key >= lo && key <= hi) mx = fmaxf(mx, __uint_as_float(v[i]));
+          }
         }
       }
+      mx *= a.scale_log2;                              // the scale is positive: max commutes with it
       const float m_new = fmaxf(m, mx);
       const float corr = (m_new == -INFINITY) ? 1.f : exp2f(m - m_new);
       // the P buffer is free once the previous tile's P.V has read it
@@ -280,7 +296,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
             const int key = key_base + c + i + x;
-            e[x] = (key >= lo && key <= hi) ? exp2f(__uint_as_float(v[i + x]) * a.scale_log2 - m_new) : 0.f;
+            e[x] = (key >= lo && key <= hi) ? fast_exp2(__uint_as_float(v[i + x]) * a.scale_log2 - m_new) : 0.f;
             sum += e[x];
           }
           w[i >> 1] = pack2(e[0], e[1]);
