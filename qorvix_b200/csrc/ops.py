@@ -321,22 +321,44 @@ def attention_decode_bf16(out, q, cache_layer, tok_pos, tok_seg, block_table, H,
     return True
 
 
+def _attention_portions_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, Hkv, hd, page,
+                             window, scale) -> bool:
+    """Prompt portions: tcgen05 kernel for long portions at head sizes 64/128, else mma.sync kernels."""
+    if max_q_len >= 32 and attention_prefill_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len,
+                                                H, Hkv, hd, page, window, scale):
+        return True
+    return attention_prefill_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, Hkv, hd,
+                                  page, window, scale)
+
+
 def attention(out, q, cache_layer, ctx, block_table, H, Hkv, hd, page, window, scale) -> None:
     """Attention of every token of the step over its request's pages.  bfloat16: the tensor-core
-    kernels (split-KV for steps of single tokens, flash attention otherwise) when they take the
-    sizes; float32, and sizes they refuse: the CUDA-core kernel."""
+    kernels when they take the sizes (split-KV for single tokens, flash attention for portions; a
+    step whose single-token segments come first is served by both, each on its part); float32,
+    and sizes they refuse: the CUDA-core kernel."""
     if q.dtype == torch.bfloat16:
+        T = q.shape[0]
         if ctx.max_q_len == 1:
-            splits = decode_splits(q.shape[0], Hkv, ctx.max_ctx_len)
+            splits = decode_splits(T, Hkv, ctx.max_ctx_len)
             if attention_decode_bf16(out, q, cache_layer, ctx.tok_pos, ctx.tok_seg, block_table, H, Hkv, hd, page,
                                      window, scale, splits):
                 return
-        elif ctx.max_q_len >= 32 and attention_prefill_tc(out, q, cache_layer, ctx.seg_q_start, ctx.seg_pos0, block_table,
-                                                          ctx.num_segments, ctx.max_q_len, H, Hkv, hd, page, window, scale):
-            return                                    # long portions at head sizes 64/128: tcgen05
-        elif attention_prefill_bf16(out, q, cache_layer, ctx.seg_q_start, ctx.seg_pos0, block_table, ctx.num_segments,
-                                    ctx.max_q_len, H, Hkv, hd, page, window, scale):
-            return
+        else:
+            n1 = 0                                    # leading segments of one token (decoded tokens)
+            while n1 < ctx.num_segments and ctx.seg_len[n1] == 1:
+                n1 += 1
+            S = ctx.num_segments
+            if n1 >= 4 and n1 < S:
+                rest_q = max(ctx.seg_len[n1:])
+                splits = decode_splits(n1, Hkv, ctx.max_ctx_len)
+                ok = attention_decode_bf16(out[:n1], q[:n1], cache_layer, ctx.tok_pos, ctx.tok_seg, block_table, H, Hkv,
+                                           hd, page, window, scale, splits)
+                if ok and _attention_portions_bf16(out, q, cache_layer, ctx.seg_q_start[n1:], ctx.seg_pos0[n1:],
+                                                   block_table[n1:], S - n1, rest_q, H, Hkv, hd, page, window, scale):
+                    return
+            elif _attention_portions_bf16(out, q, cache_layer, ctx.seg_q_start, ctx.seg_pos0, block_table, S,
+                                          ctx.max_q_len, H, Hkv, hd, page, window, scale):
+                return
     attention_generic(out, q, cache_layer, ctx.tok_pos, ctx.tok_seg, block_table, H, Hkv, hd, page, window, scale)
 
 

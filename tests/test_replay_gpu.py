@@ -176,3 +176,29 @@ def test_float32_is_bitwise_stable_across_cuts(models):
         outs.append(res[1:])
         i += n
     assert torch.equal(torch.cat(outs), whole)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [("B", 8.0), ("C", 1.0)])
+def test_decoded_tokens_before_a_portion(models, case, dtype):
+    """Five requests bring one decoded token each, a sixth a prompt portion, in one step: the step
+    is served by the single-token kernel and the portion kernel together."""
+    d, pm = models[case]
+    cfg = TINY[case[0]]
+    r = ModelRunner(d, dtype=dtype, max_tokens=1024, page_size=16, max_requests=8)
+    dec = {f"d{i}": random_tokens(cfg.vocab_size, 20 + 7 * i, 200 + i) for i in range(5)}
+    long = random_tokens(cfg.vocab_size, 90, 300)
+    for k, t in dec.items():
+        r.step([StepEntry(k, t[:-2], [])])
+    r.step([StepEntry("p", long[:40], [])])
+    outs = {k: [] for k in dec}
+    got_p = []
+    for stepi, (a, b) in enumerate(((40, 73), (73, 90))):
+        entries = [StepEntry(k, [t[len(t) - 2 + stepi]], [0]) for k, t in dec.items()] + [StepEntry("p", long[a:b], list(range(b - a)))]
+        out = r.step(entries)
+        for i, k in enumerate(dec):
+            outs[k].append(out[i:i + 1])
+        got_p.append(out[5:])
+    for k, t in dec.items():
+        assert_close_logits(torch.cat(outs[k]), pm.logits(t)[-2:], dtype, f"decoded {k}", sharp=case[1] > 1)
+    assert_close_logits(torch.cat(got_p), pm.logits(long)[40:], dtype, "portion beside decoded tokens", sharp=case[1] > 1)
