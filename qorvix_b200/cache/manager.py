@@ -156,6 +156,21 @@ class CacheManager:
             out[gi] = max(0, blocks - have)
         return out
 
+    def one_more_token_fits(self, req_ids: Sequence[Hashable]) -> int:
+        """How many of the given live requests, taken in order, can each hold one more token with
+        the pages that are free now.  One pass; the scheduler's check for a round of decoding."""
+        free = {gi: self.groups[gi].pool.num_free for gi in self.paged_groups()}
+        page = self.page_size
+        for n, rid in enumerate(req_ids):
+            r = self._requests[rid]
+            blocks = r.length // page + 1
+            for gi in free:
+                if len(r.tables[gi]) < blocks:
+                    if free[gi] == 0:
+                        return n
+                    free[gi] -= 1
+        return len(req_ids)
+
     def can_reserve(self, wants: Sequence[Tuple[Hashable, int]]) -> bool:
         """Whether all (request or None, new tokens) of a step fit together."""
         total: Dict[int, int] = {}

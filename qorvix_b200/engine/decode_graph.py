@@ -51,6 +51,8 @@ class DecodeGraph:
         self.host_np[4 * S:] = cache.scratch_page
         self.event: Optional[torch.cuda.Event] = None
         self.row_state = {g: [None] * S for g in self.groups}
+        self._last_keys, self._last_lens = None, None
+        self._windowed = any(cache.groups[g].spec.window > 0 for g in self.groups)
         o = self.n_dyn
         self.dbuf[o:o + S] = torch.arange(S, dtype=torch.int32)                 # tok_seg
         self.dbuf[o + S:o + 2 * S + 1] = torch.arange(S + 1, dtype=torch.int32)   # seg_q_start
@@ -124,7 +126,15 @@ class DecodeGraph:
         h[2 * S + n:3 * S] = 0
         h[3 * S:3 * S + n] = [s["slot"] for s in segs]
         h[3 * S + n:4 * S] = scratch_slot
+        # nothing to do for the block tables when the same requests sit in the same rows and none of
+        # their tables grew (the usual decode step)
+        keys = [s["rid"] for s in segs]
+        lens = [len(t) for g in self.groups for t in tables[g]]
+        unchanged = keys == self._last_keys and lens == self._last_lens and not self._windowed
+        self._last_keys, self._last_lens = keys, lens
         for k, g in enumerate(self.groups):
+            if unchanged:
+                break
             base = 4 * S + k * S * W
             state = self.row_state[g]
             windowed = cache.groups[g].spec.window > 0

@@ -138,15 +138,15 @@ class Scheduler:
             wants = []                                    # (request id, new tokens) so far
             plan.decode, plan.prefill = [], []
             fits = True
-            for rid in self._running:                     # decode tokens first
-                r = self._requests[rid]
-                if r.pending is not None and budget > 0:
-                    wants.append((rid, 1))
-                    if not cache.can_reserve(wants):
-                        fits = False
-                        break
-                    plan.decode.append(rid)
-                    budget -= 1
+            # decode tokens first: one per running request that has a sampled token to feed
+            ready = [rid for rid in self._running if self._requests[rid].pending is not None][:budget]
+            n_fit = cache.one_more_token_fits(ready)
+            if n_fit < len(ready):
+                fits = False
+            else:
+                plan.decode = ready
+                wants = [(rid, 1) for rid in ready]
+                budget -= len(ready)
             if fits:
                 for rid in self._running:                 # then portions of running prompts
                     r = self._requests[rid]
