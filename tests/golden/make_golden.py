@@ -137,7 +137,9 @@ def golden_config(m: dict) -> dict:
 
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/reference")
+    ref = Path(sys.argv[1])
     with tempfile.TemporaryDirectory() as tmp:
         tmp = Path(tmp)
         (tmp / "driver.cpp").write_text(DRIVER)
