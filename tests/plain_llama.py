@@ -73,7 +73,7 @@ def read_model_dir(model_dir):
 
 def embedding(table: torch.Tensor, ids) -> torch.Tensor:
     """x = tokenEmbd[token, :], no scaling (runtime/src/text_model.cpp:120)."""
-    return table[torch.as_tensor(ids, dtype=torch.long)]
+    return table[torch.as_tensor(ids, dtype=torch.long, device=table.device)]
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -140,8 +140,8 @@ def rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor) -> to
     pairs (i, i+half): a' = a cos - b sin, b' = a sin + b cos, theta = pos * f_i."""
     half = x.shape[-1] // 2
     theta = positions.to(torch.float64)[:, None] * inv_freq.to(torch.float64)[None, :]
-    cos = torch.cos(theta).to(x.dtype)[:, None, :]
-    sin = torch.sin(theta).to(x.dtype)[:, None, :]
+    cos = torch.cos(theta).to(x.dtype).to(x.device)[:, None, :]
+    sin = torch.sin(theta).to(x.dtype).to(x.device)[:, None, :]
     a, b = x[..., :half], x[..., half:]
     return torch.cat([a * cos - b * sin, a * sin + b * cos], dim=-1)
 

@@ -202,3 +202,30 @@ def test_decoded_tokens_before_a_portion(models, case, dtype):
     for k, t in dec.items():
         assert_close_logits(torch.cat(outs[k]), pm.logits(t)[-2:], dtype, f"decoded {k}", sharp=case[1] > 1)
     assert_close_logits(torch.cat(got_p), pm.logits(long)[40:], dtype, "portion beside decoded tokens", sharp=case[1] > 1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_layer_of_llama31_8b_sizes(dtype):
+    """The real sizes (hidden 4096, 32 heads over 8 kv heads of 128, feed-forward 14336, vocabulary
+    128256, llama3 scaling from 8192) on one layer: whole, in portions and token by token, against
+    the plain implementation (run in float64 on the GPU, or it would take minutes)."""
+    import plain_llama as plain
+    from qorvix_b200 import LlamaConfig
+    from qorvix_b200.config import RopeScaling
+    from qorvix_b200.weights import random_tensors
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
+                      num_hidden_layers=1, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                      max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=500000.0,
+                      rope_scaling=RopeScaling("llama3", 8.0, 1.0, 4.0, 8192), tie_word_embeddings=False)
+    # N(0, 0.02) weights at this width already give scores with a standard deviation of about 1.6,
+    # so keys matter without any sharpening
+    tensors = dict(random_tensors(cfg, 3, "cuda", torch.bfloat16))
+    toks = random_tokens(cfg.vocab_size, 200, 77)
+    ref = plain.forward(cfg.to_dict() | {"rope_scaling": cfg.rope_scaling.to_dict()}, tensors, toks).cpu()
+    r = ModelRunner(config=cfg, tensors=tensors, dtype=dtype, max_tokens=512, max_requests=2)
+    whole = r.step([StepEntry("w", toks, list(range(200)))], end=["w"])
+    assert_close_logits(whole, ref, dtype, "8B-size layer, whole")
+    outs = [r.step([StepEntry("p", toks[:130], list(range(130)))]), r.step([StepEntry("p", toks[130:190], list(range(60)))])]
+    for i in range(190, 200):
+        outs.append(r.step([StepEntry("p", [toks[i]], [0])]))
+    assert_close_logits(torch.cat(outs), ref, dtype, "8B-size layer, portions and decoding")
