@@ -192,11 +192,23 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int ld, T* __restrict_
     T* v = row + (size_t)head * hd;
     const bool to_cache = head >= H && cache;
     T* dst = to_cache ? kdst + (size_t)(head - H) * page * hd : v;
-    for (int i = lane; i < half; i += 32) {
-      const float a = to_f(v[i]), b = to_f(v[i + half]);
-      const float2 c = cs[i];
-      dst[i] = from_f<T>(a * c.x - b * c.y);
-      dst[i + half] = from_f<T>(a * c.y + b * c.x);
+    if (sizeof(T) == 2 && (half & 1) == 0 && (((uintptr_t)v | (uintptr_t)dst) & 3) == 0) {
+      // bfloat16: two neighbouring pairs per lane, 4-byte loads and stores
+      for (int i = 2 * lane; i < half; i += 64) {
+        const __nv_bfloat162 a2 = *(const __nv_bfloat162*)((const bf16*)v + i);
+        const __nv_bfloat162 b2 = *(const __nv_bfloat162*)((const bf16*)v + i + half);
+        const float2 c0 = cs[i], c1 = cs[i + 1];
+        const float a0 = __low2float(a2), a1 = __high2float(a2), b0 = __low2float(b2), b1 = __high2float(b2);
+        *(__nv_bfloat162*)((bf16*)dst + i) = __floats2bfloat162_rn(a0 * c0.x - b0 * c0.y, a1 * c1.x - b1 * c1.y);
+        *(__nv_bfloat162*)((bf16*)dst + i + half) = __floats2bfloat162_rn(a0 * c0.y + b0 * c0.x, a1 * c1.y + b1 * c1.x);
+      }
+    } else {
+      for (int i = lane; i < half; i += 32) {
+        const float a = to_f(v[i]), b = to_f(v[i + half]);
+        const float2 c = cs[i];
+        dst[i] = from_f<T>(a * c.x - b * c.y);
+        dst[i + half] = from_f<T>(a * c.y + b * c.x);
+      }
     }
     if (to_cache)      // dims beyond the rotated ones pass through
       for (int i = rot + lane; i < hd; i += 32) dst[i] = v[i];
@@ -204,7 +216,11 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int ld, T* __restrict_
     const int vh = head - H - Hkv;
     const T* v = row + (size_t)head * hd;
     T* dst = vdst + (size_t)vh * page * hd;
-    for (int i = lane; i < hd; i += 32) dst[i] = v[i];
+    if (sizeof(T) == 2 && (hd & 7) == 0 && (((uintptr_t)v | (uintptr_t)dst) & 15) == 0) {
+      for (int i = 8 * lane; i < hd; i += 256) *(uint4*)((bf16*)dst + i) = *(const uint4*)((const bf16*)v + i);
+    } else {
+      for (int i = lane; i < hd; i += 32) dst[i] = v[i];
+    }
   }
 }
 
