@@ -215,6 +215,8 @@ def main() -> int:
         for b in (1, 64):
             ms, _ = decode_device(b, ctx, max(16, K // 2), W)
             points[f"decode_b{b}"] = b / (ms / 1e3)
+        ms, _ = decode_device(B, 8192 - 64, max(16, K // 2), W)      # the longest context the configuration names
+        points[f"decode_b{B}_ctx8192"] = B / (ms / 1e3)
 
     # ---- end to end through the public API: host tokens in, sampled ids out, every step
     sched = llm.new_scheduler()
