@@ -284,30 +284,40 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
       if (ok) ok = mbar_wait(p_empty, (j & 1) ^ 1, a.err, 18);
       // pass 2: exponentials, row sum, P into shared memory (K-major, 128-byte swizzle)
       float sum = 0.f;
+      const float neg_m = -m_new;
 #pragma unroll 1
-      for (int c = 0; c < KT; c += 32) {
-        uint32_t v[32];
+      for (int c = 0; c < KT; c += 64) {
+        uint32_t v[64];
         tmem_ld32(s_addr + c, v);
+        tmem_ld32(s_addr + c + 32, v + 32);
         tmem_wait_ld();
-        uint32_t w[16];
+        uint32_t w[32];
+        if (all_visible) {                             // most tiles: no mask, two instructions per score
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float e[2];
-#pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            const int key = key_base + c + i + x;
-            e[x] = (key >= lo && key <= hi) ? fast_exp2(__uint_as_float(v[i + x]) * a.scale_log2 - m_new) : 0.f;
-            sum += e[x];
+          for (int i = 0; i < 64; i += 2) {
+            const float e0 = fast_exp2(fmaf(__uint_as_float(v[i]), a.scale_log2, neg_m));
+            const float e1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), a.scale_log2, neg_m));
+            sum += e0 + e1;
+            w[i >> 1] = pack2(e0, e1);
           }
-          w[i >> 1] = pack2(e[0], e[1]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; i += 2) {
+            float e[2];
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+              const int key = key_base + c + i + x;
+              e[x] = (key >= lo && key <= hi) ? fast_exp2(fmaf(__uint_as_float(v[i + x]), a.scale_log2, neg_m)) : 0.f;
+            }
+            sum += e[0] + e[1];
+            w[i >> 1] = pack2(e[0], e[1]);
+          }
         }
-        // 32 keys = 4 chunks of 16 bytes in half (c / 64), chunk index (c % 64) / 8 + k
+        // 64 keys = the 8 chunks of 16 bytes of this row in half (c / 64)
         uint8_t* prow = sP + (c >> 6) * HALF_BYTES + r * 128;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int chunk = ((c & 63) >> 3) + k;
-          *(uint4*)(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
-        }
+        for (int k = 0; k < 8; ++k)
+          *(uint4*)(prow + ((k ^ (r & 7)) << 4)) = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
       }
       tc_fence_before();
       mbar_arrive(&s_empty[s]);                       // S[s] may be overwritten by tile j + 2
