@@ -12,15 +12,21 @@ out again at once.  Reservation is all-or-nothing over all groups and happens be
 is built, so running out of pages is the caller's decision to handle, never a fault inside
 a step (the reference breaks out of its grow loop and then writes through a null slot,
 runtime/src/text_model.cpp:138-140).
+
+The bookkeeping (free lists, block tables, slots, reservation, window release, invariants)
+is C++ (csrc/host_runtime.cpp); this class owns the device tensors and maps request ids of
+any hashable type to the integers the C++ side uses.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import torch
 
-from .page_pool import PageError, PagePool
+from . import native
+from .page_pool import PageError
 from .spec import FixedStateSpec, PagedKVSpec
 
 
@@ -44,26 +50,37 @@ class LayerCacheView:
     page_size: int = 0
 
 
+class _PoolView:
+    """Read-only view of one paged group's pool in the native manager."""
+
+    def __init__(self, manager, paged_index: int):
+        self._m, self._g = manager, paged_index
+
+    @property
+    def num_pages(self) -> int:
+        return self._m.num_pages
+
+    @property
+    def num_free(self) -> int:
+        return self._m._lib.qvh_free_pages(self._m._h, self._g)
+
+    @property
+    def num_held(self) -> int:
+        return self._m._lib.qvh_held_pages(self._m._h, self._g)
+
+
 @dataclass
 class _Group:
     spec: object
     layers: List[int]
-    pool: Optional[PagePool] = None
+    pool: Optional[_PoolView] = None
     tensor: Optional[torch.Tensor] = None
-
-
-@dataclass
-class _Request:
-    slot: int
-    length: int = 0
-    tables: Dict[int, List[int]] = field(default_factory=dict)     # group -> page id per block (-1: given back)
-    admitted_at: int = 0
 
 
 class CacheManager:
     def __init__(self, needs: Sequence[Tuple[object, Optional[int]]], max_tokens: int, page_size: int,
                  max_requests: int, device="cuda", dtype=torch.bfloat16, allocate: bool = True):
-        """needs[i] = (cache spec or None, index of the layer whose cache layer i reads or None).
+        """needs[i] = (cache spec or None, index of the run whose cache run i reads or None).
         max_tokens: how many tokens (each request rounded up to whole pages) fit at once."""
         if page_size <= 0 or page_size % 16:
             raise ValueError(f"page_size {page_size} must be a positive multiple of 16")
@@ -90,22 +107,38 @@ class CacheManager:
         for li, src in enumerate(self._reads_from):
             if src is not None and (not 0 <= src < len(needs) or needs[src][0] is None):
                 raise ValueError(f"layer {li} reads the cache of layer {src}, which keeps none")
-        for g in self.groups:
+        # the native side knows only the paged groups, numbered in the order they appear here
+        self._paged: List[int] = []
+        windows: List[int] = []
+        for gi, g in enumerate(self.groups):
             if isinstance(g.spec, PagedKVSpec):
-                g.pool = PagePool(self.num_pages)
+                self._paged.append(gi)
+                windows.append(int(g.spec.window))
+            elif not isinstance(g.spec, FixedStateSpec):
+                raise TypeError(f"unknown cache spec {g.spec!r}")
+        self._native_index = {gi: k for k, gi in enumerate(self._paged)}
+        self._lib = native.lib()
+        self._h = self._lib.qvh_create(len(windows), native.ints(windows) if windows else None, self.num_pages,
+                                       self.page_size, self.max_requests)
+        if not self._h:
+            raise ValueError("the cache manager could not be created with these sizes")
+        for gi, g in enumerate(self.groups):
+            if isinstance(g.spec, PagedKVSpec):
+                g.pool = _PoolView(self, self._native_index[gi])
                 if allocate:
                     g.tensor = torch.zeros((len(g.layers), self.num_pages + 1, 2, g.spec.num_kv_heads,
                                             self.page_size, g.spec.head_dim), device=self.device, dtype=dtype)
-            elif isinstance(g.spec, FixedStateSpec):
-                if allocate:
-                    # one more slot than requests: the last is scratch for padded rows of a captured step
-                    g.tensor = torch.zeros((len(g.layers), self.max_requests + 1, *g.spec.shape),
-                                           device=self.device, dtype=_DTYPES.get(g.spec.dtype, g.spec.dtype))
-            else:
-                raise TypeError(f"unknown cache spec {g.spec!r}")
-        self._free_slots: List[int] = list(range(self.max_requests - 1, -1, -1))
-        self._requests: Dict[Hashable, _Request] = {}
-        self._clock = 0
+            elif allocate:
+                # one more slot than requests: the last is scratch for padded rows of a captured step
+                g.tensor = torch.zeros((len(g.layers), self.max_requests + 1, *g.spec.shape),
+                                       device=self.device, dtype=_DTYPES.get(g.spec.dtype, g.spec.dtype))
+        self._ids: Dict[Hashable, int] = {}          # request id -> the integer the native side knows it by
+        self._next_id = 1
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.qvh_destroy(self._h)
+            self._h = None
 
     # ------------------------------------------------------------------ queries
     @property
@@ -117,85 +150,78 @@ class CacheManager:
         return self.max_requests
 
     def paged_groups(self) -> List[int]:
-        return [i for i, g in enumerate(self.groups) if g.pool is not None]
+        return list(self._paged)
 
     def free_pages(self, group: int = None) -> int:
-        pools = [g.pool for g in self.groups if g.pool is not None] if group is None else [self.groups[group].pool]
-        return min((p.num_free for p in pools), default=self.num_pages)
+        if not self._paged:
+            return self.num_pages
+        return self._lib.qvh_free_pages(self._h, -1 if group is None else self._native_index[group])
 
     def free_slots(self) -> int:
-        return len(self._free_slots)
+        return self._lib.qvh_free_slots(self._h)
 
     def has(self, req_id) -> bool:
-        return req_id in self._requests
+        return req_id in self._ids
+
+    def native_id(self, req_id) -> int:
+        return self._ids[req_id]
 
     def length(self, req_id) -> int:
-        return self._requests[req_id].length
+        return self._lib.qvh_length(self._h, self._ids[req_id])
 
     def slot(self, req_id) -> int:
-        return self._requests[req_id].slot
+        return self._lib.qvh_slot(self._h, self._ids[req_id])
 
     def epoch(self, req_id) -> int:
         """A number that differs between two admissions of the same request id."""
-        return self._requests[req_id].admitted_at
+        return self._lib.qvh_epoch(self._h, self._ids[req_id])
 
     def live_requests(self) -> list:
-        return list(self._requests)
+        return list(self._ids)
 
     def block_table(self, req_id, group: int) -> List[int]:
-        return self._requests[req_id].tables[group]
+        nid, g = self._ids[req_id], self._native_index[group]
+        n = self._lib.qvh_table_len(self._h, nid, g)
+        out = (ctypes.c_int * max(n, 1))()
+        self._lib.qvh_table_copy(self._h, nid, g, out, n)
+        return list(out[:n])
 
     def pages_needed(self, req_id, n_new: int) -> Dict[int, int]:
         """Pages each paged group must add so that `n_new` more tokens fit (req_id None: a new request)."""
-        r = self._requests.get(req_id) if req_id is not None else None
-        length = r.length if r else 0
-        blocks = -(-(length + n_new) // self.page_size)
-        out = {}
-        for gi in self.paged_groups():
-            have = len(r.tables[gi]) if r else 0
-            out[gi] = max(0, blocks - have)
-        return out
+        known = req_id is not None and req_id in self._ids
+        nid = self._ids[req_id] if known else 0
+        return {gi: self._lib.qvh_pages_needed(self._h, nid, 1 if known else 0, n_new, self._native_index[gi])
+                for gi in self._paged}
+
+    def can_reserve(self, wants: Sequence[Tuple[Hashable, int]]) -> bool:
+        """Whether all (request or None, new tokens) of a step fit together."""
+        n = len(wants)
+        if n == 0:
+            return True
+        rids = [self._ids.get(r, 0) if r is not None else 0 for r, _ in wants]
+        new = [0 if (r is not None and r in self._ids) else 1 for r, _ in wants]
+        return bool(self._lib.qvh_can_reserve(self._h, n, native.longs(rids), native.ints(new),
+                                              native.ints([k for _, k in wants])))
 
     def one_more_token_fits(self, req_ids: Sequence[Hashable]) -> int:
         """How many of the given live requests, taken in order, can each hold one more token with
         the pages that are free now.  One pass; the scheduler's check for a round of decoding."""
-        free = {gi: self.groups[gi].pool.num_free for gi in self.paged_groups()}
-        page = self.page_size
-        for n, rid in enumerate(req_ids):
-            r = self._requests[rid]
-            blocks = r.length // page + 1
-            for gi in free:
-                if len(r.tables[gi]) < blocks:
-                    if free[gi] == 0:
-                        return n
-                    free[gi] -= 1
-        return len(req_ids)
-
-    def can_reserve(self, wants: Sequence[Tuple[Hashable, int]]) -> bool:
-        """Whether all (request or None, new tokens) of a step fit together."""
-        total: Dict[int, int] = {}
-        new_slots = 0
-        for req_id, n in wants:
-            if req_id is None or req_id not in self._requests:
-                new_slots += 1
-                req_id = None
-            for gi, k in self.pages_needed(req_id, n).items():
-                total[gi] = total.get(gi, 0) + k
-        if new_slots > len(self._free_slots):
-            return False
-        return all(k <= self.groups[gi].pool.num_free for gi, k in total.items())
+        n = len(req_ids)
+        if n == 0:
+            return 0
+        return self._lib.qvh_one_more_token_fits(self._h, n, native.longs([self._ids[r] for r in req_ids]))
 
     # ------------------------------------------------------------------ life of a request
     def admit(self, req_id) -> int:
         """Gives the request a slot (its state slots are zeroed); no pages yet."""
-        if req_id in self._requests:
+        if req_id in self._ids:
             raise ValueError(f"request {req_id!r} is already live")
-        if not self._free_slots:
+        nid = self._next_id
+        slot = self._lib.qvh_admit(self._h, nid)
+        if slot == -1:
             raise OutOfSlots(f"all {self.max_requests} request slots are taken")
-        slot = self._free_slots.pop()
-        self._clock += 1
-        self._requests[req_id] = _Request(slot=slot, tables={gi: [] for gi in self.paged_groups()},
-                                          admitted_at=self._clock)
+        self._next_id += 1
+        self._ids[req_id] = nid
         for g in self.groups:
             if g.pool is None and g.tensor is not None:
                 g.tensor[:, slot].zero_()
@@ -203,44 +229,38 @@ class CacheManager:
 
     def reserve(self, req_id, n_new: int) -> bool:
         """Pages for n_new more tokens in every paged group, or nothing at all."""
-        r = self._requests[req_id]
-        need = self.pages_needed(req_id, n_new)
-        if any(k > self.groups[gi].pool.num_free for gi, k in need.items()):
-            return False
-        for gi, k in need.items():
-            r.tables[gi].extend(self.groups[gi].pool.alloc(k))
-        return True
+        return self._lib.qvh_reserve(self._h, self._ids[req_id], n_new) == 1
 
     def commit(self, req_id, n_new: int) -> None:
         """The request now holds n_new more tokens; pages a window has passed are given back."""
-        r = self._requests[req_id]
-        r.length += n_new
-        for gi in self.paged_groups():
-            g = self.groups[gi]
-            if len(r.tables[gi]) * self.page_size < r.length:
-                raise PageError(f"request {req_id!r} holds {r.length} tokens but only {len(r.tables[gi])} pages in group {gi}")
-            w = g.spec.window
-            if w > 0:
-                first_needed = max(0, r.length - w + 1)        # the oldest key a later query reads
-                dead_blocks = first_needed // self.page_size
-                table = r.tables[gi]
-                gone = [p for p in table[:dead_blocks] if p >= 0]
-                if gone:
-                    g.pool.free(gone)
-                    for b in range(dead_blocks):
-                        table[b] = -1
+        rc = self._lib.qvh_commit(self._h, self._ids[req_id], n_new)
+        if rc == -3:
+            raise PageError(f"request {req_id!r} holds more tokens than its pages have room for")
 
     def release(self, req_id) -> None:
         """The request ends: everything it holds goes back."""
-        r = self._requests.pop(req_id)
-        for gi, table in r.tables.items():
-            self.groups[gi].pool.free([p for p in table if p >= 0])
-        self._free_slots.append(r.slot)
+        nid = self._ids.pop(req_id)                  # KeyError for a request that is not live
+        self._lib.qvh_release(self._h, nid)
 
     def youngest(self, among=None):
         """The most recently admitted live request (the one to preempt first)."""
-        ids = [i for i in (among if among is not None else self._requests) if i in self._requests]
-        return max(ids, key=lambda i: self._requests[i].admitted_at) if ids else None
+        ids = [i for i in (among if among is not None else self._ids) if i in self._ids]
+        if not ids:
+            return None
+        k = self._lib.qvh_youngest(self._h, len(ids), native.longs([self._ids[i] for i in ids]))
+        return ids[k] if k >= 0 else None
+
+    # ------------------------------------------------------------------ captured decode steps
+    def fill_decode_rows(self, req_ids: Sequence[Hashable], tokens: Optional[Sequence[int]], rows: int, width: int,
+                         host_ptr: int, row_epoch_ptr: int, row_len_ptr: int) -> None:
+        """Writes positions, slots and block tables (and tokens, if given) of a decode-only step for
+        the given live requests into the pinned buffer at host_ptr, padded to `rows` rows."""
+        n = len(req_ids)
+        rc = self._lib.qvh_fill_decode(self._h, n, native.longs([self._ids[r] for r in req_ids]),
+                                       native.ints(list(tokens)) if tokens is not None else None, rows, width,
+                                       self.scratch_page, self.scratch_slot, host_ptr, row_epoch_ptr, row_len_ptr)
+        if rc != 0:
+            raise KeyError("a request of the decode step is not live")
 
     # ------------------------------------------------------------------ what the model sees
     def layer_view(self, layer: int) -> LayerCacheView:
@@ -257,25 +277,9 @@ class CacheManager:
 
     # ------------------------------------------------------------------ checks (tests)
     def check_invariants(self) -> None:
-        """No page lost, none held twice, none both free and held."""
-        for gi in self.paged_groups():
-            pool = self.groups[gi].pool
-            seen = {}
-            for rid, r in self._requests.items():
-                for p in r.tables[gi]:
-                    if p < 0:
-                        continue
-                    if p in seen:
-                        raise PageError(f"group {gi}: page {p} is held by {seen[p]!r} and {rid!r}")
-                    if not pool.is_held(p):
-                        raise PageError(f"group {gi}: page {p} of {rid!r} is on the free list")
-                    seen[p] = rid
-            if len(seen) != pool.num_held:
-                raise PageError(f"group {gi}: {pool.num_held} pages are taken but requests hold {len(seen)}")
-            if len(set(pool._free)) != len(pool._free):
-                raise PageError(f"group {gi}: a page is on the free list twice")
-        slots = [r.slot for r in self._requests.values()]
-        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
-            raise PageError("a request slot is held twice or is both free and held")
-        if len(slots) + len(self._free_slots) != self.max_requests:
-            raise PageError("a request slot was lost")
+        """No page lost, none held twice, none both free and held; the same for request slots."""
+        buf = ctypes.create_string_buffer(512)
+        if self._lib.qvh_check(self._h, buf, 512) != 0:
+            raise PageError(buf.value.decode())
+        if self._lib.qvh_num_live(self._h) != len(self._ids):
+            raise PageError("the request table and the native manager disagree on the live requests")

@@ -36,7 +36,9 @@ LIBRARIES = {
     "gemm_bf16": "gemm_bf16.cu",
     "attention_bf16": "attention_bf16.cu",
     "attention_tc": "attention_tc.cu",
+    "host_runtime": "host_runtime.cpp",          # host-side cache bookkeeping: plain C++, no CUDA
 }
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -48,6 +50,13 @@ class KernelBuildError(RuntimeError):
 
 def _say(msg: str) -> None:
     print(f"[qorvix_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def find_host_compiler() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and (os.path.isfile(cand) or shutil.which(cand)):
+            return shutil.which(cand) or cand
+    return find_nvcc()             # nvcc hands .cpp files to its host compiler
 
 
 def find_nvcc() -> str:
@@ -99,11 +108,17 @@ def compile_library(name: str, verbose: bool = True) -> Path:
     out = library_path(name)
     if out.is_file():
         return out
-    nvcc = find_nvcc()
     tmp = out.with_name(out.name + f".tmp{os.getpid()}")
-    cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-o", str(tmp), str(src)]
-    if verbose:
-        _say(f"compiling {src.name} for sm_100a ...")
+    if src.suffix == ".cpp":
+        cxx = find_host_compiler()
+        flags = ["--shared", "-Xcompiler", "-fPIC", "-O2", "-std=c++17"] if os.path.basename(cxx).startswith("nvcc") else HOST_FLAGS
+        cmd = [cxx, *flags, "-I", str(CSRC), "-o", str(tmp), str(src)]
+        if verbose:
+            _say(f"compiling {src.name} ...")
+    else:
+        cmd = [find_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-o", str(tmp), str(src)]
+        if verbose:
+            _say(f"compiling {src.name} for sm_100a ...")
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     done = threading.Event()
@@ -121,7 +136,7 @@ def compile_library(name: str, verbose: bool = True) -> Path:
             tmp.unlink()
         except OSError:
             pass
-        raise KernelBuildError(f"nvcc failed on {src.name}:\n{log}")
+        raise KernelBuildError(f"the compiler failed on {src.name}:\n{log}")
     os.replace(tmp, out)
     for old in out.parent.glob(f"qv_{name}-*.so"):      # drop binaries of older sources
         if old != out:

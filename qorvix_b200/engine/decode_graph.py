@@ -16,8 +16,9 @@ from __future__ import annotations
 
 import gc
 import weakref
-from typing import Dict, List, Optional
+from typing import Optional
 
+import numpy as np
 import torch
 
 from ..csrc import ops
@@ -50,9 +51,10 @@ class DecodeGraph:
         self.host_np[3 * S:4 * S] = cache.scratch_slot          # padded rows: scratch slot, scratch page
         self.host_np[4 * S:] = cache.scratch_page
         self.event: Optional[torch.cuda.Event] = None
-        self.row_state = {g: [None] * S for g in self.groups}
-        self._last_keys, self._last_lens = None, None
-        self._windowed = any(cache.groups[g].spec.window > 0 for g in self.groups)
+        # what each block-table row of the mirror holds: the admission it belongs to and how many
+        # entries of it are written (0: padding)
+        self.row_epoch = np.zeros(max(1, len(self.groups) * S), dtype=np.int64)
+        self.row_len = np.zeros(max(1, len(self.groups) * S), dtype=np.int32)
         o = self.n_dyn
         self.dbuf[o:o + S] = torch.arange(S, dtype=torch.int32)                 # tok_seg
         self.dbuf[o + S:o + 2 * S + 1] = torch.arange(S + 1, dtype=torch.int32)   # seg_q_start
@@ -108,54 +110,18 @@ class DecodeGraph:
         self.kernels = ops.launch_count() - before
         self.dbuf[0:self.S].zero_()
 
-    def run(self, segs: List[dict], tables: Dict[int, List[List[int]]], with_tokens: bool) -> None:
-        """Refreshes the integer buffer from `segs` (tokens only if with_tokens) and replays."""
-        S, n, W = self.S, len(segs), self.width
-        cache = self.runner.cache
-        scratch_page, scratch_slot = cache.scratch_page, cache.scratch_slot
+    def run(self, req_ids, tokens) -> None:
+        """Refreshes the integer buffer for the given live requests, whose pages for one more token
+        are reserved, and replays.  tokens None: the token slots keep what the last replay left."""
+        S, n = self.S, len(req_ids)
+        if n > S:
+            raise ValueError(f"{n} requests in a captured step of {S}")
         if self.event is not None:
             self.event.synchronize()                          # the last copy has read the mirror
-        h = self.host_np
-        if with_tokens:
-            h[0:n] = [s["tokens"][0] for s in segs]
-            h[n:S] = 0
-        pos = [s["pos0"] for s in segs]
-        h[S:S + n] = pos
-        h[S + n:2 * S] = 0
-        h[2 * S:2 * S + n] = pos
-        h[2 * S + n:3 * S] = 0
-        h[3 * S:3 * S + n] = [s["slot"] for s in segs]
-        h[3 * S + n:4 * S] = scratch_slot
-        # nothing to do for the block tables when the same requests sit in the same rows and none of
-        # their tables grew (the usual decode step)
-        keys = [s["rid"] for s in segs]
-        lens = [len(t) for g in self.groups for t in tables[g]]
-        unchanged = keys == self._last_keys and lens == self._last_lens and not self._windowed
-        self._last_keys, self._last_lens = keys, lens
-        for k, g in enumerate(self.groups):
-            if unchanged:
-                break
-            base = 4 * S + k * S * W
-            state = self.row_state[g]
-            windowed = cache.groups[g].spec.window > 0
-            for i in range(S):
-                row = base + i * W
-                if i >= n:
-                    if state[i] is not None:
-                        h[row:row + W] = scratch_page
-                        state[i] = None
-                    continue
-                t = tables[g][i]
-                key = segs[i]["rid"]
-                st = state[i]
-                if st is not None and st[0] == key and st[1] <= len(t) and not windowed:
-                    if st[1] < len(t):
-                        h[row + st[1]:row + len(t)] = t[st[1]:]
-                else:
-                    h[row:row + W] = scratch_page
-                    h[row:row + len(t)] = [(p if p >= 0 else scratch_page) for p in t]
-                state[i] = (key, len(t))
-        lo = 0 if with_tokens else S
+        # Block-table rows are kept between steps; the C++ side writes only what grew or changed.
+        self.runner.cache.fill_decode_rows(req_ids, tokens, S, self.width, self.host.data_ptr(),
+                                           self.row_epoch.ctypes.data, self.row_len.ctypes.data)
+        lo = 0 if tokens is not None else S
         self.dbuf[lo:self.n_dyn].copy_(self.host[lo:], non_blocking=True)
         if self.event is None:
             self.event = torch.cuda.Event()
@@ -182,13 +148,10 @@ class DecodeLoop:
 
     def step(self) -> None:
         r = self.runner
-        segs = []
         for rid in self.req_ids:
             if not r.cache.reserve(rid, 1):
                 raise RuntimeError("out of pages in a decode loop")
-            segs.append(dict(tokens=[0], pos0=r.cache.length(rid), slot=r.cache.slot(rid), rid=(rid, r.cache.epoch(rid))))
-        tables = {g: [r.cache.block_table(rid, g) for rid in self.req_ids] for g in r.cache.paged_groups()}
-        self.graph.run(segs, tables, with_tokens=False)
+        self.graph.run(self.req_ids, None)
         for rid in self.req_ids:
             r.cache.commit(rid, 1)
         self.produced += 1

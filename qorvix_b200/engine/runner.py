@@ -128,12 +128,14 @@ class ModelRunner:
                 self.cache.admit(e.req_id)
             ok = self.cache.reserve(e.req_id, len(e.tokens))
             assert ok, "reservation was checked for the whole step"
+            if not build:
+                continue
             segs.append(dict(tokens=[int(t) for t in e.tokens], pos0=self.cache.length(e.req_id),
                              slot=self.cache.slot(e.req_id), want=[int(w) for w in e.want], first=first,
                              rid=(e.req_id, self.cache.epoch(e.req_id))))
-        tables = {g: [self.cache.block_table(e.req_id, g) for e in entries] for g in self.cache.paged_groups()}
         if not build:
-            return segs, tables
+            return None
+        tables = {g: [self.cache.block_table(e.req_id, g) for e in entries] for g in self.cache.paged_groups()}
         return self._builder.build(segs, tables, self.cache.scratch_page)
 
     def step(self, entries: Sequence[StepEntry], end: Iterable[Hashable] = ()) -> Optional[torch.Tensor]:
@@ -144,9 +146,9 @@ class ModelRunner:
         logits = None
         if entries and self.use_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries):
             # decode-only: replay the captured step
-            segs, tables = self.prepare(entries, build=False)
+            self.prepare(entries, build=False)
             graph = self.decode_graph(len(entries))
-            graph.run(segs, tables, with_tokens=True)
+            graph.run([e.req_id for e in entries], [int(e.tokens[0]) for e in entries])
             rows = [i for i, e in enumerate(entries) if len(e.want)]
             if rows:
                 if len(rows) == len(entries):

@@ -130,3 +130,51 @@ def test_random_orders_keep_every_page_accounted_for(seed):
     for rid in list(live):
         m.release(rid)
     assert all(m.free_pages(g) == m.num_pages for g in m.paged_groups()) and m.free_slots() == 5
+
+
+@pytest.mark.parametrize("seed", range(3))
+def test_decode_rows_kept_between_steps_equal_rows_written_afresh(seed):
+    """The rows of a captured decode step are updated in place from step to step; after any order
+    of admissions, growth, window release and ends they equal rows written from the block tables."""
+    import numpy as np
+    rng = random.Random(100 + seed)
+    needs = [(KV, None), (WIN, None)]
+    m = manager(needs, tokens=640, max_requests=4)
+    S, W = 4, 12
+    groups = m.paged_groups()
+    host = np.full(4 * S + len(groups) * S * W, -7, dtype=np.int32)
+    host[4 * S:] = m.scratch_page
+    row_epoch = np.zeros(len(groups) * S, dtype=np.int64)
+    row_len = np.zeros(len(groups) * S, dtype=np.int32)
+    live, counter = [], 0
+    for step in range(300):
+        op = rng.random()
+        if op < 0.15 and m.free_slots():
+            counter += 1
+            rid = ("req", counter % 3, counter)
+            m.admit(rid)
+            n = rng.choice([1, 5, 16, 40])
+            assert m.reserve(rid, n)
+            m.commit(rid, n)
+            live.insert(rng.randrange(len(live) + 1), rid)
+        elif op < 0.25 and live:
+            m.release(live.pop(rng.randrange(len(live))))
+        rows = [r for r in live if m.length(r) + 1 <= W * 16 and m.reserve(r, 1)]
+        tokens = [rng.randrange(100) for _ in rows]
+        m.fill_decode_rows(rows, tokens, S, W, host.ctypes.data, row_epoch.ctypes.data, row_len.ctypes.data)
+        want = np.zeros_like(host)
+        want[3 * S:4 * S] = m.scratch_slot
+        want[4 * S:] = m.scratch_page
+        for i, r in enumerate(rows):
+            want[i], want[S + i], want[2 * S + i], want[3 * S + i] = tokens[i], m.length(r), m.length(r), m.slot(r)
+            for k, g in enumerate(groups):
+                t = [p if p >= 0 else m.scratch_page for p in m.block_table(r, g)]
+                base = 4 * S + (k * S + i) * W
+                want[base:base + len(t)] = t
+        assert (host == want).all(), f"step {step}"
+        for r in rows:
+            m.commit(r, 1)
+        for r in [r for r in live if r not in rows]:
+            live.remove(r)
+            m.release(r)
+        m.check_invariants()
