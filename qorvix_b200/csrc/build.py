@@ -24,7 +24,7 @@ from typing import Dict
 CSRC = Path(__file__).resolve().parent
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--shared", "-Xcompiler", "-fPIC"]
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "tc_common.cuh", "attention_mma.cuh", "attention_noalloc.h"]
 
 # library name -> source file; every kernel family is its own library so that a model
 # compiles only what it uses.
@@ -36,6 +36,7 @@ LIBRARIES = {
     "gemm_bf16": "gemm_bf16.cu",
     "attention_bf16": "attention_bf16.cu",
     "attention_tc": "attention_tc.cu",
+    "decode_fused": "decode_fused.cu",
     "host_runtime": "host_runtime.cpp",          # host-side cache bookkeeping: plain C++, no CUDA
 }
 HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC"]

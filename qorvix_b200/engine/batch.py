@@ -43,6 +43,8 @@ class StepContext:
     seg_first: List[bool] = field(default_factory=list)     # the request's first portion
     max_q_len: int = 0
     max_ctx_len: int = 0
+    captured: bool = False             # the step is being captured or replayed as a CUDA graph
+    fused: object = None               # engine.fused_decode.FusedDecode of a captured decode step, if the model allows
 
     @property
     def decode_only(self) -> bool:

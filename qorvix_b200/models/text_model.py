@@ -51,6 +51,11 @@ class TextModel:
         T = ctx.num_tokens
         residual = torch.empty((T, self.spec.hidden_size), device=self.rt.device, dtype=torch.float32)
         ops.embed(residual, self.embedding, ctx.token_ids)
+        fused = getattr(ctx, "fused", None)
+        if fused is not None:
+            # a captured decode step of a model the fused kernel takes: all layers and the final norm
+            # in one launch; every row is wanted
+            return self.lm_head(fused.run(residual), out_dtype=torch.float32)
         pending = None
         for run, li in enumerate(self.order):
             residual, pending = self.blocks[li].forward(residual, pending, ctx, cache.layer_view(run))
