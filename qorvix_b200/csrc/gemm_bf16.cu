@@ -18,6 +18,8 @@
 // CTA winds down (tensor memory is freed) instead of hanging the device.
 #include "tc_common.cuh"
 
+#define A_TILE_BYTES (BM * BK * 2)
+
 namespace {
 
 struct GemmArgs {
@@ -29,6 +31,7 @@ struct GemmArgs {
   int ldc;
   int kblocks_per_split;
   int splits;
+  const uint8_t* packed;   // the weight matrix as 16 KB tiles (see qv_pack_weight_tiles), or null
 };
 
 // BN: columns of the accumulator (rows of the narrow operand per tile).  SWAP: the wide operand
@@ -89,9 +92,12 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
       const int w_row0 = SWAP ? wide0 : narrow0, x_row0 = SWAP ? narrow0 : wide0;
       const int w_off = SWAP ? 0 : A_BYTES, x_off = SWAP ? A_BYTES : 0;
       const int pre = num_kb < STAGES ? num_kb : STAGES;
+      // a packed weight matrix is read tile by tile with contiguous 16 KB copies (swap layout only)
+      const uint8_t* wp = (SWAP && args.packed) ? args.packed + ((size_t)blockIdx.x * total_kb + kb0) * (size_t)A_BYTES : nullptr;
       for (int kb = 0; kb < pre; ++kb) {
         mbar_expect_tx(&full[kb], STAGE_BYTES);
-        tma_load_2d(tiles + kb * STAGE_BYTES + w_off, w_map, &full[kb], (kb0 + kb) * BK, w_row0);
+        if (wp) bulk_load_1d(tiles + kb * STAGE_BYTES + w_off, wp + (size_t)kb * A_BYTES, &full[kb], A_BYTES);
+        else tma_load_2d(tiles + kb * STAGE_BYTES + w_off, w_map, &full[kb], (kb0 + kb) * BK, w_row0);
       }
       pdl_wait();
       for (int kb = 0; kb < pre; ++kb)
@@ -102,7 +108,8 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
         if (!mbar_wait(&empty[s], ph ^ 1, args.err, 1)) break;
         mbar_expect_tx(&full[s], STAGE_BYTES);
         uint8_t* a = tiles + s * STAGE_BYTES;
-        tma_load_2d(a, &map_wide, &full[s], (kb0 + kb) * BK, wide0);
+        if (wp) bulk_load_1d(a, wp + (size_t)kb * A_BYTES, &full[s], A_BYTES);
+        else tma_load_2d(a, &map_wide, &full[s], (kb0 + kb) * BK, wide0);
         tma_load_2d(a + A_BYTES, &map_narrow, &full[s], (kb0 + kb) * BK, narrow0);
       }
     }
@@ -262,16 +269,26 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
           float acc[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) acc[j] = red[(j0 + j) * BM + row];
-          for (int sidx = 1; sidx < args.splits; ++sidx) {
-            float v[16];
+          // the other CTAs' partial sums, three CTAs' worth of loads in flight together (one trip
+          // through distributed shared memory for up to four splits), added in split order
+          for (int s0 = 1; s0 < args.splits; s0 += 3) {
+            float v[3][16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              uint32_t remote;
-              asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr + (uint32_t)(((j0 + j) * BM + row) * 4)), "r"(sidx));
-              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[j]) : "r"(remote) : "memory");
+            for (int q = 0; q < 3; ++q) {
+              uint32_t remote = 0;
+              if (s0 + q < args.splits)
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr + (uint32_t)((j0 * BM + row) * 4)), "r"(s0 + q));
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                v[q][j] = 0.f;
+                if (s0 + q < args.splits && narrow0 + j0 + j < ntok)
+                  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[q][j]) : "r"(remote + (uint32_t)(j * BM * 4)) : "memory");
+              }
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] += v[j];
+            for (int q = 0; q < 3; ++q)
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[j] += v[q][j];
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j)
@@ -506,18 +523,18 @@ extern "C" void qv_gemm_bf16_set_prefill_variant(int v) { g_prefill_variant = v;
 // C (bf16 or f32) [M,N] = A (bf16) [M,K] * W (bf16) [N,K]^T.  Returns QV_ERR_UNSUPPORTED for shapes
 // the tensor-core path does not take (the caller then uses the CUDA-core kernel):
 // K not a multiple of 8 elements, or operands whose rows do not start on 16-byte boundaries.
-extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
-                               int c_dt, int* err, int force_splits, int epilogue, void* stream) {
+static int gemm_bf16_entry(void* C, const void* A, const void* W, const void* packed, int M, int N, int K, int lda, int ldw, int ldc,
+                           int c_dt, int* err, int force_splits, int epilogue, void* stream) {
   // epilogue 0: C[M,N] = A W^T.  epilogue 1: W's rows are 16 gate rows / 16 up rows interleaved and
   // C[M,N/2] = silu(gate) * up (bfloat16 out, N a multiple of 32).
   if (M <= 0 || N <= 0) return 0;
   if (epilogue != 0 && (epilogue != 1 || c_dt != QV_DT_BF16 || (N & 31))) return QV_ERR_UNSUPPORTED;
   if (K < 8 || (K & 7) || (lda & 7) || (ldw & 7)) return QV_ERR_UNSUPPORTED;
-  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return QV_ERR_UNSUPPORTED;
+  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)packed & 15)) return QV_ERR_UNSUPPORTED;
   if (c_dt != QV_DT_BF16 && c_dt != QV_DT_F32) return QV_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   GemmArgs args;
-  args.C = C; args.err = err;
+  args.C = C; args.err = err; args.packed = nullptr;
   args.K = K; args.ldc = ldc;
   const int total_kb = (K + BK - 1) / BK;
   CUtensorMap mw, mn;
@@ -536,7 +553,9 @@ extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int
     int per = (total_kb + splits - 1) / splits;
     splits = (total_kb + per - 1) / per;            // no empty split
     args.rows_wide = N; args.rows_narrow = M; args.kblocks_per_split = per; args.splits = splits;
-    if (!make_map(&mw, W, N, K, ldw, BM) || !make_map(&mn, A, M, K, lda, bn)) return QV_ERR_UNSUPPORTED;
+    if (!make_map(&mn, A, M, K, lda, bn)) return QV_ERR_UNSUPPORTED;
+    if (packed) { args.packed = (const uint8_t*)packed; mw = mn; }
+    else if (!W || !make_map(&mw, W, N, K, ldw, BM)) return QV_ERR_UNSUPPORTED;
     dim3 grid(tiles, 1, splits);
 #define SWAP_LAUNCH(BN_, ST_)                                                                     \
   (c_dt == QV_DT_BF16 ? launch<BN_, ST_, true, bf16>(mw, mn, args, grid, st) : launch<BN_, ST_, true, float>(mw, mn, args, grid, st))
@@ -552,6 +571,7 @@ extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int
 #undef SWAP_LAUNCH
   }
   // many tokens: tokens on the 128-row side, 128 weight rows per tile
+  if (!W) return QV_ERR_UNSUPPORTED;
   args.rows_wide = M; args.rows_narrow = N; args.kblocks_per_split = total_kb; args.splits = 1;
   if (g_prefill_variant == 0) {
     // persistent kernel, 128 x 256 tiles, accumulator double-buffered in tensor memory
@@ -567,4 +587,46 @@ extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int
   if (epilogue == 1) return launch<128, 3, false, bf16, true>(mw, mn, args, grid, st);
   if (c_dt == QV_DT_BF16) return launch<128, 3, false, bf16>(mw, mn, args, grid, st);
   return launch<128, 3, false, float>(mw, mn, args, grid, st);
+}
+
+extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
+                               int c_dt, int* err, int force_splits, int epilogue, void* stream) {
+  return gemm_bf16_entry(C, A, W, nullptr, M, N, K, lda, ldw, ldc, c_dt, err, force_splits, epilogue, stream);
+}
+
+// As qv_gemm_bf16_tc for at most 64 tokens, with the weight matrix given as packed tiles
+// (qv_pack_weight_tiles): every CTA then streams its tiles with contiguous 16 KB copies, which an
+// SM takes in ~1.6x faster than tensor tiles of 128-byte rows and HBM serves ~15 % faster.
+extern "C" int qv_gemm_bf16_packed(void* C, const void* A, const void* packed, int M, int N, int K, int lda, int ldc, int c_dt,
+                                   int* err, int force_splits, int epilogue, void* stream) {
+  if (M > 64 || !packed) return QV_ERR_UNSUPPORTED;
+  return gemm_bf16_entry(C, A, nullptr, packed, M, N, K, lda, K, ldc, c_dt, err, force_splits, epilogue, stream);
+}
+
+// ---------------------------------------------------------------- packed weights
+// W [N, K] (row stride ldw) -> tiles of 128 rows x 64 k, tile (t, kb) at byte ((t * kblocks + kb) * 16384),
+// each stored as the shared-memory image the MMA reads (128-byte rows, 16-byte chunk c of row r at
+// chunk c ^ (r % 8)), zero where the matrix ends.
+__global__ void pack_weight_tiles_kernel(uint4* __restrict__ out, const bf16* __restrict__ W, int N, int K, int ldw, int kblocks) {
+  const int kb = blockIdx.x, t = blockIdx.y;
+  const int r = threadIdx.x >> 3, c = threadIdx.x & 7;      // 16 rows x 8 chunks per pass
+  uint4* tile = out + ((size_t)t * kblocks + kb) * (A_TILE_BYTES / 16);
+  for (int rr = r; rr < BM; rr += 16) {
+    const int row = t * BM + rr, k0 = kb * BK + c * 8;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < N && k0 < K) v = *(const uint4*)(W + (size_t)row * ldw + k0);
+    tile[(rr >> 3) * 64 + (rr & 7) * 8 + (c ^ (rr & 7))] = v;
+  }
+}
+
+extern "C" long long qv_packed_weight_bytes(int N, int K) {
+  return (long long)((N + BM - 1) / BM) * ((K + BK - 1) / BK) * A_TILE_BYTES;
+}
+
+extern "C" int qv_pack_weight_tiles(void* out, const void* W, int N, int K, int ldw, void* stream) {
+  if (N <= 0 || K < 8 || (K & 7) || (ldw & 7) || ((uintptr_t)W & 15) || ((uintptr_t)out & 15)) return QV_ERR_UNSUPPORTED;
+  const int tiles = (N + BM - 1) / BM, kblocks = (K + BK - 1) / BK;
+  if (tiles > 65535) return QV_ERR_TOO_LARGE;
+  pack_weight_tiles_kernel<<<dim3(kblocks, tiles), 128, 0, (cudaStream_t)stream>>>((uint4*)out, (const bf16*)W, N, K, ldw, kblocks);
+  return (int)cudaGetLastError();
 }

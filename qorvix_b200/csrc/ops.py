@@ -196,6 +196,35 @@ def gemm_bf16_tc(c, a, w, force_splits: int = 0, swiglu: bool = False) -> bool:
     return True
 
 
+def pack_weight(w: torch.Tensor) -> torch.Tensor:
+    """The bfloat16 matrix w [N, K] as the 16 KB tiles (128 rows x 64 k, in the shared-memory layout of
+    the MMA) that gemm_bf16_packed streams with contiguous copies.  K must be a multiple of 8."""
+    _need_cuda(w)
+    assert w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1
+    N, K = w.shape
+    lib = load_library("gemm_bf16")
+    lib.qv_packed_weight_bytes.restype = c_longlong
+    out = torch.empty(lib.qv_packed_weight_bytes(c_int(N), c_int(K)) // 2, device=w.device, dtype=torch.bfloat16)
+    _check(lib.qv_pack_weight_tiles(_ptr(out), _ptr(w), c_int(N), c_int(K), c_int(w.stride(0)), _stream()), "pack_weight_tiles")
+    return out
+
+
+def gemm_bf16_packed(c, a, packed, N: int, force_splits: int = 0, swiglu: bool = False) -> bool:
+    """As gemm_bf16_tc for at most 64 rows of a, with the weights given by pack_weight."""
+    _need_cuda(c, a, packed)
+    M, K = a.shape
+    assert a.dtype == torch.bfloat16 and packed.dtype == torch.bfloat16 and M <= 64
+    assert c.shape == ((M, N // 2) if swiglu else (M, N)) and a.stride(1) == 1 and c.stride(1) == 1
+    st = _tc_buffers(a.device)
+    rc = load_library("gemm_bf16").qv_gemm_bf16_packed(
+        _ptr(c), _ptr(a), _ptr(packed), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(c.stride(0)),
+        c_int(dt_code(c.dtype)), _ptr(st["err"]), c_int(force_splits), c_int(1 if swiglu else 0), _stream())
+    if rc == -2:
+        return False
+    _check(rc, "gemm_bf16_packed")
+    return True
+
+
 def gemm_bf16_set_prefill_variant(variant: int) -> None:
     """0 (default): more than 64 tokens run on the persistent kernel (128 x 256 tiles, double-buffered
     accumulator); 1: on the one-tile-per-CTA kernel (128 x 128 tiles)."""
@@ -230,23 +259,37 @@ def attention_generic(out, q, cache_layer, tok_pos, tok_seg, block_table, H, Hkv
 
 # ------------------------------------------------------------------ dispatch
 
-def gemm(out, x, w) -> None:
+def packed_weights_enabled() -> bool:
+    """Whether bfloat16 weight matrices also get a packed copy for steps of few tokens
+    (QORVIX_PACKED_WEIGHTS=0 switches it off and halves the weights' memory)."""
+    import os
+    return os.environ.get("QORVIX_PACKED_WEIGHTS", "1") != "0"
+
+
+def gemm(out, x, w, packed=None) -> None:
     """out = x @ w^T with the kernel that fits the dtypes and the shape: bfloat16 operands go to
-    the tensor-core kernel when it takes the shape, everything else to the CUDA-core kernel."""
-    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and gemm_bf16_tc(out, x, w):
-        return
+    the tensor-core kernel when it takes the shape (for at most 64 rows and a packed copy of w, to the
+    one that streams packed tiles), everything else to the CUDA-core kernel."""
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        if packed is not None and x.shape[0] <= 64 and gemm_bf16_packed(out, x, packed, w.shape[0]):
+            return
+        if gemm_bf16_tc(out, x, w):
+            return
     gemm_simt(out, x, w)
 
 
-def gemm_swiglu(out, x, w_interleaved) -> None:
+def gemm_swiglu(out, x, w_interleaved, packed=None) -> None:
     """out[M,f] = silu(x Wg^T) * (x Wu^T) with gate and up rows interleaved in groups of 16 in
     w_interleaved [2f, K]: one tensor-core kernel when it takes the shape, else the product followed
     by the activation kernel."""
-    if (x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
-            and gemm_bf16_tc(out, x, w_interleaved, swiglu=True)):
-        return
+    if x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
+        if (packed is not None and x.shape[0] <= 64
+                and gemm_bf16_packed(out, x, packed, w_interleaved.shape[0], swiglu=True)):
+            return
+        if gemm_bf16_tc(out, x, w_interleaved, swiglu=True):
+            return
     gu = torch.empty((x.shape[0], w_interleaved.shape[0]), device=x.device, dtype=out.dtype)
-    gemm(gu, x, w_interleaved)
+    gemm(gu, x, w_interleaved, packed)
     swiglu(out, gu, interleaved=True)
 
 

@@ -44,6 +44,12 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
 
+// Contiguous bytes (a multiple of 16, both addresses 16-byte aligned) into shared memory.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* src, uint64_t* bar, uint32_t bytes) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
 // Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes, groups of 8
 // rows 1024 bytes apart (SBO); LBO is not used by swizzled K-major layouts; version 1 (sm_100).
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {

@@ -15,6 +15,13 @@ class Linear:
         assert weight.dim() == 2
         self.weight = weight.contiguous()
         self.out_features, self.in_features = weight.shape
+        # Steps of few tokens stream the whole matrix once; they read a second copy of it, stored as
+        # the 16 KB tiles the MMA consumes, which HBM and the SM's copy engine deliver faster than
+        # rows.  Steps of many tokens read the rows.
+        self.packed = None
+        if (self.weight.is_cuda and self.weight.dtype == torch.bfloat16 and self.in_features % 8 == 0
+                and ops.packed_weights_enabled()):
+            self.packed = ops.pack_weight(self.weight)
 
     def forward(self, x: torch.Tensor, out: torch.Tensor = None, out_dtype: torch.dtype = None) -> torch.Tensor:
         M = x.shape[0]
@@ -22,7 +29,7 @@ class Linear:
             out = torch.empty((M, self.out_features), device=x.device, dtype=out_dtype or x.dtype)
         if M == 0:
             return out
-        ops.gemm(out, x, self.weight)
+        ops.gemm(out, x, self.weight, self.packed)
         return out
 
     __call__ = forward
