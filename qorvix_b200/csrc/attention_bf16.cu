@@ -20,6 +20,7 @@
 //            tile are the query heads that share the kv head; the 4 warps take alternate
 //            16-key blocks and merge through shared memory; slices merge in a second kernel.
 #include "attention_mma.cuh"
+#include "tc_common.cuh"
 
 namespace {
 
@@ -374,6 +375,132 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(bf16* __restrict__ out
   }
 }
 
+// The same slice of work with the keys and values brought into shared memory by the copy engine:
+// one thread requests, for every block of 16 keys, the kv head's 16 key rows and 16 value rows of
+// the page (two contiguous copies of 16 * HD * 2 bytes) into a ring of stages; the four consumer
+// warps take alternate blocks from the ring.  Per-thread loads keep too few bytes in flight to
+// pull the cache at HBM speed (a 16-key block cost a warp ~3 us); bulk copies do not go through
+// the load/store unit's miss queue.  Waits are bounded; a wait that gives up records a code in *err.
+#define DEC_STAGES 8
+template <int HD>
+__global__ void __launch_bounds__(160) attn_decode_bulk_kernel(bf16* __restrict__ out, int ld_out, const bf16* __restrict__ q, int ld_q,
+                                                               const bf16* __restrict__ cache, const int* __restrict__ tok_pos,
+                                                               const int* __restrict__ tok_seg, const int* __restrict__ block_table,
+                                                               int max_blocks, int H, int Hkv, int page, int window, float scale_log2,
+                                                               int splits, float* __restrict__ partial, int* err) {
+  extern __shared__ uint8_t dec_smem[];
+  constexpr int KB = 16 * HD * 2;                       // bytes of 16 key rows (and of 16 value rows)
+  constexpr int STAGE = 2 * KB;
+  constexpr int ROW = HD + 2;
+  constexpr int RING = DEC_STAGES * STAGE, SCRATCH = 4 * 16 * ROW * 4;
+  uint8_t* ring = (uint8_t*)(((uintptr_t)dec_smem + 127) & ~(uintptr_t)127);
+  float* sm = (float*)ring;                             // the merge reuses the ring once it is drained
+  uint64_t* full = (uint64_t*)(ring + (RING > SCRATCH ? RING : SCRATCH));
+  uint64_t* empty = full + DEC_STAGES;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < DEC_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  const int G = H / Hkv;
+  const int pos = tok_pos[t];
+  const int* bt = block_table + (size_t)tok_seg[t] * max_blocks;
+  const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int start = first & ~15;
+  const int total = pos + 1 - start;
+  int chunk = (total + splits - 1) / splits;
+  chunk = (chunk + 63) & ~63;
+  const int k_begin = start + split * chunk;
+  int k_stop = k_begin + chunk;                  // exclusive
+  if (k_stop > pos + 1) k_stop = pos + 1;
+  const int nblk = k_stop > k_begin ? (k_stop - k_begin + 15) >> 4 : 0;
+  RowState<HD> st;
+  st.init();
+  if (warp == 4) {
+    if (lane == 0) {
+      const size_t page_elems = (size_t)2 * Hkv * page * HD;
+      const size_t v_off = (size_t)Hkv * page * HD;
+      int pg = k_begin / page, in_pg = k_begin - pg * page;
+      for (int i = 0; i < nblk; ++i) {
+        const int s = i % DEC_STAGES;
+        if (!mbar_wait(&empty[s], ((i / DEC_STAGES) & 1) ^ 1, err, 31)) break;
+        const bf16* kblk = cache + (size_t)bt[pg] * page_elems + ((size_t)kvh * page + in_pg) * HD;
+        mbar_expect_tx(&full[s], STAGE);
+        bulk_load_1d(ring + (size_t)s * STAGE, kblk, &full[s], KB);
+        bulk_load_1d(ring + (size_t)s * STAGE + KB, kblk + v_off, &full[s], KB);
+        in_pg += 16;
+        if (in_pg == page) { in_pg = 0; ++pg; }
+      }
+    }
+  } else {
+    const bf16* qtok = q + (size_t)t * ld_q + (size_t)kvh * G * HD;
+    QFrag<HD> qf;
+    load_q<HD>(qf, g < G ? qtok + (size_t)g * HD : nullptr, g + 8 < G ? qtok + (size_t)(g + 8) * HD : nullptr, tg);
+    const int lo[2] = {first, first};
+    const int hi[2] = {g < G ? pos : -1, g + 8 < G ? pos : -1};
+    for (int i = warp; i < nblk; i += 4) {
+      const int s = i % DEC_STAGES;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(&full[s], (i / DEC_STAGES) & 1, err, 32) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      const bf16* kblk = (const bf16*)(ring + (size_t)s * STAGE);
+      block16<HD, true>(st, qf, kblk, kblk + 16 * HD, k_begin + 16 * i, lo, hi, scale_log2, g, tg);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+      st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    }
+  }
+  __syncthreads();                              // every block is consumed: the ring is free for the merge
+  if (warp < 4) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + 8 * r;
+      if (row >= G) continue;
+      float* dst = sm + ((size_t)warp * 16 + row) * ROW;
+#pragma unroll
+      for (int i = 0; i < Shape<HD>::NT; ++i) {
+        dst[out_dim<HD>(i, 2 * tg)] = st.o[i][2 * r];
+        dst[out_dim<HD>(i, 2 * tg + 1)] = st.o[i][2 * r + 1];
+      }
+      if (tg == 0) { dst[HD] = st.m[r]; dst[HD + 1] = st.l[r]; }
+    }
+  }
+  __syncthreads();
+  // merge the 4 warps in a fixed order (warp 0, 1, 2, 3)
+  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+    const int row = idx / HD, d = idx - row * HD;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, sm[((size_t)w * 16 + row) * ROW + HD]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float* src = sm + ((size_t)w * 16 + row) * ROW;
+      const float f = (src[HD] == -INFINITY) ? 0.f : exp2f(src[HD] - m);
+      acc += src[d] * f;
+      l += src[HD + 1] * f;
+    }
+    const int h = kvh * G + row;
+    if (splits == 1) {
+      out[(size_t)t * ld_out + (size_t)h * HD + d] = __float2bfloat16_rn(acc / l);
+    } else {
+      float* dst = partial + (((size_t)t * H + h) * splits + split) * ROW;
+      dst[d] = acc;
+      if (d == 0) { dst[HD] = m; dst[HD + 1] = l; }
+    }
+  }
+}
+
 // merges the slices of one (token, head) in slice order
 __global__ void attn_combine_kernel(bf16* __restrict__ out, int ld_out, const float* __restrict__ partial, int H, int hd, int splits) {
   pdl_wait();
@@ -404,20 +531,38 @@ int launch_prefill(bf16* out, int ld_out, const bf16* q, int ld_q, const bf16* c
                    max_blocks, H, Hkv, page, window, scale_log2);
 }
 
+// 0: keys and values through the copy engine into shared memory (needs the error word); 1: per-thread loads
+int g_decode_variant = 0;
+int* g_decode_err = nullptr;
+
 template <int HD>
 int launch_decode(bf16* out, int ld_out, const bf16* q, int ld_q, const bf16* cache, const int* tok_pos, const int* tok_seg,
                   const int* bt, int max_blocks, int T, int H, int Hkv, int page, int window, float scale_log2, int splits,
                   float* partial, cudaStream_t st) {
-  const size_t smem = (size_t)4 * 16 * (HD + 2) * sizeof(float);
-  static bool configured = false;
-  if (!configured && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
   dim3 grid(splits, Hkv, T);
-  int rc = qv_launch(attn_decode_kernel<HD>, grid, dim3(128), smem, st, out, ld_out, q, ld_q, cache, tok_pos, tok_seg, bt,
-                     max_blocks, H, Hkv, page, window, scale_log2, splits, partial);
+  int rc;
+  if (g_decode_variant == 0 && g_decode_err != nullptr) {
+    constexpr int ring = DEC_STAGES * 2 * 16 * HD * 2, scratch = 4 * 16 * (HD + 2) * 4;
+    const size_t smem = (size_t)(ring > scratch ? ring : scratch) + 2 * DEC_STAGES * 8 + 128;
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_bulk_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    rc = qv_launch(attn_decode_bulk_kernel<HD>, grid, dim3(160), smem, st, out, ld_out, q, ld_q, cache, tok_pos, tok_seg, bt,
+                   max_blocks, H, Hkv, page, window, scale_log2, splits, partial, g_decode_err);
+  } else {
+    const size_t smem = (size_t)4 * 16 * (HD + 2) * sizeof(float);
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    rc = qv_launch(attn_decode_kernel<HD>, grid, dim3(128), smem, st, out, ld_out, q, ld_q, cache, tok_pos, tok_seg, bt,
+                   max_blocks, H, Hkv, page, window, scale_log2, splits, partial);
+  }
   if (rc || splits == 1) return rc;
   return qv_launch(attn_combine_kernel, dim3(H, T), dim3(HD < 128 ? 64 : 128), 0, st, out, ld_out, (const float*)partial, H,
                    (int)HD, splits);
@@ -426,6 +571,11 @@ int launch_decode(bf16* out, int ld_out, const bf16* q, int ld_q, const bf16* ca
 }  // namespace
 
 #define FOR_HEAD_DIMS(X) X(16) X(32) X(48) X(64) X(80) X(96) X(112) X(128)
+
+// Which decode kernel runs (0: shared-memory ring filled by bulk copies, the default once the error
+// word is set; 1: per-thread loads), and the device word that bounded waits report into.
+extern "C" void qv_attn_set_decode_variant(int v) { g_decode_variant = v; }
+extern "C" void qv_attn_set_error_word(int* err) { g_decode_err = err; }
 
 // Floats of workspace that qv_attn_decode_bf16 needs for `splits` > 1.
 extern "C" long long qv_attn_decode_workspace_floats(int T, int H, int hd, int splits) {

@@ -333,11 +333,26 @@ def attention_prefill_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table
     return True
 
 
+_decode_variant_forced = None
+
+
+def decode_variant(T: int, Hkv: int) -> int:
+    """Which decode kernel a step of T tokens takes: 0 reads keys and values through a ring in shared
+    memory that bulk copies fill (the faster one when many (token, kv head) pairs stream long key
+    ranges), 1 through per-thread loads (less set-up; better when there are few pairs)."""
+    if _decode_variant_forced is not None:
+        return _decode_variant_forced
+    return 0 if T * Hkv >= 32 else 1
+
+
 def decode_splits(T: int, Hkv: int, max_ctx: int) -> int:
-    """How many slices of the keys each (token, kv head) is cut into, so that about three CTAs per
-    SM are busy; a function of the step's shape only (a captured step keeps it)."""
-    want = -(-3 * 148 // max(1, T * Hkv))
-    return max(1, min(16, want, -(-max_ctx // 64)))
+    """How many slices of the keys each (token, kv head) is cut into: about three CTAs per SM for the
+    per-thread-load kernel, two (each with 64 KB of keys and values in flight) and at least 256 keys
+    a slice for the bulk-copy kernel; a function of the step's shape only (a captured step keeps it)."""
+    pairs = max(1, T * Hkv)
+    if decode_variant(T, Hkv) == 0:
+        return max(1, min(16, (2 * 148) // pairs, max_ctx // 256))
+    return max(1, min(16, -(-3 * 148 // pairs), -(-max_ctx // 64)))
 
 
 def attention_decode_bf16(out, q, cache_layer, tok_pos, tok_seg, block_table, H, Hkv, hd, page, window, scale,
@@ -352,7 +367,13 @@ def attention_decode_bf16(out, q, cache_layer, tok_pos, tok_seg, block_table, H,
     partial = None
     if splits > 1:
         partial = torch.empty(T * H * splits * (hd + 2), dtype=torch.float32, device=q.device)
-    rc = load_library("attention_bf16").qv_attn_decode_bf16(
+    lib = load_library("attention_bf16")
+    lib.qv_attn_set_decode_variant(c_int(decode_variant(T, Hkv)))
+    if not getattr(lib, "_qv_err_set", False):
+        # the word that the kernel's bounded waits report into (see check_kernel_errors)
+        lib.qv_attn_set_error_word(_ptr(_tc_buffers(q.device)["err"]))
+        lib._qv_err_set = True
+    rc = lib.qv_attn_decode_bf16(
         _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(cache_layer), _ptr(tok_pos), _ptr(tok_seg),
         _ptr(block_table), c_int(block_table.shape[-1]), c_int(T), c_int(H), c_int(Hkv), c_int(hd), c_int(page),
         c_int(window), c_float(scale), c_int(splits), _ptr(partial), _stream())
@@ -362,6 +383,13 @@ def attention_decode_bf16(out, q, cache_layer, tok_pos, tok_seg, block_table, H,
     if splits > 1:
         add_launches(1)                              # the merge of the slices
     return True
+
+
+def attention_set_decode_variant(variant) -> None:
+    """Forces the decode kernel (0: bulk copies into shared memory, 1: per-thread loads) or, with
+    None, gives the choice back to decode_variant().  For comparison and tests."""
+    global _decode_variant_forced
+    _decode_variant_forced = variant
 
 
 def _attention_portions_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, Hkv, hd, page,

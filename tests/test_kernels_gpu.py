@@ -292,13 +292,19 @@ def test_attention_prefill_bf16(H, Hkv, hd, page, window, variant):
     assert torch.allclose(out.double().cpu(), d["ref"], rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("variant", [0, 1])        # 0: bulk copies into a shared-memory ring; 1: per-thread loads
 @pytest.mark.parametrize("splits", [1, 3, 16])
 @pytest.mark.parametrize("H,Hkv,hd,page,window", ATT_SHAPES)
-def test_attention_decode_bf16(H, Hkv, hd, page, window, splits):
+def test_attention_decode_bf16(H, Hkv, hd, page, window, splits, variant):
     d = _segments([(1, 70), (1, 1), (1, 333), (1, 16), (1, 17), (1, 1024), (1, 64)], H, Hkv, hd, page, seed=62, window=window)
     out = torch.full_like(d["q"], float("nan"))
-    assert ops.attention_decode_bf16(out, d["q"], d["cache"], d["pos"], d["seg"], d["bt"], H, Hkv, hd, page, window,
-                                     1.0 / math.sqrt(hd), splits)
+    ops.attention_set_decode_variant(variant)
+    try:
+        assert ops.attention_decode_bf16(out, d["q"], d["cache"], d["pos"], d["seg"], d["bt"], H, Hkv, hd, page, window,
+                                         1.0 / math.sqrt(hd), splits)
+        ops.check_kernel_errors()
+    finally:
+        ops.attention_set_decode_variant(None)
     assert torch.allclose(out.double().cpu(), d["ref"], rtol=2e-2, atol=2e-2)
 
 
@@ -311,10 +317,14 @@ def test_attention_bf16_finds_a_far_key_and_respects_page_edges():
         q = d["q"].view(1, H, hd)
         d["cache"][pages[far // page], 0, 0, far % page] = (q[0, 1].float() * 6.0).to(torch.bfloat16)   # kv head 0 serves heads 0..3
         d["cache"][pages[far // page], 1, 0, far % page] = 50.0
-        for fn in ("decode", "prefill"):
+        for fn in ("decode", "decode_bulk", "prefill"):
             out = torch.zeros_like(d["q"])
-            if fn == "decode":
-                assert ops.attention_decode_bf16(out, d["q"], d["cache"], d["pos"], d["seg"], d["bt"], H, Hkv, hd, page, 0, 1 / math.sqrt(hd), 4)
+            if fn.startswith("decode"):
+                ops.attention_set_decode_variant(0 if fn == "decode_bulk" else 1)
+                try:
+                    assert ops.attention_decode_bf16(out, d["q"], d["cache"], d["pos"], d["seg"], d["bt"], H, Hkv, hd, page, 0, 1 / math.sqrt(hd), 4)
+                finally:
+                    ops.attention_set_decode_variant(None)
             else:
                 assert ops.attention_prefill_bf16(out, d["q"], d["cache"], d["qstart"], d["pos0"], d["bt"], 1, 1, H, Hkv, hd, page, 0, 1 / math.sqrt(hd))
             assert float(out.view(H, hd)[1].float().min()) > 49.0, f"{fn}: key {far} was not found"
