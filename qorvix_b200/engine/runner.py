@@ -138,12 +138,18 @@ class ModelRunner:
         tables = {g: [self.cache.block_table(e.req_id, g) for e in entries] for g in self.cache.paged_groups()}
         return self._builder.build(segs, tables, self.cache.scratch_page)
 
-    def step(self, entries: Sequence[StepEntry], end: Iterable[Hashable] = ()) -> Optional[torch.Tensor]:
+    step_views = True          # step() takes copy_logits and sets last_greedy_ids
+
+    def step(self, entries: Sequence[StepEntry], end: Iterable[Hashable] = (), copy_logits: bool = True) -> Optional[torch.Tensor]:
         """Runs one batch.  Returns float32 logits [number of wanted places, vocab] on the device,
         ordered by entry and then by `want`, or None when nothing is wanted.  Requests in `end`
-        are finished after this step and what they hold is given back."""
+        are finished after this step and what they hold is given back.  With copy_logits=False the
+        result may be a view of a buffer that the next step overwrites (for a caller that consumes it
+        at once).  After a captured decode step whose every row is wanted, last_greedy_ids holds
+        the argmax of each row (computed inside the captured step), else it is None."""
         entries = list(entries)
         logits = None
+        self.last_greedy_ids = None
         if entries and self.use_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries):
             # decode-only: replay the captured step
             self.prepare(entries, build=False)
@@ -152,7 +158,10 @@ class ModelRunner:
             rows = [i for i, e in enumerate(entries) if len(e.want)]
             if rows:
                 if len(rows) == len(entries):
-                    logits = graph.logits[: len(rows)].clone()
+                    logits = graph.logits[: len(rows)]
+                    if copy_logits:
+                        logits = logits.clone()
+                    self.last_greedy_ids = graph.next_ids[: len(rows)]
                 else:
                     logits = graph.logits[torch.tensor(rows, device=self.device)]
             for e in entries:

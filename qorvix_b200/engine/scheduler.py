@@ -240,7 +240,8 @@ class Scheduler:
                 samplers.append(r)
         if not entries:
             return finished
-        logits = self.runner.step(entries)
+        views = getattr(self.runner, "step_views", False)      # the logits are consumed before the next step
+        logits = self.runner.step(entries, copy_logits=False) if views else self.runner.step(entries)
         self.stats["steps"] += 1
         self.stats["tokens"] += plan.num_tokens
         for rid in plan.decode:
@@ -250,7 +251,11 @@ class Scheduler:
         for rid, n in plan.prefill:
             self._requests[rid].computed += n
         if samplers:
-            ids = self.sampler.sample(logits, [r.sampler for r in samplers], [r.history() for r in samplers])
+            greedy_ids = getattr(self.runner, "last_greedy_ids", None) if views else None
+            if greedy_ids is not None and all(r.sampler.params.greedy and not r.sampler.params.has_penalties for r in samplers):
+                ids = greedy_ids                              # the captured step has taken the argmax already
+            else:
+                ids = self.sampler.sample(logits, [r.sampler for r in samplers], [r.history() for r in samplers])
             ids = ids.tolist() if hasattr(ids, "tolist") else list(ids)
             for r, tok in zip(samplers, ids):
                 self._accept(r, int(tok))
