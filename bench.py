@@ -223,7 +223,7 @@ def main() -> int:
     sp = SamplingParams.greedy_params(max_new_tokens=W + K + 8, ignore_eos=True)
     for _ in range(B):
         sched.submit(prompt(ctx - 1), sp)
-    while sched.waiting() or any(sched._requests[r].pending is None for r in sched._running):
+    while not sched.decoding():
         sched.step()                                              # prefill until every request decodes
     for _ in range(W):
         sched.step()
@@ -235,7 +235,9 @@ def main() -> int:
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     h2d = (runner.h2d_bytes - h2d0) / K
+    ahead = sched.stats.get("ahead_steps", 0)
     sched.run_to_completion()
+    print(f"[bench] end to end: {ahead} of {sched.stats['steps']} rounds were launched ahead of the host", file=sys.stderr)
     e2e = {"value": B * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B,
            "ms_per_step": e2e_s / K * 1e3}
 

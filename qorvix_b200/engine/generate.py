@@ -21,13 +21,13 @@ from .scheduler import RequestResult, Scheduler, SchedulerConfig
 class LLM:
     def __init__(self, model=None, *, config=None, tensors=None, dtype="bfloat16", max_tokens: int = 8192,
                  page_size: int = 16, max_concurrent: int = 8, max_batch_tokens: int = 2048,
-                 max_chunk: int = 0, max_model_len: Optional[int] = None, device="cuda"):
+                 max_chunk: int = 0, max_model_len: Optional[int] = None, device="cuda", lookahead: bool = True):
         self.runner = ModelRunner(model, config=config, tensors=tensors, dtype=dtype, max_tokens=max_tokens,
                                   page_size=page_size, max_requests=max_concurrent,
                                   max_model_len=max_model_len, device=device)
         self.sampler = Sampler(self.runner.device)
         self.scheduler_config = SchedulerConfig(max_concurrent=max_concurrent, max_batch_tokens=max_batch_tokens,
-                                                max_chunk=max_chunk)
+                                                max_chunk=max_chunk, lookahead=lookahead)
         eos = getattr(self.runner.config, "eos_token_ids", ())
         self.eos_token_ids = tuple(eos)
         self.last_stats = {}

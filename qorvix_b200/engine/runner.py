@@ -140,13 +140,17 @@ class ModelRunner:
 
     step_views = True          # step() takes copy_logits and sets last_greedy_ids
 
-    def step(self, entries: Sequence[StepEntry], end: Iterable[Hashable] = (), copy_logits: bool = True) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], end: Iterable[Hashable] = (), copy_logits: bool = True,
+             device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs one batch.  Returns float32 logits [number of wanted places, vocab] on the device,
         ordered by entry and then by `want`, or None when nothing is wanted.  Requests in `end`
         are finished after this step and what they hold is given back.  With copy_logits=False the
         result may be a view of a buffer that the next step overwrites (for a caller that consumes it
         at once).  After a captured decode step whose every row is wanted, last_greedy_ids holds
-        the argmax of each row (computed inside the captured step), else it is None."""
+        the argmax of each row (computed inside the captured step), else it is None.
+        device_tokens: int32 ids on the device, one per entry, to feed instead of the entries' own
+        (placeholder) tokens; only for a decode-only step that runs as a captured graph, which lets
+        a caller launch a step before it has read the ids the step before produced."""
         entries = list(entries)
         logits = None
         self.last_greedy_ids = None
@@ -154,7 +158,11 @@ class ModelRunner:
             # decode-only: replay the captured step
             self.prepare(entries, build=False)
             graph = self.decode_graph(len(entries))
-            graph.run([e.req_id for e in entries], [int(e.tokens[0]) for e in entries])
+            if device_tokens is not None:
+                graph.dbuf[0: len(entries)].copy_(device_tokens[: len(entries)])
+                graph.run([e.req_id for e in entries], None)
+            else:
+                graph.run([e.req_id for e in entries], [int(e.tokens[0]) for e in entries])
             rows = [i for i, e in enumerate(entries) if len(e.want)]
             if rows:
                 if len(rows) == len(entries):
@@ -169,6 +177,8 @@ class ModelRunner:
             self.steps_run += 1
             self.tokens_run += len(entries)
         elif entries:
+            if device_tokens is not None:
+                raise ValueError("device_tokens need a decode-only step that runs as a captured graph")
             ctx = self.prepare(entries)
             logits = self.model.forward(ctx, self.cache)
             for e in entries:

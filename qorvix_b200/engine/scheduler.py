@@ -33,6 +33,7 @@ class SchedulerConfig:
     max_concurrent: int = 8          # requests running at once (reference default, scheduler.hpp:47)
     max_batch_tokens: int = 2048     # token budget of one step
     max_chunk: int = 0               # longest prompt portion; 0: the budget alone limits it
+    lookahead: bool = False          # while all requests decode, launch a step before the last one's ids are read
 
 
 @dataclass
@@ -84,6 +85,16 @@ class StepPlan:
         return len(self.decode) + sum(n for _, n in self.prefill)
 
 
+@dataclass
+class _InFlight:
+    """A decode step that has been launched and whose sampled ids are still on the device."""
+    requests: List[_Request]                 # one per row
+    ids: object                              # device tensor [rows] of sampled ids (the next launch feeds them)
+    host_ids: object = None                  # their copy to pinned host memory, requested right after the step ...
+    copied: object = None                    # ... and the event that says it has arrived
+    dead: set = field(default_factory=set)   # rows whose request ended in the step before: their id is dropped
+
+
 class Scheduler:
     def __init__(self, runner, sampler, config: SchedulerConfig = None, eos_token_ids: Sequence[int] = ()):
         """runner: has .cache (CacheManager), .step(entries, end), .release(id), .max_model_len.
@@ -99,7 +110,9 @@ class Scheduler:
         self._requests: Dict[int, _Request] = {}
         self._running: List[int] = []              # in admission order
         self._early: List[RequestResult] = []
-        self.stats = {"steps": 0, "tokens": 0, "preemptions": 0, "admitted": 0}
+        self._ahead: Optional[_InFlight] = None      # lookahead: the decode step whose ids are not read yet
+        self._pinned: list = []                      # host buffers the ids of launched steps are copied to
+        self.stats = {"steps": 0, "tokens": 0, "preemptions": 0, "admitted": 0, "ahead_steps": 0}
 
     # ------------------------------------------------------------------ submitting
     def submit(self, prompt: Sequence[int], params: SamplingParams = None, priority: int = 0,
@@ -119,13 +132,18 @@ class Scheduler:
         return rid
 
     def idle(self) -> bool:
-        return not self._waiting and not self._running and not self._early
+        return not self._waiting and not self._running and not self._early and self._ahead is None
 
     def waiting(self) -> int:
         return len(self._waiting)
 
     def active(self) -> int:
         return len(self._running)
+
+    def decoding(self) -> bool:
+        """Nothing waits and every running request has its whole prompt in the cache."""
+        return not self._waiting and bool(self._running) and all(
+            self._requests[rid].computed >= len(self._requests[rid].prompt) for rid in self._running)
 
     # ------------------------------------------------------------------ deciding
     def plan_step(self) -> StepPlan:
@@ -220,8 +238,103 @@ class Scheduler:
 
     # ------------------------------------------------------------------ running
     def step(self) -> List[RequestResult]:
-        """One round: plan, run the batch, sample, finish and free.  Returns the requests that
-        finished in this round."""
+        """One round.  Returns the requests that finished in it."""
+        if self.config.lookahead and getattr(self.runner, "step_views", False):
+            return self._step_lookahead()
+        return self._step_sync()
+
+    # Lookahead: while every running request decodes and nothing waits, the next step is launched
+    # before the ids of the one in flight are read, so that the device never waits for the host's
+    # bookkeeping.  The tokens it feeds are the in-flight step's ids, taken on the device.  A request
+    # that turns out to have ended in the step in flight (end of sequence, stop token) has then run
+    # one token too far: that token is dropped, and its pages go back at once (the step that still
+    # writes to them is ahead of any later use in stream order).  Limits that the host can foresee
+    # (max_new_tokens, the sequence limit, pages, new arrivals) end the lookahead before they bite,
+    # and the rounds in between run one at a time as without it.
+    def _steady(self, reqs: List[_Request]) -> bool:
+        if self._waiting or not reqs or len(reqs) > getattr(self.runner, "max_graph_batch", 0):
+            return False
+        if not getattr(self.runner, "use_graphs", False):
+            return False
+        for r in reqs:
+            p = r.params
+            if p.has_penalties or len(r.generated) + 1 >= p.max_new_tokens:
+                return False
+            if r.n_prompt + len(r.generated) + 1 >= self.runner.max_model_len:
+                return False
+        ids = [r.id for r in reqs]
+        return self.runner.cache.one_more_token_fits(ids) == len(ids)
+
+    def _launch(self, reqs: List[_Request], device_tokens=None) -> _InFlight:
+        entries = [StepEntry(r.id, [0 if device_tokens is not None else r.pending], [0]) for r in reqs]
+        logits = self.runner.step(entries, copy_logits=False, device_tokens=device_tokens)
+        self.stats["steps"] += 1
+        self.stats["tokens"] += len(reqs)
+        for r in reqs:
+            r.computed += 1
+            r.pending = None
+        greedy_ids = self.runner.last_greedy_ids
+        if greedy_ids is not None and all(r.params.greedy for r in reqs):
+            ids = greedy_ids.clone()                       # the next launch overwrites the step's own buffer
+        else:
+            ids = self.sampler.sample(logits, [r.sampler for r in reqs], [r.history() for r in reqs])
+        t = _InFlight(requests=list(reqs), ids=ids)
+        # The copy to the host is queued now, ahead of the next launch: queued after it, it would
+        # wait for that whole step, and reading the ids would stall the host for a step.
+        if hasattr(ids, "is_cuda") and ids.is_cuda:
+            import torch
+            if not self._pinned:
+                self._pinned = [torch.empty(max(64, self.config.max_concurrent), dtype=torch.int32, pin_memory=True) for _ in range(3)]
+            buf = self._pinned[self.stats["steps"] % 3][: len(reqs)]
+            buf.copy_(ids, non_blocking=True)
+            t.host_ids, t.copied = buf, torch.cuda.Event()
+            t.copied.record()
+        return t
+
+    def _complete(self, t: _InFlight, fed: bool) -> List[RequestResult]:
+        """Reads the ids of a launched step.  fed: the step after it is launched already and feeds
+        these ids itself; a request that goes on then has nothing pending on the host."""
+        finished = []
+        if t.copied is not None:
+            t.copied.synchronize()
+            toks = t.host_ids.tolist()
+        else:
+            toks = t.ids.tolist()
+        for r, tok in zip(t.requests, toks):
+            if r.id in t.dead:
+                continue
+            self._accept(r, int(tok))
+            if r.state == DONE:
+                self._running.remove(r.id)
+                self.runner.release(r.id)
+                finished.append(self._result(self._requests.pop(r.id)))
+            elif fed:
+                r.pending = None
+        return finished
+
+    def _step_lookahead(self) -> List[RequestResult]:
+        t = self._ahead
+        if t is None:
+            reqs = [self._requests[rid] for rid in self._running]
+            if not self._steady(reqs) or any(r.pending is None for r in reqs):
+                return self._step_sync()
+            finished, self._early = self._early, []
+            self._ahead = self._launch(reqs)               # left in flight; its ids are read in the next round
+            return finished
+        finished, self._early = self._early, []
+        live = [r for r in t.requests if r.id not in t.dead]
+        nxt = None
+        if not t.dead and [r.id for r in live] == self._running and self._steady(live):
+            nxt = self._launch(live, device_tokens=t.ids)
+            self.stats["ahead_steps"] += 1
+        finished += self._complete(t, fed=nxt is not None)
+        if nxt is not None:
+            nxt.dead = {r.id for r in nxt.requests if r.id not in self._requests}
+        self._ahead = nxt
+        return finished
+
+    def _step_sync(self) -> List[RequestResult]:
+        """One round: plan, run the batch, sample, finish and free."""
         finished: List[RequestResult] = self._early
         self._early = []
         plan = self.plan_step()

@@ -134,3 +134,30 @@ def test_command_line_generate_and_info(model_a):
     assert "6 prompt tokens, 5 generated" in p.stdout
     q = subprocess.run([sys.executable, str(ROOT / "bin" / "qorvix"), "model-info", str(d)], capture_output=True, text=True, timeout=120)
     assert json.loads(q.stdout)["hidden_size"] == 64
+
+
+def test_lookahead_gives_the_same_tokens_as_one_step_at_a_time():
+    """With lookahead the scheduler launches a decode step before it has read the ids of the one in
+    flight; requests that end on a stop token, on max_new_tokens or on the sequence limit at different
+    times, greedy and sampled, must come out token for token as without it."""
+    cfg = TINY["B"]
+    d = make_model_dir(cfg, seed=91)
+    prompts = [random_tokens(cfg.vocab_size, n, 200 + n) for n in (5, 23, 40, 64, 9, 31)]
+    params = [SamplingParams.greedy_params(max_new_tokens=60),
+              SamplingParams.greedy_params(max_new_tokens=17),
+              SamplingParams(temperature=0.9, top_k=20, top_p=0.9, seed=4, max_new_tokens=45, repetition_penalty=1.0),
+              SamplingParams(temperature=1.3, seed=5, max_new_tokens=33, repetition_penalty=1.0,
+                             stop_token_ids=tuple(range(0, cfg.vocab_size, 7))),
+              SamplingParams.greedy_params(max_new_tokens=80, stop_token_ids=tuple(range(3, cfg.vocab_size, 11))),
+              SamplingParams(temperature=0.7, min_p=0.05, seed=6, max_new_tokens=70, repetition_penalty=1.0)]
+    out = {}
+    for look in (False, True):
+        llm = LLM(d, dtype="bfloat16", max_tokens=2048, max_concurrent=4, lookahead=look, max_model_len=120)
+        res = llm.generate(prompts, params)
+        out[look] = [(r.tokens, r.finish_reason) for r in res]
+        llm.runner.cache.check_invariants()
+        assert llm.runner.cache.free_pages() == llm.runner.cache.num_pages
+        if look:
+            assert llm.last_stats["ahead_steps"] > 10, "the lookahead path did run"
+    assert out[True] == out[False]
+    assert {r for _, r in out[True]} >= {"max_new_tokens", "stop"}

@@ -172,3 +172,48 @@ def test_streaming_callback_sees_every_token_in_order():
     a = s.submit([4], greedy(4), on_token=lambda rid, tok: seen.append((rid, tok)))
     s.run_to_completion()
     assert seen == [(a, t) for t in expect([4], 4)]
+
+
+class LookaheadRunner(FakeRunner):
+    """A fake runner that can be fed the ids of the step before as a tensor, like the real one."""
+    step_views = True
+    use_graphs = True
+    max_graph_batch = 64
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.last_greedy_ids = None
+        self.fed_from_device = 0
+
+    def step(self, entries, end=(), copy_logits=True, device_tokens=None):
+        if device_tokens is not None:
+            self.fed_from_device += 1
+            fed = [int(t) for t in device_tokens[: len(entries)]]
+            entries = [type(e)(e.req_id, [fed[i]], e.want) for i, e in enumerate(entries)]
+        logits = super().step(entries, end)
+        decode_only = all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries)
+        self.last_greedy_ids = logits.argmax(-1).to(torch.int32) if (logits is not None and decode_only) else None
+        return logits
+
+
+@pytest.mark.parametrize("eos", [(), (9, 23, 31)])
+def test_lookahead_gives_the_same_results_as_one_round_at_a_time(eos):
+    """Requests that end by length, by a stop token and by end of sequence at different times:
+    launching a round before the ids of the one before are read changes nothing in what comes out,
+    gives every page back, and is what runs while all requests decode."""
+    prompts = [[1, 2, 3], [7], [20, 21, 22, 23, 24, 25], [40, 41], [5] * 30]
+    params = [greedy(12), greedy(30), greedy(25, stop_token_ids=(45,)), greedy(3), greedy(40)]
+    results = {}
+    for look in (False, True):
+        r = LookaheadRunner(tokens=512, max_requests=4)
+        s = Scheduler(r, ArgmaxSampler(), SchedulerConfig(max_concurrent=4, lookahead=look), eos_token_ids=eos)
+        ids = [s.submit(p, sp) for p, sp in zip(prompts, params)]
+        got = {x.id: x for x in s.run_to_completion()}
+        results[look] = [(got[i].tokens, got[i].finish_reason, got[i].hit_eos) for i in ids]
+        r.cache.check_invariants()
+        assert r.cache.free_pages() == r.cache.num_pages and r.cache.free_slots() == 4
+        if look:
+            assert r.fed_from_device > (10 if not eos else 0) and s.stats["ahead_steps"] == r.fed_from_device
+        else:
+            assert r.fed_from_device == 0
+    assert results[True] == results[False]
