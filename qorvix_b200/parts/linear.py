@@ -21,7 +21,10 @@ class Linear:
         self.packed = None
         if (self.weight.is_cuda and self.weight.dtype == torch.bfloat16 and self.in_features % 8 == 0
                 and ops.packed_weights_enabled()):
-            self.packed = ops.pack_weight(self.weight)
+            try:
+                self.packed = ops.pack_weight(self.weight)
+            except torch.cuda.OutOfMemoryError:
+                self.packed = None          # no room for the second copy: steps of few tokens read the rows
 
     def forward(self, x: torch.Tensor, out: torch.Tensor = None, out_dtype: torch.dtype = None) -> torch.Tensor:
         M = x.shape[0]
