@@ -295,7 +295,7 @@ int launch_prefill_tile(bf16* out, int ld_out, const bf16* q, int ld_q, const bf
 
 // ---------------------------------------------------------------- decode
 // partial results of a slice: [token][head][slice][HD + 2] floats (out unnormalised, then m, l)
-template <int HD>
+template <int HD, int ROWS>
 __global__ void __launch_bounds__(128) attn_decode_kernel(bf16* __restrict__ out, int ld_out, const bf16* __restrict__ q, int ld_q,
                                                           const bf16* __restrict__ cache, const int* __restrict__ tok_pos,
                                                           const int* __restrict__ tok_seg, const int* __restrict__ block_table,
@@ -318,27 +318,27 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(bf16* __restrict__ out
   int k_stop = k_begin + chunk;                  // exclusive
   if (k_stop > pos + 1) k_stop = pos + 1;
   const bf16* qtok = q + (size_t)t * ld_q + (size_t)kvh * G * HD;
-  QFrag<HD> qf;
-  load_q<HD>(qf, g < G ? qtok + (size_t)g * HD : nullptr, g + 8 < G ? qtok + (size_t)(g + 8) * HD : nullptr, tg);
+  QFrag<HD, ROWS> qf;
+  load_q<HD, ROWS>(qf, g < G ? qtok + (size_t)g * HD : nullptr, g + 8 < G ? qtok + (size_t)(g + 8) * HD : nullptr, tg);
   const int lo[2] = {first, first};
   const int hi[2] = {g < G ? pos : -1, g + 8 < G ? pos : -1};
-  RowState<HD> st;
+  RowState<HD, ROWS> st;
   st.init();
   const size_t page_elems = (size_t)2 * Hkv * page * HD;
   const size_t v_off = (size_t)Hkv * page * HD;
   for (int base = k_begin + 16 * warp; base < k_stop; base += 64) {
     const bf16* kblk = cache + (size_t)bt[base / page] * page_elems + ((size_t)kvh * page + (base % page)) * HD;
-    block16<HD, true>(st, qf, kblk, kblk + v_off, base, lo, hi, scale_log2, g, tg);
+    block16<HD, true, ROWS>(st, qf, kblk, kblk + v_off, base, lo, hi, scale_log2, g, tg);
   }
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
+  for (int r = 0; r < ROWS; ++r) {
     st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
     st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
   }
   // each warp leaves its rows in shared memory
   constexpr int ROW = HD + 2;
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
+  for (int r = 0; r < ROWS; ++r) {
     const int row = g + 8 * r;
     if (row >= G) continue;
     float* dst = sm + ((size_t)warp * 16 + row) * ROW;
@@ -381,9 +381,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(bf16* __restrict__ out
 // warps take alternate blocks from the ring.  Per-thread loads keep too few bytes in flight to
 // pull the cache at HBM speed (a 16-key block cost a warp ~3 us); bulk copies do not go through
 // the load/store unit's miss queue.  Waits are bounded; a wait that gives up records a code in *err.
+// ROWS = 1 when at most 8 query heads share a kv head (the lower half of the MMA tile); NW consumer warps.
 #define DEC_STAGES 8
-template <int HD>
-__global__ void __launch_bounds__(160) attn_decode_bulk_kernel(bf16* __restrict__ out, int ld_out, const bf16* __restrict__ q, int ld_q,
+template <int HD, int ROWS, int NW>
+__global__ void __launch_bounds__(32 * (NW + 1)) attn_decode_bulk_kernel(bf16* __restrict__ out, int ld_out, const bf16* __restrict__ q, int ld_q,
                                                                const bf16* __restrict__ cache, const int* __restrict__ tok_pos,
                                                                const int* __restrict__ tok_seg, const int* __restrict__ block_table,
                                                                int max_blocks, int H, int Hkv, int page, int window, float scale_log2,
@@ -392,7 +393,7 @@ __global__ void __launch_bounds__(160) attn_decode_bulk_kernel(bf16* __restrict_
   constexpr int KB = 16 * HD * 2;                       // bytes of 16 key rows (and of 16 value rows)
   constexpr int STAGE = 2 * KB;
   constexpr int ROW = HD + 2;
-  constexpr int RING = DEC_STAGES * STAGE, SCRATCH = 4 * 16 * ROW * 4;
+  constexpr int RING = DEC_STAGES * STAGE, SCRATCH = NW * 8 * ROWS * ROW * 4;
   uint8_t* ring = (uint8_t*)(((uintptr_t)dec_smem + 127) & ~(uintptr_t)127);
   float* sm = (float*)ring;                             // the merge reuses the ring once it is drained
   uint64_t* full = (uint64_t*)(ring + (RING > SCRATCH ? RING : SCRATCH));
@@ -419,9 +420,9 @@ __global__ void __launch_bounds__(160) attn_decode_bulk_kernel(bf16* __restrict_
   int k_stop = k_begin + chunk;                  // exclusive
   if (k_stop > pos + 1) k_stop = pos + 1;
   const int nblk = k_stop > k_begin ? (k_stop - k_begin + 15) >> 4 : 0;
-  RowState<HD> st;
+  RowState<HD, ROWS> st;
   st.init();
-  if (warp == 4) {
+  if (warp == NW) {
     if (lane == 0) {
       const size_t page_elems = (size_t)2 * Hkv * page * HD;
       const size_t v_off = (size_t)Hkv * page * HD;
@@ -439,34 +440,34 @@ __global__ void __launch_bounds__(160) attn_decode_bulk_kernel(bf16* __restrict_
     }
   } else {
     const bf16* qtok = q + (size_t)t * ld_q + (size_t)kvh * G * HD;
-    QFrag<HD> qf;
-    load_q<HD>(qf, g < G ? qtok + (size_t)g * HD : nullptr, g + 8 < G ? qtok + (size_t)(g + 8) * HD : nullptr, tg);
+    QFrag<HD, ROWS> qf;
+    load_q<HD, ROWS>(qf, g < G ? qtok + (size_t)g * HD : nullptr, g + 8 < G ? qtok + (size_t)(g + 8) * HD : nullptr, tg);
     const int lo[2] = {first, first};
     const int hi[2] = {g < G ? pos : -1, g + 8 < G ? pos : -1};
-    for (int i = warp; i < nblk; i += 4) {
+    for (int i = warp; i < nblk; i += NW) {
       const int s = i % DEC_STAGES;
       int ok = 1;
       if (lane == 0) ok = mbar_wait(&full[s], (i / DEC_STAGES) & 1, err, 32) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       const bf16* kblk = (const bf16*)(ring + (size_t)s * STAGE);
-      block16<HD, true>(st, qf, kblk, kblk + 16 * HD, k_begin + 16 * i, lo, hi, scale_log2, g, tg);
+      block16<HD, true, ROWS>(st, qf, kblk, kblk + 16 * HD, k_begin + 16 * i, lo, hi, scale_log2, g, tg);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
     }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < ROWS; ++r) {
       st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
       st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
     }
   }
   __syncthreads();                              // every block is consumed: the ring is free for the merge
-  if (warp < 4) {
+  if (warp < NW) {
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < ROWS; ++r) {
       const int row = g + 8 * r;
       if (row >= G) continue;
-      float* dst = sm + ((size_t)warp * 16 + row) * ROW;
+      float* dst = sm + ((size_t)warp * 8 * ROWS + row) * ROW;
 #pragma unroll
       for (int i = 0; i < Shape<HD>::NT; ++i) {
         dst[out_dim<HD>(i, 2 * tg)] = st.o[i][2 * r];
@@ -476,16 +477,16 @@ __global__ void __launch_bounds__(160) attn_decode_bulk_kernel(bf16* __restrict_
     }
   }
   __syncthreads();
-  // merge the 4 warps in a fixed order (warp 0, 1, 2, 3)
+  // merge the warps in a fixed order (warp 0, 1, 2, ...)
   for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
     const int row = idx / HD, d = idx - row * HD;
     float m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) m = fmaxf(m, sm[((size_t)w * 16 + row) * ROW + HD]);
+    for (int w = 0; w < NW; ++w) m = fmaxf(m, sm[((size_t)w * 8 * ROWS + row) * ROW + HD]);
     float acc = 0.f, l = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float* src = sm + ((size_t)w * 16 + row) * ROW;
+    for (int w = 0; w < NW; ++w) {
+      const float* src = sm + ((size_t)w * 8 * ROWS + row) * ROW;
       const float f = (src[HD] == -INFINITY) ? 0.f : exp2f(src[HD] - m);
       acc += src[d] * f;
       l += src[HD + 1] * f;
@@ -542,25 +543,34 @@ int launch_decode(bf16* out, int ld_out, const bf16* q, int ld_q, const bf16* ca
   dim3 grid(splits, Hkv, T);
   int rc;
   if (g_decode_variant == 0 && g_decode_err != nullptr) {
-    constexpr int ring = DEC_STAGES * 2 * 16 * HD * 2, scratch = 4 * 16 * (HD + 2) * 4;
-    const size_t smem = (size_t)(ring > scratch ? ring : scratch) + 2 * DEC_STAGES * 8 + 128;
-    static bool configured = false;
-    if (!configured && smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(attn_decode_bulk_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-      configured = true;
-    }
-    rc = qv_launch(attn_decode_bulk_kernel<HD>, grid, dim3(160), smem, st, out, ld_out, q, ld_q, cache, tok_pos, tok_seg, bt,
-                   max_blocks, H, Hkv, page, window, scale_log2, splits, partial, g_decode_err);
+    // at most 8 query heads per kv head: half-tile state (fewer registers, fewer instructions)
+    const int G = H / Hkv;
+#define BULK_LAUNCH(ROWS_, NW_)                                                                                          \
+  do {                                                                                                                   \
+    constexpr int ring = DEC_STAGES * 2 * 16 * HD * 2, scratch = NW_ * 8 * ROWS_ * (HD + 2) * 4;                         \
+    const size_t smem = (size_t)(ring > scratch ? ring : scratch) + 2 * DEC_STAGES * 8 + 128;                            \
+    static bool configured = false;                                                                                      \
+    if (!configured && smem > 48 * 1024) {                                                                               \
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_bulk_kernel<HD, ROWS_, NW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return (int)e;                                                                               \
+      configured = true;                                                                                                 \
+    }                                                                                                                    \
+    rc = qv_launch(attn_decode_bulk_kernel<HD, ROWS_, NW_>, grid, dim3(32 * (NW_ + 1)), smem, st, out, ld_out, q, ld_q, cache, tok_pos, \
+                   tok_seg, bt, max_blocks, H, Hkv, page, window, scale_log2, splits, partial, g_decode_err);           \
+  } while (0)
+    if (G > 8) BULK_LAUNCH(2, 4);
+    else BULK_LAUNCH(1, 4);
+#undef BULK_LAUNCH
   } else {
     const size_t smem = (size_t)4 * 16 * (HD + 2) * sizeof(float);
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    rc = qv_launch(attn_decode_kernel<HD>, grid, dim3(128), smem, st, out, ld_out, q, ld_q, cache, tok_pos, tok_seg, bt,
+    // (the half-tile state that helps the bulk kernel measured slower here: 14.8 against 13.6 us)
+    rc = qv_launch(attn_decode_kernel<HD, 2>, grid, dim3(128), smem, st, out, ld_out, q, ld_q, cache, tok_pos, tok_seg, bt,
                    max_blocks, H, Hkv, page, window, scale_log2, splits, partial);
   }
   if (rc || splits == 1) return rc;

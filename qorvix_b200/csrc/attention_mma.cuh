@@ -38,15 +38,17 @@ template <int HD> struct Shape {
 };
 
 // Q rows g and g+8 of a 16-row tile as A fragments, in the k order of the K loads.
-template <int HD> struct QFrag { uint32_t w[Shape<HD>::KCH][2][Shape<HD>::KW]; };
+// ROWS = 1: only rows 0..7 of the tile are real (at most 8 query rows); the fragments, the running
+// state and the outputs of rows 8..15 are then not kept at all, which frees ~48 registers.
+template <int HD, int ROWS = 2> struct QFrag { uint32_t w[Shape<HD>::KCH][ROWS][Shape<HD>::KW]; };
 
-template <int HD>
-__device__ __forceinline__ void load_q(QFrag<HD>& q, const bf16* row_lo, const bf16* row_hi, int tg) {
+template <int HD, int ROWS = 2>
+__device__ __forceinline__ void load_q(QFrag<HD, ROWS>& q, const bf16* row_lo, const bf16* row_hi, int tg) {
   constexpr int KW = Shape<HD>::KW;
 #pragma unroll
   for (int c = 0; c < Shape<HD>::KCH; ++c) {
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < ROWS; ++r) {
       const bf16* p = r ? row_hi : row_lo;
       if (p) {
         Words<KW> v = load_words<KW>(p + c * KW * 8 + tg * KW * 2);
@@ -61,13 +63,16 @@ __device__ __forceinline__ void load_q(QFrag<HD>& q, const bf16* row_lo, const b
 }
 
 // Running softmax state of rows g and g+8 and their output fragments.
-template <int HD> struct RowState {
-  float m[2], l[2];
-  float o[Shape<HD>::NT][4];
+template <int HD, int ROWS = 2> struct RowState {
+  float m[ROWS], l[ROWS];
+  float o[Shape<HD>::NT][2 * ROWS];
   __device__ __forceinline__ void init() {
-    m[0] = m[1] = -INFINITY; l[0] = l[1] = 0.f;
 #pragma unroll
-    for (int i = 0; i < Shape<HD>::NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int r = 0; r < ROWS; ++r) { m[r] = -INFINITY; l[r] = 0.f; }
+#pragma unroll
+    for (int i = 0; i < Shape<HD>::NT; ++i)
+#pragma unroll
+      for (int e = 0; e < 2 * ROWS; ++e) o[i][e] = 0.f;
   }
 };
 
@@ -76,8 +81,8 @@ template <int HD> struct RowState {
 // first key.  Row r in {0,1} (tile rows g, g+8) sees keys in [lo[r], hi[r]] (inclusive).
 // EARLY_V: the V rows are requested together with the K rows, before the scores are formed,
 // so that both round trips to memory overlap (decode, where latency is what costs).
-template <int HD, bool EARLY_V>
-__device__ __forceinline__ void block16(RowState<HD>& st, const QFrag<HD>& q, const bf16* __restrict__ kblk,
+template <int HD, bool EARLY_V, int ROWS = 2>
+__device__ __forceinline__ void block16(RowState<HD, ROWS>& st, const QFrag<HD, ROWS>& q, const bf16* __restrict__ kblk,
                                         const bf16* __restrict__ vblk, int base, const int* lo, const int* hi,
                                         float scale_log2, int g, int tg) {
   constexpr int KW = Shape<HD>::KW, KCH = Shape<HD>::KCH, VW = Shape<HD>::VW, VCH = Shape<HD>::VCH;
@@ -106,17 +111,21 @@ __device__ __forceinline__ void block16(RowState<HD>& st, const QFrag<HD>& q, co
 #pragma unroll
     for (int c = 0; c < KCH; ++c) {
 #pragma unroll
-      for (int step = 0; step < KW / 2; ++step)
-        mma_bf16(s[j], q.w[c][0][2 * step], q.w[c][1][2 * step], q.w[c][0][2 * step + 1], q.w[c][1][2 * step + 1],
-                 kw[j][c].w[2 * step], kw[j][c].w[2 * step + 1]);
+      for (int step = 0; step < KW / 2; ++step) {
+        // with ROWS == 1 rows 8..15 of the tile are zero: their fragments are the constant 0
+        const uint32_t a1 = ROWS == 2 ? q.w[c][ROWS - 1][2 * step] : 0u, a3 = ROWS == 2 ? q.w[c][ROWS - 1][2 * step + 1] : 0u;
+        mma_bf16(s[j], q.w[c][0][2 * step], a1, q.w[c][0][2 * step + 1], a3, kw[j][c].w[2 * step], kw[j][c].w[2 * step + 1]);
+      }
     }
   }
   // mask, running maximum
-  float mx[2] = {-INFINITY, -INFINITY};
+  float mx[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) mx[r] = -INFINITY;
 #pragma unroll
   for (int j = 0; j < 2; ++j)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
+    for (int e = 0; e < 2 * ROWS; ++e) {
       const int r = e >> 1;
       const int key = base + 8 * j + 2 * tg + (e & 1);
       const float v = (key >= lo[r] && key <= hi[r]) ? s[j][e] * scale_log2 : -INFINITY;
@@ -124,13 +133,13 @@ __device__ __forceinline__ void block16(RowState<HD>& st, const QFrag<HD>& q, co
       mx[r] = fmaxf(mx[r], v);
     }
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
+  for (int r = 0; r < ROWS; ++r) {
     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
   }
-  float corr[2];
+  float corr[ROWS];
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
+  for (int r = 0; r < ROWS; ++r) {
     const float m_new = fmaxf(st.m[r], mx[r]);
     // a row with no visible key so far keeps m = -inf; exp2(-inf - (-inf)) must not be formed
     corr[r] = (m_new == -INFINITY) ? 1.f : exp2f(st.m[r] - m_new);
@@ -140,20 +149,20 @@ __device__ __forceinline__ void block16(RowState<HD>& st, const QFrag<HD>& q, co
   uint32_t p[4];     // A fragment of P: a0 (row g, keys 2tg..), a1 (row g+8), a2 (row g, keys 8+2tg..), a3
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
-    float e[4];
+    float e[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int x = 0; x < 4; ++x) {
+    for (int x = 0; x < 2 * ROWS; ++x) {
       const int r = x >> 1;
       e[x] = (s[j][x] == -INFINITY) ? 0.f : exp2f(s[j][x] - st.m[r]);
       st.l[r] += e[x];
     }
     p[2 * j] = pack_bf16(e[0], e[1]);
-    p[2 * j + 1] = pack_bf16(e[2], e[3]);
+    p[2 * j + 1] = ROWS == 2 ? pack_bf16(e[2], e[3]) : 0u;
   }
 #pragma unroll
   for (int i = 0; i < Shape<HD>::NT; ++i) {
-    st.o[i][0] *= corr[0]; st.o[i][1] *= corr[0];
-    st.o[i][2] *= corr[1]; st.o[i][3] *= corr[1];
+#pragma unroll
+    for (int e = 0; e < 2 * ROWS; ++e) st.o[i][e] *= corr[e >> 1];
   }
   // P.V: this thread supplies keys 2tg, 2tg+1, 8+2tg, 9+2tg for output column n = g of each n-tile;
   // n-tile e of chunk c is head dim c*VW*16 + g*VW*2 + e.
@@ -171,7 +180,15 @@ __device__ __forceinline__ void block16(RowState<HD>& st, const QFrag<HD>& q, co
       const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
       const uint32_t b0 = __byte_perm(vw[c][0].w[w], vw[c][1].w[w], sel);
       const uint32_t b1 = __byte_perm(vw[c][2].w[w], vw[c][3].w[w], sel);
-      mma_bf16(st.o[c * VW * 2 + e], p[0], p[1], p[2], p[3], b0, b1);
+      if (ROWS == 2) {
+        mma_bf16(st.o[c * VW * 2 + e], p[0], p[1], p[2], p[3], b0, b1);
+      } else {
+        // rows 8..15 are not kept: their accumulators go in as zero and come out unused
+        float d[4] = {st.o[c * VW * 2 + e][0], st.o[c * VW * 2 + e][1], 0.f, 0.f};
+        mma_bf16(d, p[0], 0u, p[2], 0u, b0, b1);
+        st.o[c * VW * 2 + e][0] = d[0];
+        st.o[c * VW * 2 + e][1] = d[1];
+      }
     }
   }
 }
