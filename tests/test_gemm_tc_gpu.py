@@ -92,3 +92,51 @@ def test_fused_swiglu_epilogue(M, f, K):
     out2 = torch.empty_like(out)
     ops.swiglu(out2, gu, interleaved=True)
     assert (out2.double() - ref).abs().max().item() <= 3e-2 * max(1.0, ref.abs().max().item())
+
+
+def test_packed_weight_tiles_are_the_swizzled_image_of_the_rows():
+    """pack_weight stores tile (t, kb) of 128 rows x 64 k at ((t * kblocks + kb) * 8192) elements, row r at
+    128-byte pitch with its 16-byte chunk c at position c ^ (r % 8), zero where the matrix ends."""
+    N, K = 200, 328                                   # two row tiles (the second ragged), six k blocks (the last ragged)
+    w = rnd(N, K, seed=3)
+    packed = ops.pack_weight(w).cpu().view(2, 6, 128, 8, 8)      # [tile][kb][row][chunk position][8 elements]
+    wc = torch.zeros(256, 384, dtype=torch.bfloat16)
+    wc[:N, :K] = w.cpu()
+    for t in range(2):
+        for kb in range(6):
+            for r in (0, 1, 7, 8, 63, 127):
+                for c in range(8):
+                    got = packed[t, kb, r, c ^ (r & 7)]
+                    want = wc[t * 128 + r, kb * 64 + c * 8: kb * 64 + c * 8 + 8]
+                    assert torch.equal(got, want), (t, kb, r, c)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 6144, 4096), (8, 4096, 14336), (3, 200, 96), (17, 1000, 328),
+                                   (40, 520, 1024), (64, 4096, 4096)])
+def test_packed_weights_give_the_same_product_bit_for_bit(M, N, K, out_dtype):
+    a, w = rnd(M, K, seed=M + K), rnd(N, K, seed=N + 1, scale=0.05)
+    packed = ops.pack_weight(w)
+    c_rows = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+    c_tiles = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+    assert ops.gemm_bf16_tc(c_rows, a, w)
+    assert ops.gemm_bf16_packed(c_tiles, a, packed, N)
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    assert torch.equal(c_rows, c_tiles)
+    ref = a.double() @ w.double().t()
+    tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
+    assert (c_tiles.double() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+
+
+def test_packed_weights_with_the_fused_swiglu_epilogue():
+    M, f, K = 8, 1008, 328
+    g, u = rnd(f, K, seed=5, scale=0.1), rnd(f, K, seed=6, scale=0.1)
+    w = torch.stack([g.view(f // 16, 16, K), u.view(f // 16, 16, K)], dim=1).reshape(2 * f, K).contiguous()
+    a = rnd(M, K, seed=7)
+    o_rows = torch.empty((M, f), device=DEV, dtype=torch.bfloat16)
+    o_tiles = torch.empty_like(o_rows)
+    assert ops.gemm_bf16_tc(o_rows, a, w, swiglu=True)
+    assert ops.gemm_bf16_packed(o_tiles, a, ops.pack_weight(w), 2 * f, swiglu=True)
+    ops.check_kernel_errors()
+    assert torch.equal(o_rows, o_tiles)
