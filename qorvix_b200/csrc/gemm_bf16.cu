@@ -92,8 +92,9 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
       const int w_row0 = SWAP ? wide0 : narrow0, x_row0 = SWAP ? narrow0 : wide0;
       const int w_off = SWAP ? 0 : A_BYTES, x_off = SWAP ? A_BYTES : 0;
       const int pre = num_kb < STAGES ? num_kb : STAGES;
-      // a packed weight matrix is read tile by tile with contiguous 16 KB copies (swap layout only)
-      const uint8_t* wp = (SWAP && args.packed) ? args.packed + ((size_t)blockIdx.x * total_kb + kb0) * (size_t)A_BYTES : nullptr;
+      // a packed weight matrix is read tile by tile with contiguous 16 KB copies; its tiles are 128
+      // rows, so the weight side of this kernel's tile must be 128 rows too (the host sees to that)
+      const uint8_t* wp = args.packed ? args.packed + ((size_t)(SWAP ? blockIdx.x : blockIdx.y) * total_kb + kb0) * (size_t)A_BYTES : nullptr;
       for (int kb = 0; kb < pre; ++kb) {
         mbar_expect_tx(&full[kb], STAGE_BYTES);
         if (wp) bulk_load_1d(tiles + kb * STAGE_BYTES + w_off, wp + (size_t)kb * A_BYTES, &full[kb], A_BYTES);
@@ -108,9 +109,9 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
         if (!mbar_wait(&empty[s], ph ^ 1, args.err, 1)) break;
         mbar_expect_tx(&full[s], STAGE_BYTES);
         uint8_t* a = tiles + s * STAGE_BYTES;
-        if (wp) bulk_load_1d(a, wp + (size_t)kb * A_BYTES, &full[s], A_BYTES);
-        else tma_load_2d(a, &map_wide, &full[s], (kb0 + kb) * BK, wide0);
-        tma_load_2d(a + A_BYTES, &map_narrow, &full[s], (kb0 + kb) * BK, narrow0);
+        if (wp) bulk_load_1d(a + w_off, wp + (size_t)kb * A_BYTES, &full[s], A_BYTES);
+        else tma_load_2d(a + w_off, w_map, &full[s], (kb0 + kb) * BK, w_row0);
+        tma_load_2d(a + x_off, x_map, &full[s], (kb0 + kb) * BK, x_row0);
       }
     }
   } else if (warp == 1) {
@@ -351,6 +352,23 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
 
   if (warp == 0) {
     if (lane == 0) {
+      // Arms stage s and requests the BN weight rows from n0 for k block kb: one tensor tile, or,
+      // from a packed matrix, BN/128 of its 16 KB tiles (a last tile that does not exist is left out;
+      // its columns are never stored).
+      const int w_tiles = (N + BM - 1) / BM;
+      auto load_w = [&](int s, int kb, int n0) {
+        uint8_t* dst = tiles + s * STAGE_BYTES + A_BYTES;
+        if (args.packed) {
+          const int t0 = n0 / BM;
+          const int nt = (w_tiles - t0) < BN / BM ? (w_tiles - t0) : BN / BM;
+          mbar_expect_tx(&full[s], A_BYTES + nt * A_BYTES);
+          for (int j = 0; j < nt; ++j)
+            bulk_load_1d(dst + j * A_BYTES, args.packed + ((size_t)(t0 + j) * num_kb + kb) * (size_t)A_BYTES, &full[s], A_BYTES);
+        } else {
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          tma_load_2d(dst, &map_w, &full[s], kb * BK, n0);
+        }
+      };
       // the first stages' weight tiles do not depend on the kernel ahead
       int it = 0;
       bool first = true;
@@ -359,10 +377,7 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
         int kb = 0;
         if (first) {
           const int pre = num_kb < STAGES ? num_kb : STAGES;
-          for (int k = 0; k < pre; ++k) {
-            mbar_expect_tx(&full[k], STAGE_BYTES);
-            tma_load_2d(tiles + k * STAGE_BYTES + A_BYTES, &map_w, &full[k], k * BK, n0);
-          }
+          for (int k = 0; k < pre; ++k) load_w(k, k, n0);
           pdl_wait();
           for (int k = 0; k < pre; ++k) tma_load_2d(tiles + k * STAGE_BYTES, &map_x, &full[k], k * BK, m0);
           kb = pre;
@@ -374,10 +389,8 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, args.err, 1)) { ok = false; break; }
-          mbar_expect_tx(&full[s], STAGE_BYTES);
-          uint8_t* a = tiles + s * STAGE_BYTES;
-          tma_load_2d(a, &map_x, &full[s], kb * BK, m0);
-          tma_load_2d(a + A_BYTES, &map_w, &full[s], kb * BK, n0);
+          load_w(s, kb, n0);
+          tma_load_2d(tiles + s * STAGE_BYTES, &map_x, &full[s], kb * BK, m0);
         }
         if (!ok) break;
       }
@@ -571,17 +584,22 @@ static int gemm_bf16_entry(void* C, const void* A, const void* W, const void* pa
 #undef SWAP_LAUNCH
   }
   // many tokens: tokens on the 128-row side, 128 weight rows per tile
-  if (!W) return QV_ERR_UNSUPPORTED;
+  if (!W && !packed) return QV_ERR_UNSUPPORTED;
+  args.packed = (const uint8_t*)packed;
   args.rows_wide = M; args.rows_narrow = N; args.kblocks_per_split = total_kb; args.splits = 1;
   if (g_prefill_variant == 0) {
     // persistent kernel, 128 x 256 tiles, accumulator double-buffered in tensor memory
-    if (!make_map(&mw, A, M, K, lda, BM) || !make_map(&mn, W, N, K, ldw, 256)) return QV_ERR_UNSUPPORTED;
+    if (!make_map(&mw, A, M, K, lda, BM)) return QV_ERR_UNSUPPORTED;
+    if (packed) mn = mw;
+    else if (!make_map(&mn, W, N, K, ldw, 256)) return QV_ERR_UNSUPPORTED;
     const int total_tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
     if (epilogue == 1) return launch_persistent<256, 4, bf16, true>(mw, mn, args, total_tiles, st);
     if (c_dt == QV_DT_BF16) return launch_persistent<256, 4, bf16, false>(mw, mn, args, total_tiles, st);
     return launch_persistent<256, 4, float, false>(mw, mn, args, total_tiles, st);
   }
-  if (!make_map(&mw, A, M, K, lda, BM) || !make_map(&mn, W, N, K, ldw, 128)) return QV_ERR_UNSUPPORTED;
+  if (!make_map(&mw, A, M, K, lda, BM)) return QV_ERR_UNSUPPORTED;
+  if (packed) mn = mw;
+  else if (!make_map(&mn, W, N, K, ldw, 128)) return QV_ERR_UNSUPPORTED;
   dim3 grid((M + BM - 1) / BM, (N + 127) / 128, 1);
   if (grid.y > 65535) return QV_ERR_TOO_LARGE;
   if (epilogue == 1) return launch<128, 3, false, bf16, true>(mw, mn, args, grid, st);
@@ -594,12 +612,12 @@ extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int
   return gemm_bf16_entry(C, A, W, nullptr, M, N, K, lda, ldw, ldc, c_dt, err, force_splits, epilogue, stream);
 }
 
-// As qv_gemm_bf16_tc for at most 64 tokens, with the weight matrix given as packed tiles
-// (qv_pack_weight_tiles): every CTA then streams its tiles with contiguous 16 KB copies, which an
-// SM takes in ~1.6x faster than tensor tiles of 128-byte rows and HBM serves ~15 % faster.
+// As qv_gemm_bf16_tc, with the weight matrix given as packed tiles (qv_pack_weight_tiles): every CTA
+// then fetches its weight tiles with contiguous 16 KB copies, which an SM takes in ~1.6x faster than
+// tensor tiles of 128-byte rows and HBM serves ~15 % faster.
 extern "C" int qv_gemm_bf16_packed(void* C, const void* A, const void* packed, int M, int N, int K, int lda, int ldc, int c_dt,
                                    int* err, int force_splits, int epilogue, void* stream) {
-  if (M > 64 || !packed) return QV_ERR_UNSUPPORTED;
+  if (!packed) return QV_ERR_UNSUPPORTED;
   return gemm_bf16_entry(C, A, nullptr, packed, M, N, K, lda, K, ldc, c_dt, err, force_splits, epilogue, stream);
 }
 

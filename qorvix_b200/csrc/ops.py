@@ -210,10 +210,10 @@ def pack_weight(w: torch.Tensor) -> torch.Tensor:
 
 
 def gemm_bf16_packed(c, a, packed, N: int, force_splits: int = 0, swiglu: bool = False) -> bool:
-    """As gemm_bf16_tc for at most 64 rows of a, with the weights given by pack_weight."""
+    """As gemm_bf16_tc, with the weights given by pack_weight (for any number of rows of a)."""
     _need_cuda(c, a, packed)
     M, K = a.shape
-    assert a.dtype == torch.bfloat16 and packed.dtype == torch.bfloat16 and M <= 64
+    assert a.dtype == torch.bfloat16 and packed.dtype == torch.bfloat16
     assert c.shape == ((M, N // 2) if swiglu else (M, N)) and a.stride(1) == 1 and c.stride(1) == 1
     st = _tc_buffers(a.device)
     rc = load_library("gemm_bf16").qv_gemm_bf16_packed(
@@ -260,36 +260,38 @@ def attention_generic(out, q, cache_layer, tok_pos, tok_seg, block_table, H, Hkv
 # ------------------------------------------------------------------ dispatch
 
 def packed_weights_enabled() -> bool:
-    """Whether bfloat16 weight matrices also get a packed copy for steps of few tokens
-    (QORVIX_PACKED_WEIGHTS=0 switches it off and halves the weights' memory)."""
+    """Whether bfloat16 weight matrices are stored as packed tiles (QORVIX_PACKED_WEIGHTS=0: as rows)."""
     import os
     return os.environ.get("QORVIX_PACKED_WEIGHTS", "1") != "0"
 
 
-def gemm(out, x, w, packed=None) -> None:
-    """out = x @ w^T with the kernel that fits the dtypes and the shape: bfloat16 operands go to
-    the tensor-core kernel when it takes the shape (for at most 64 rows and a packed copy of w, to the
-    one that streams packed tiles), everything else to the CUDA-core kernel."""
-    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-        if packed is not None and x.shape[0] <= 64 and gemm_bf16_packed(out, x, packed, w.shape[0]):
-            return
-        if gemm_bf16_tc(out, x, w):
-            return
+def gemm(out, x, w, packed=None, n: int = 0) -> None:
+    """out = x @ w^T with the kernel that fits the dtypes and the shape.  w is the matrix as rows
+    [n, K] (or None when only its packed tiles are kept, `packed` with `n` rows): bfloat16 operands
+    go to the tensor-core kernels (over the packed tiles when there are any), everything else to the
+    CUDA-core kernel."""
+    if x.dtype == torch.bfloat16 and packed is not None and gemm_bf16_packed(out, x, packed, n or w.shape[0]):
+        return
+    if w is None:
+        raise KernelError("the product's shape is one the tensor-core kernel refuses and the weight rows were not kept")
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and gemm_bf16_tc(out, x, w):
+        return
     gemm_simt(out, x, w)
 
 
-def gemm_swiglu(out, x, w_interleaved, packed=None) -> None:
+def gemm_swiglu(out, x, w_interleaved, packed=None, n: int = 0) -> None:
     """out[M,f] = silu(x Wg^T) * (x Wu^T) with gate and up rows interleaved in groups of 16 in
     w_interleaved [2f, K]: one tensor-core kernel when it takes the shape, else the product followed
     by the activation kernel."""
-    if x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
-        if (packed is not None and x.shape[0] <= 64
-                and gemm_bf16_packed(out, x, packed, w_interleaved.shape[0], swiglu=True)):
+    n = n or w_interleaved.shape[0]
+    if x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
+        if packed is not None and gemm_bf16_packed(out, x, packed, n, swiglu=True):
             return
-        if gemm_bf16_tc(out, x, w_interleaved, swiglu=True):
+        if (w_interleaved is not None and w_interleaved.dtype == torch.bfloat16
+                and gemm_bf16_tc(out, x, w_interleaved, swiglu=True)):
             return
-    gu = torch.empty((x.shape[0], w_interleaved.shape[0]), device=x.device, dtype=out.dtype)
-    gemm(gu, x, w_interleaved, packed)
+    gu = torch.empty((x.shape[0], n), device=x.device, dtype=out.dtype)
+    gemm(gu, x, w_interleaved, packed, n)
     swiglu(out, gu, interleaved=True)
 
 

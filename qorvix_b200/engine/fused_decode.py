@@ -83,7 +83,7 @@ class FusedDecode:
             if a.position is not None and type(a.position) is not RotaryEmbedding:
                 return None
             mats = (a.qkv_proj.weight, a.o_proj.weight, ff.gate_up.weight, ff.down.weight)
-            if any(m.dtype != torch.bfloat16 or m.shape[1] % 8 for m in mats):
+            if any(m is None or m.dtype != torch.bfloat16 or m.shape[1] % 8 for m in mats):     # needs the rows
                 return None
             view = cache.layer_view(run)
             if view.kind != "paged" or view.tensor is None or view.tensor.dtype != torch.bfloat16:

@@ -11,20 +11,23 @@ from ..csrc import ops
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor):
+    def __init__(self, weight: torch.Tensor, keep_rows: bool = False):
         assert weight.dim() == 2
         self.weight = weight.contiguous()
         self.out_features, self.in_features = weight.shape
-        # Steps of few tokens stream the whole matrix once; they read a second copy of it, stored as
-        # the 16 KB tiles the MMA consumes, which HBM and the SM's copy engine deliver faster than
-        # rows.  Steps of many tokens read the rows.
+        # A bfloat16 matrix is stored as the 16 KB tiles the MMA consumes (128 rows x 64 k in its
+        # swizzled shared-memory layout), which HBM and an SM's copy engine deliver faster than
+        # rows; the rows are then dropped (keep_rows, or QORVIX_KEEP_ROWS=1, keeps them: the
+        # opt-in fused decode kernel and tests that compare the two layouts read rows).
         self.packed = None
         if (self.weight.is_cuda and self.weight.dtype == torch.bfloat16 and self.in_features % 8 == 0
                 and ops.packed_weights_enabled()):
             try:
                 self.packed = ops.pack_weight(self.weight)
             except torch.cuda.OutOfMemoryError:
-                self.packed = None          # no room for the second copy: steps of few tokens read the rows
+                self.packed = None          # no room for the tiles beside the rows: the rows serve
+            if self.packed is not None and not (keep_rows or _keep_rows()):
+                self.weight = None
 
     def forward(self, x: torch.Tensor, out: torch.Tensor = None, out_dtype: torch.dtype = None) -> torch.Tensor:
         M = x.shape[0]
@@ -32,7 +35,12 @@ class Linear:
             out = torch.empty((M, self.out_features), device=x.device, dtype=out_dtype or x.dtype)
         if M == 0:
             return out
-        ops.gemm(out, x, self.weight, self.packed)
+        ops.gemm(out, x, self.weight, self.packed, self.out_features)
         return out
 
     __call__ = forward
+
+
+def _keep_rows() -> bool:
+    import os
+    return os.environ.get("QORVIX_KEEP_ROWS", "0") == "1" or os.environ.get("QORVIX_FUSED_DECODE", "0") == "1"

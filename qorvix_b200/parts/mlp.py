@@ -34,7 +34,7 @@ class SwiGLU(FeedForward):
     def forward(self, x, ctx):
         act = torch.empty((x.shape[0], self.f), device=x.device, dtype=self.rt.dtype)
         if self.interleaved:
-            ops.gemm_swiglu(act, x, self.gate_up.weight, self.gate_up.packed)
+            ops.gemm_swiglu(act, x, self.gate_up.weight, self.gate_up.packed, self.gate_up.out_features)
         else:
             gu = self.gate_up(x, out_dtype=self.rt.dtype)
             ops.swiglu(act, gu)
