@@ -15,6 +15,10 @@
 // Softmax statistics, rescaling and the output sum are float32.  Every mbarrier wait is bounded
 // and reports through *err instead of hanging.
 #include "common.cuh"
+
+#ifndef QV_P_TMEM
+#define QV_P_TMEM 1      // P goes to the P.V product through tensor memory (1) or shared memory (0)
+#endif
 #include <cuda.h>
 
 #define QT 128             // query rows per CTA
@@ -74,6 +78,13 @@ __device__ __forceinline__ void umma(uint32_t d, uint64_t a, uint64_t b, uint32_
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
 }
+// the same with the A operand in tensor memory (row = lane, two bfloat16 of consecutive k per column)
+__device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -89,6 +100,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // 2^x for x <= 0 on the special-function unit (results below the normal range flush to zero; P is
@@ -175,6 +198,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tmem_pv = tmem + 256;
+  const uint32_t tmem_p = tmem + 384;                // 64 columns: a row of P, two keys per column
 
   if (warp == 0) {
     if (lane == 0) {
@@ -226,6 +250,14 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
         if (!mbar_wait(p_full, j & 1, a.err, 15)) break;
         if (!mbar_wait(pv_empty, (j & 1) ^ 1, a.err, 16)) break;
         tc_fence_after();
+#if QV_P_TMEM
+        // P [128 rows][128 keys] in tensor memory (64 columns of two keys); V [128 keys][HD] MN-major
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk) {
+          const uint32_t v_addr = smem_u32(sV + s * K_BYTES + (kk * 16) * 128);
+          umma_ts(tmem_pv, tmem_p + (uint32_t)(kk * 8), desc_mnmajor(v_addr, HALF_BYTES), idesc_pv, kk > 0 ? 1u : 0u);
+        }
+#else
         // P [128 rows][128 keys] as two K-major halves of 64 keys; V [128 keys][HD] MN-major
 #pragma unroll
         for (int kh = 0; kh < 2; ++kh) {
@@ -236,6 +268,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
             umma(tmem_pv, dp + 2 * kk, desc_mnmajor(v_addr, HALF_BYTES), idesc_pv, (kh > 0 || kk > 0) ? 1u : 0u);
           }
         }
+#endif
         umma_commit(pv_full);
         umma_commit(&kv_empty[s]);
         umma_commit(p_empty);
@@ -316,6 +349,15 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
             w[i >> 1] = pack2(e[0], e[1]);
           }
         }
+#if QV_P_TMEM
+        // 64 keys = 32 columns of this row's P in tensor memory
+        tmem_st32(tmem_p + lane_base + (uint32_t)(c >> 1), w);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&s_empty[s]);                       // S[s] may be overwritten by tile j + 2
+      mbar_arrive(p_full);
+#else
         // 64 keys = the 8 chunks of 16 bytes of this row in half (c / 64)
         uint8_t* prow = sP + (c >> 6) * HALF_BYTES + r * 128;
 #pragma unroll
@@ -326,6 +368,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
       mbar_arrive(&s_empty[s]);                       // S[s] may be overwritten by tile j + 2
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(p_full);
+#endif
       // fold in the previous tile's P.V, then rescale to the new maximum
       if (j > 0) {
         if (ok) ok = mbar_wait(pv_full, (j - 1) & 1, a.err, 19);
