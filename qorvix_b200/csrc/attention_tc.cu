@@ -19,6 +19,10 @@
 #ifndef QV_P_TMEM
 #define QV_P_TMEM 1      // P goes to the P.V product through tensor memory (1) or shared memory (0)
 #endif
+#ifndef QV_O_TMEM
+#define QV_O_TMEM 1      // the output row accumulates in tensor memory across key tiles (1) or in registers (0)
+#endif
+#define RESCALE_STEP 8.0f   // with QV_O_TMEM: the reference maximum of a row moves only when it grew by more than 2^8
 #include <cuda.h>
 
 #define QT 128             // query rows per CTA
@@ -248,14 +252,16 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
         if (!ok) break;
         const int s = j & 1;
         if (!mbar_wait(p_full, j & 1, a.err, 15)) break;
+#if !QV_O_TMEM
         if (!mbar_wait(pv_empty, (j & 1) ^ 1, a.err, 16)) break;
+#endif
         tc_fence_after();
 #if QV_P_TMEM
         // P [128 rows][128 keys] in tensor memory (64 columns of two keys); V [128 keys][HD] MN-major
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk) {
           const uint32_t v_addr = smem_u32(sV + s * K_BYTES + (kk * 16) * 128);
-          umma_ts(tmem_pv, tmem_p + (uint32_t)(kk * 8), desc_mnmajor(v_addr, HALF_BYTES), idesc_pv, kk > 0 ? 1u : 0u);
+          umma_ts(tmem_pv, tmem_p + (uint32_t)(kk * 8), desc_mnmajor(v_addr, HALF_BYTES), idesc_pv, (kk > 0 || (QV_O_TMEM && j > 0)) ? 1u : 0u);
         }
 #else
         // P [128 rows][128 keys] as two K-major halves of 64 keys; V [128 keys][HD] MN-major
@@ -276,6 +282,123 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
     }
   } else {
     // softmax: thread = query row
+#if QV_O_TMEM && QV_P_TMEM
+    // The output row lives in tensor memory and the P.V products accumulate into it; a row's
+    // reference maximum moves only when the true maximum has grown by more than 2^RESCALE_STEP
+    // (then the row in tensor memory is scaled down once), so P may reach 2^RESCALE_STEP and most
+    // tiles need neither a second pass over S nor any work on O.
+    const int qd = warp & 3;
+    const int r = qd * 32 + lane;
+    const int row_in_seg = tile0 + r;
+    const int hi = row_in_seg < qlen ? pos0 + row_in_seg : -1;
+    const int lo = (a.window > 0 && hi - a.window + 1 > 0) ? hi - a.window + 1 : 0;
+    const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j & 1;
+      const int key_base = (tile_begin + j) * KT;
+      ok = mbar_wait(&s_full[s], (j >> 1) & 1, a.err, 17);
+      tc_fence_after();
+      const uint32_t s_addr = tmem + lane_base + (uint32_t)(s * KT);
+      uint32_t sv[KT];                                   // this row of S, read once
+#pragma unroll
+      for (int c = 0; c < KT; c += 32) tmem_ld32(s_addr + c, sv + c);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&s_empty[s]);                       // S[s] may be overwritten by tile j + 2
+      const bool all_visible = key_base >= lo && key_base + KT - 1 <= hi;   // no mask needed in this tile
+      float mx = -INFINITY;
+      if (all_visible) {
+#pragma unroll
+        for (int i = 0; i < KT; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < KT; ++i) {
+          const int key = key_base + i;
+          if (key >= lo && key <= hi) mx = fmaxf(mx, __uint_as_float(sv[i]));
+        }
+      }
+      mx *= a.scale_log2;                              // the scale is positive: max commutes with it
+      float corr = 1.f;
+      if (mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY)) {
+        corr = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - mx);
+        m_ref = mx;
+      }
+      // P's columns are free, and the output row is at rest, once the previous tile's P.V is done
+      if (ok) ok = mbar_wait(p_empty, (j & 1) ^ 1, a.err, 18);
+      tc_fence_after();
+      if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+        // some row of this warp moves its reference: scale the warp's rows of O (by 1 where nothing moved)
+#pragma unroll
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_pv + lane_base + c, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+          tmem_st32(tmem_pv + lane_base + c, v);
+        }
+      }
+      l *= corr;
+      float sum = 0.f;
+      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+#pragma unroll
+      for (int c = 0; c < KT; c += 64) {
+        uint32_t w[32];
+        if (all_visible) {                             // most tiles: no mask, two instructions per score
+#pragma unroll
+          for (int i = 0; i < 64; i += 2) {
+            const float e0 = fast_exp2(fmaf(__uint_as_float(sv[c + i]), a.scale_log2, neg_m));
+            const float e1 = fast_exp2(fmaf(__uint_as_float(sv[c + i + 1]), a.scale_log2, neg_m));
+            sum += e0 + e1;
+            w[i >> 1] = pack2(e0, e1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; i += 2) {
+            float e[2];
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+              const int key = key_base + c + i + x;
+              e[x] = (key >= lo && key <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c + i + x]), a.scale_log2, neg_m)) : 0.f;
+            }
+            sum += e[0] + e[1];
+            w[i >> 1] = pack2(e[0], e[1]);
+          }
+        }
+        tmem_st32(tmem_p + lane_base + (uint32_t)(c >> 1), w);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full);
+      l += sum;
+    }
+    if (ok && n_tiles > 0) {
+      ok = mbar_wait(pv_full, (n_tiles - 1) & 1, a.err, 20);
+      tc_fence_after();
+      // every lane takes part in the loads (they are warp-wide); only rows of the segment are stored
+      const bool store = ok && row_in_seg < qlen;
+      const float inv = store ? 1.f / l : 0.f;
+      bf16* orow = a.out + (size_t)(q0 + (store ? row_in_seg : 0)) * a.ld_out + (size_t)h * HD;
+#pragma unroll
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_pv + lane_base + c, v);
+        tmem_wait_ld();
+        if (store) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8)
+            *(uint4*)(orow + c + i) = make_uint4(pack2(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv),
+                                                 pack2(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv),
+                                                 pack2(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv),
+                                                 pack2(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv));
+        }
+      }
+    }
+    tc_fence_before();
+  }
+#else
     const int qd = warp & 3;
     const int r = qd * 32 + lane;
     const int row_in_seg = tile0 + r;
@@ -409,6 +532,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
     }
     tc_fence_before();
   }
+#endif
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
