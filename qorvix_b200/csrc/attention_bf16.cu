@@ -32,9 +32,11 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(bf16* __restrict__ ou
                                                            int max_blocks, int H, int Hkv, int page, int window, float scale_log2) {
   pdl_wait();
   pdl_launch_dependents();
-  const int seg = blockIdx.z, h = blockIdx.y;
+  // grid (heads, query tiles, segments), the last query tile (most keys) first: CTAs are handed out
+  // x-fastest, so the longest work starts first
+  const int seg = blockIdx.z, h = blockIdx.x;
   const int q0 = seg_q_start[seg], qlen = seg_q_start[seg + 1] - q0;
-  const int tile0 = blockIdx.x * 64;
+  const int tile0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * 64;
   if (tile0 >= qlen) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
   const int r0 = tile0 + warp * 16;                 // first row of this warp within the segment
@@ -116,9 +118,11 @@ __global__ void __launch_bounds__(128) attn_prefill_tile_kernel(bf16* __restrict
   bf16* sV = sK + 2 * 64 * HD;                      // [2][64][HD]
   pdl_wait();
   pdl_launch_dependents();
-  const int seg = blockIdx.z, h = blockIdx.y;
+  // grid (heads, query tiles, segments), the last query tile (most keys) first: CTAs are handed out
+  // x-fastest, so the longest work starts first
+  const int seg = blockIdx.z, h = blockIdx.x;
   const int q0 = seg_q_start[seg], qlen = seg_q_start[seg + 1] - q0;
-  const int tile0 = blockIdx.x * 64;
+  const int tile0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * 64;
   if (tile0 >= qlen) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
   const int pos0 = seg_pos0[seg];
@@ -288,7 +292,7 @@ int launch_prefill_tile(bf16* out, int ld_out, const bf16* q, int ld_q, const bf
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((max_q_len + 63) / 64, H, S);
+  dim3 grid(H, (max_q_len + 63) / 64, S);
   return qv_launch(attn_prefill_tile_kernel<HD>, grid, dim3(128), (size_t)smem, st, out, ld_out, q, ld_q, cache, seg_q_start, seg_pos0,
                    bt, max_blocks, H, Hkv, page, window, scale_log2);
 }
@@ -527,7 +531,7 @@ template <int HD>
 int launch_prefill(bf16* out, int ld_out, const bf16* q, int ld_q, const bf16* cache, const int* seg_q_start, const int* seg_pos0,
                    const int* bt, int max_blocks, int S, int max_q_len, int H, int Hkv, int page, int window, float scale_log2,
                    cudaStream_t st) {
-  dim3 grid((max_q_len + 63) / 64, H, S);
+  dim3 grid(H, (max_q_len + 63) / 64, S);
   return qv_launch(attn_prefill_kernel<HD>, grid, dim3(128), 0, st, out, ld_out, q, ld_q, cache, seg_q_start, seg_pos0, bt,
                    max_blocks, H, Hkv, page, window, scale_log2);
 }
@@ -601,7 +605,7 @@ extern "C" int qv_attn_prefill_bf16(void* out, int ld_out, const void* q, int ld
   // register-direct one; variant 1: always the register-direct kernel.
   if (S <= 0 || max_q_len <= 0) return 0;
   if (Hkv <= 0 || H % Hkv || page % 16 || (ld_q & 7) || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15)) return QV_ERR_UNSUPPORTED;
-  if (S > 65535 || H > 65535) return QV_ERR_TOO_LARGE;
+  if (S > 65535 || (max_q_len + 63) / 64 > 65535) return QV_ERR_TOO_LARGE;
   const float sl2 = scale * 1.4426950408889634f;
   if ((hd == 64 || hd == 128) && (ld_out & 1) == 0 && variant == 0) {
     if (hd == 64)

@@ -588,7 +588,7 @@ extern "C" int qv_attn_prefill_tc(void* out, int ld_out, const void* q, int ld_q
   if ((hd != 64 && hd != 128) || Hkv <= 0 || H % Hkv || page % 16 || (ld_q & 7) || (ld_out & 7) || ((uintptr_t)q & 15) ||
       ((uintptr_t)cache & 15) || ((uintptr_t)out & 15))
     return QV_ERR_UNSUPPORTED;
-  if (S > 65535 || H > 65535) return QV_ERR_TOO_LARGE;
+  if (S > 65535 || (max_q_len + QT - 1) / QT > 65535) return QV_ERR_TOO_LARGE;
   CUtensorMap mq, mkv;
   if (!make_map(&mq, q, T, H * hd, ld_q, QT)) return QV_ERR_UNSUPPORTED;
   if (!make_map(&mkv, cache, cache_pages * 2 * Hkv * page, hd, hd, 16)) return QV_ERR_UNSUPPORTED;
