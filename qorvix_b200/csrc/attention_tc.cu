@@ -22,6 +22,7 @@
 #ifndef QV_O_TMEM
 #define QV_O_TMEM 1      // the output row accumulates in tensor memory across key tiles (1) or in registers (0)
 #endif
+#define KV_ST (QV_P_TMEM ? 3 : 2)   // stages of keys and values in shared memory (P's buffer, when there is one, takes a stage's room)
 #define RESCALE_STEP 8.0f   // with QV_O_TMEM: the reference maximum of a row moves only when it grew by more than 2^8
 #include <cuda.h>
 
@@ -152,19 +153,19 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = base;
   uint8_t* sK = sQ + Q_BYTES;                        // 2 stages
-  uint8_t* sV = sK + 2 * K_BYTES;                    // 2 stages
-  uint8_t* sP = sV + 2 * K_BYTES;
-  uint64_t* bars = (uint64_t*)(sP + P_BYTES);
+  uint8_t* sV = sK + KV_ST * K_BYTES;                // KV_ST stages each
+  uint8_t* sP = sV + KV_ST * K_BYTES;                // only without QV_P_TMEM
+  uint64_t* bars = (uint64_t*)(sP + (QV_P_TMEM ? 0 : P_BYTES));
   uint64_t* q_full = bars;                           // 1
-  uint64_t* kv_full = bars + 1;                      // 2
-  uint64_t* kv_empty = bars + 3;                     // 2
+  uint64_t* kv_full = bars + 13;                     // KV_ST
+  uint64_t* kv_empty = bars + 16;                    // KV_ST
   uint64_t* s_full = bars + 5;                       // 2
   uint64_t* s_empty = bars + 7;                      // 2
   uint64_t* p_full = bars + 9;
   uint64_t* p_empty = bars + 10;
   uint64_t* pv_full = bars + 11;
   uint64_t* pv_empty = bars + 12;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 13);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 19);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Grid (heads, query tiles, segments): CTAs are handed out in x-fastest order, so all heads of the
@@ -188,7 +189,8 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128); }
+    for (int i = 0; i < KV_ST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128); }
     mbar_init(p_full, 128); mbar_init(p_empty, 1); mbar_init(pv_full, 1); mbar_init(pv_empty, 128);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -210,8 +212,8 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
       for (int hf = 0; hf < NH; ++hf) tma_load_2d(sQ + hf * HALF_BYTES, &map_q, q_full, h * HD + hf * 64, q0 + tile0);
       const int last_block = k_last & ~15;
       for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, a.err, 11)) break;
+        const int s = j % KV_ST;
+        if (!mbar_wait(&kv_empty[s], ((j / KV_ST) & 1) ^ 1, a.err, 11)) break;
         mbar_expect_tx(&kv_full[s], 2 * K_BYTES);
         for (int blk = 0; blk < KT / 16; ++blk) {
           int key0 = (tile_begin + j) * KT + blk * 16;
@@ -231,15 +233,15 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
       constexpr uint32_t idesc_pv = idesc_f16(QT, HD, 1);
       bool ok = mbar_wait(q_full, 0, a.err, 12);
       auto issue_qk = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait(&kv_full[s], (j >> 1) & 1, a.err, 13)) return false;
+        const int s = j & 1, ks = j % KV_ST;
+        if (!mbar_wait(&kv_full[ks], (j / KV_ST) & 1, a.err, 13)) return false;
         if (!mbar_wait(&s_empty[s], ((j >> 1) & 1) ^ 1, a.err, 14)) return false;
         tc_fence_after();
         const uint32_t d = tmem + (uint32_t)(s * KT);
 #pragma unroll
         for (int hf = 0; hf < NH; ++hf) {
           const uint64_t dq = desc_kmajor(smem_u32(sQ + hf * HALF_BYTES));
-          const uint64_t dk = desc_kmajor(smem_u32(sK + s * K_BYTES + hf * HALF_BYTES));
+          const uint64_t dk = desc_kmajor(smem_u32(sK + ks * K_BYTES + hf * HALF_BYTES));
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) umma(d, dq + 2 * kk, dk + 2 * kk, idesc_qk, (hf > 0 || kk > 0) ? 1u : 0u);
         }
@@ -250,7 +252,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);
         if (!ok) break;
-        const int s = j & 1;
+        const int s = j % KV_ST;                     // the stage of this tile's keys and values
         if (!mbar_wait(p_full, j & 1, a.err, 15)) break;
 #if !QV_O_TMEM
         if (!mbar_wait(pv_empty, (j & 1) ^ 1, a.err, 16)) break;
@@ -566,7 +568,7 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, long 
 
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const AttnArgs& args, dim3 grid, cudaStream_t st) {
-  constexpr int smem = QT * HD * 2 + 4 * KT * HD * 2 + QT * KT * 2 + 1024 + 256;
+  constexpr int smem = QT * HD * 2 + 2 * KV_ST * KT * HD * 2 + (QV_P_TMEM ? 0 : QT * KT * 2) + 1024 + 256;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
