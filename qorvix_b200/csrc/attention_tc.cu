@@ -207,24 +207,30 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(const __grid_const
   const uint32_t tmem_p = tmem + 384;                // 64 columns: a row of P, two keys per column
 
   if (warp == 0) {
+    // The whole warp requests: a tile of keys and values is 8 blocks of 16 keys (a page may hold no
+    // more), each in NH halves of 64 dims, i.e. up to 32 small TMA loads.  One thread issuing them
+    // all took as long as the tile's softmax; the lanes issue one load each.
     if (lane == 0) {
       mbar_expect_tx(q_full, Q_BYTES);
       for (int hf = 0; hf < NH; ++hf) tma_load_2d(sQ + hf * HALF_BYTES, &map_q, q_full, h * HD + hf * 64, q0 + tile0);
-      const int last_block = k_last & ~15;
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j % KV_ST;
-        if (!mbar_wait(&kv_empty[s], ((j / KV_ST) & 1) ^ 1, a.err, 11)) break;
-        mbar_expect_tx(&kv_full[s], 2 * K_BYTES);
-        for (int blk = 0; blk < KT / 16; ++blk) {
-          int key0 = (tile_begin + j) * KT + blk * 16;
-          if (key0 > last_block) key0 = last_block;            // keys nobody sees: any valid page will do
-          const int row = ((bt[key0 / a.page] * 2) * a.Hkv + kvh) * a.page + (key0 % a.page);
-          const int vrow = row + a.Hkv * a.page;
-          for (int hf = 0; hf < NH; ++hf) {
-            tma_load_2d(sK + s * K_BYTES + hf * HALF_BYTES + blk * 16 * 128, &map_kv, &kv_full[s], hf * 64, row);
-            tma_load_2d(sV + s * K_BYTES + hf * HALF_BYTES + blk * 16 * 128, &map_kv, &kv_full[s], hf * 64, vrow);
-          }
-        }
+    }
+    const int last_block = k_last & ~15;
+    const int which = lane / (8 * NH);               // 0: keys, 1: values
+    const int blk = (lane % (8 * NH)) / NH, hf = lane % NH;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j % KV_ST;
+      if (lane == 0) {
+        ok = mbar_wait(&kv_empty[s], ((j / KV_ST) & 1) ^ 1, a.err, 11);
+        if (ok) mbar_expect_tx(&kv_full[s], 2 * K_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      if (which < 2) {
+        int key0 = (tile_begin + j) * KT + blk * 16;
+        if (key0 > last_block) key0 = last_block;            // keys nobody sees: any valid page will do
+        const int row = ((bt[key0 / a.page] * 2 + which) * a.Hkv + kvh) * a.page + (key0 % a.page);
+        tma_load_2d((which ? sV : sK) + s * K_BYTES + hf * HALF_BYTES + blk * 16 * 128, &map_kv, &kv_full[s], hf * 64, row);
       }
     }
   } else if (warp == 1) {
