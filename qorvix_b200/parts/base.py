@@ -4,8 +4,10 @@ Mixer         forward(x[T,d], ctx, cache) -> [T,d] in the compute dtype; cache_s
               it keeps per request (cache.spec.PagedKVSpec / FixedStateSpec / None);
               reads_cache_of() names another layer whose cache it reads instead.
 FeedForward   forward(x[T,d], ctx) -> [T,d].
-Norm          add_norm(residual, delta, out=None, rows=None): residual (float32) += delta, returns the
-              normed rows in the compute dtype.  The sum and the norm are computed in float32.
+Norm          add_norm(residual, delta, rows=None): residual (float32) += delta (delta may be None), returns
+              the normed rows in the compute dtype; with rows (int32 row indices) only those rows of
+              residual + delta are normed and the residual is left as it is.  The sum and the norm
+              are computed in float32.
 Position      table() -> float32 [positions, rotary_dim/2, 2] of (cos, sin) if it is a rotation
               the attention kernels can fuse, else None; apply(qkv, ctx, H, Hkv, hd) rotates q and k
               in place for mixers that do not fuse it.

@@ -61,6 +61,8 @@ class AttentionSpec:
         if self.kv_from is None:
             t[self.k_proj] = ((self.num_kv_heads * self.head_dim, self.hidden_size), "matrix")
             t[self.v_proj] = ((self.num_kv_heads * self.head_dim, self.hidden_size), "matrix")
+        if self.position is not None:
+            t.update(self.position.tensors())       # a position encoding may have weights of its own
         return t
 
 
