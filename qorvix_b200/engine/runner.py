@@ -179,8 +179,22 @@ class ModelRunner:
         elif entries:
             if device_tokens is not None:
                 raise ValueError("device_tokens need a decode-only step that runs as a captured graph")
+            # A mixed step runs its single-token entries first: the attention kernels then serve the
+            # decoded tokens and the prompt portions each with the kernel made for them.  The logits
+            # go back in the order the caller gave.
+            order = sorted(range(len(entries)), key=lambda i: len(entries[i].tokens) != 1)
+            back = None
+            if order != list(range(len(entries))):
+                first_row, row = {}, 0
+                for i in order:
+                    first_row[i] = row
+                    row += len(entries[i].want)
+                back = [first_row[i] + k for i, e in enumerate(entries) for k in range(len(e.want))]
+                entries = [entries[i] for i in order]
             ctx = self.prepare(entries)
             logits = self.model.forward(ctx, self.cache)
+            if logits is not None and back is not None and back != list(range(len(back))):
+                logits = logits[torch.tensor(back, device=self.device)]
             for e in entries:
                 self.cache.commit(e.req_id, len(e.tokens))
             self.steps_run += 1

@@ -205,6 +205,30 @@ def test_decoded_tokens_before_a_portion(models, case, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_logits_keep_the_callers_order_when_portions_come_before_decoded_tokens(models, dtype):
+    """Entries in the order portion, token, portion, token, token, token, each with wanted places:
+    the engine runs the single tokens first, the logits come back in the order given."""
+    d, pm = models[("B", 8.0)]
+    cfg = TINY["B"]
+    r = ModelRunner(d, dtype=dtype, max_tokens=1024, page_size=16, max_requests=8)
+    dec = {f"d{i}": random_tokens(cfg.vocab_size, 18 + 5 * i, 400 + i) for i in range(4)}
+    p1, p2 = random_tokens(cfg.vocab_size, 50, 410), random_tokens(cfg.vocab_size, 37, 411)
+    for k, t in dec.items():
+        r.step([StepEntry(k, t[:-1], [])])
+    r.step([StepEntry("p1", p1[:12], [])])
+    names = list(dec)
+    entries = [StepEntry("p1", p1[12:], [0, 37, 5]), StepEntry(names[0], [dec[names[0]][-1]], [0]),
+               StepEntry("p2", p2, [36]), StepEntry(names[1], [dec[names[1]][-1]], [0]),
+               StepEntry(names[2], [dec[names[2]][-1]], []), StepEntry(names[3], [dec[names[3]][-1]], [0])]
+    out = r.step(entries)
+    assert out.shape[0] == 7
+    ref = torch.cat([pm.logits(p1)[[12, 49, 17]], pm.logits(dec[names[0]])[-1:], pm.logits(p2)[-1:],
+                     pm.logits(dec[names[1]])[-1:], pm.logits(dec[names[3]])[-1:]])
+    assert_close_logits(out, ref, dtype, "caller's order", sharp=True)
+    r.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_one_layer_of_llama31_8b_sizes(dtype):
     """The real sizes (hidden 4096, 32 heads over 8 kv heads of 128, feed-forward 14336, vocabulary
     128256, llama3 scaling from 8192) on one layer: whole, in portions and token by token, against
