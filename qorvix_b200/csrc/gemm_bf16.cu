@@ -559,8 +559,9 @@ static int gemm_bf16_entry(void* C, const void* A, const void* W, const void* pa
     if (epilogue == 1) splits = 1;                  // the fused activation needs whole sums
     else if (force_splits > 0) splits = force_splits;
     else if (tiles < 96) {                          // too few CTAs to pull full bandwidth: split along K
-      // a power of two (clusters of 2, 4 or 8 CTAs place well), at most ~200 CTAs in all
-      while (splits < 8 && tiles * splits * 2 <= 200 && total_kb / (splits * 2) >= 4) splits *= 2;
+      // a power of two, at most 4: clusters of 8 CTAs do not all find room at once (measured: a
+      // 2048 x 8192 product takes 22.5 us at 8 splits, 13.2 us at 4), and at most ~200 CTAs in all
+      while (splits < 4 && tiles * splits * 2 <= 200 && total_kb / (splits * 2) >= 4) splits *= 2;
     }
     if (splits > total_kb) splits = total_kb;
     int per = (total_kb + splits - 1) / splits;
