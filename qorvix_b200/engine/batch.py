@@ -10,6 +10,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -82,32 +83,39 @@ class BatchBuilder:
         """segs: dicts with tokens, pos0, slot, want, first.  group_tables[g][s] = page ids of
         segment s in cache group g (-1 entries, given back to the pool, read as the scratch page)."""
         S = len(segs)
-        T = sum(len(s["tokens"]) for s in segs)
+        lens = [len(s["tokens"]) for s in segs]
+        T = sum(lens)
         R = sum(len(s["want"]) for s in segs)
         widths = {g: max(1, max((len(t) for t in tabs), default=1)) for g, tabs in group_tables.items()}
         total = 3 * T + (S + 1) + 2 * S + R + sum(S * w for w in widths.values())
         host, ring_slot = self._host_buffer(max(total, 1))
-        flat: List[int] = []
-        ids, pos, seg, qstart, pos0, slots, rows = [], [], [], [0], [], [], []
+        h = host.numpy()                                          # the arrays are written in place, no lists of T ints
+        qstart = np.zeros(S + 1, dtype=np.int64)
+        np.cumsum(lens, out=qstart[1:])
+        pos0 = np.fromiter((s["pos0"] for s in segs), dtype=np.int64, count=S)
         for si, s in enumerate(segs):
-            n = len(s["tokens"])
-            ids.extend(s["tokens"])
-            pos.extend(range(s["pos0"], s["pos0"] + n))
-            seg.extend([si] * n)
-            base = qstart[-1]
-            rows.extend(base + w for w in s["want"])
-            qstart.append(base + n)
-            pos0.append(s["pos0"])
-            slots.append(s["slot"])
-        flat = ids + pos + seg + qstart + pos0 + slots + rows
+            a, b = int(qstart[si]), int(qstart[si + 1])
+            h[a:b] = s["tokens"]
+            h[T + a: T + b] = np.arange(s["pos0"], s["pos0"] + (b - a), dtype=np.int32)
+            h[2 * T + a: 2 * T + b] = si
+        o = 3 * T
+        h[o: o + S + 1] = qstart; o += S + 1
+        h[o: o + S] = pos0; o += S
+        h[o: o + S] = [s["slot"] for s in segs]; o += S
+        if R:
+            h[o: o + R] = [int(qstart[si]) + w for si, s in enumerate(segs) for w in s["want"]]
+        o += R
         offsets = {}
         for g, tabs in group_tables.items():
-            offsets[g] = len(flat)
+            offsets[g] = o
             w = widths[g]
-            for t in tabs:
-                flat.extend((p if p >= 0 else scratch_page) for p in t)
-                flat.extend([scratch_page] * (w - len(t)))
-        host[: len(flat)] = torch.tensor(flat, dtype=torch.int32) if flat else host[:0]
+            block = h[o: o + S * w].reshape(S, w)
+            block[:] = scratch_page
+            for si, t in enumerate(tabs):
+                if len(t):
+                    row = np.asarray(t, dtype=np.int32)
+                    block[si, : len(t)] = np.where(row >= 0, row, scratch_page)
+            o += S * w
         if self.device.type == "cuda":
             dev = host.to(self.device, non_blocking=True)
             self.h2d_bytes += host.numel() * 4
@@ -127,7 +135,6 @@ class BatchBuilder:
         token_ids, tok_pos, tok_seg = take(T), take(T), take(T)
         seg_q_start, seg_pos0, seg_slot, want_rows = take(S + 1), take(S), take(S), take(R)
         block_tables = {g: dev[offsets[g]: offsets[g] + S * widths[g]].view(S, widths[g]) for g in group_tables}
-        lens = [len(s["tokens"]) for s in segs]
         return StepContext(
             num_tokens=T, num_segments=S, num_wanted=R, token_ids=token_ids, tok_pos=tok_pos,
             tok_seg=tok_seg, seg_q_start=seg_q_start, seg_pos0=seg_pos0, seg_slot=seg_slot,

@@ -12,6 +12,7 @@ from __future__ import annotations
 from pathlib import Path
 from typing import Dict, Hashable, Iterable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import CacheManager, OutOfPages, OutOfSlots
@@ -101,6 +102,7 @@ class ModelRunner:
         """Admits new requests, reserves pages for every entry (all or nothing) and builds the
         step's context.  Raises OutOfPages / OutOfSlots with nothing changed."""
         seen = set()
+        arrays = []
         for e in entries:
             if e.req_id in seen:
                 raise ValueError(f"request {e.req_id!r} appears twice in one step")
@@ -108,9 +110,19 @@ class ModelRunner:
             n = len(e.tokens)
             if n == 0:
                 raise ValueError(f"request {e.req_id!r} brings no tokens")
-            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
-            if bad:
-                raise ValueError(f"request {e.req_id!r}: token id {bad[0]} is outside the vocabulary of {self.vocab_size}")
+            if n == 1:                                  # a decoded token: no array for one id
+                toks = [int(e.tokens[0])]
+                bad = None if 0 <= toks[0] < self.vocab_size else toks[0]
+            else:
+                toks = np.asarray(e.tokens, dtype=np.int64)
+                if toks.ndim != 1:
+                    raise ValueError(f"request {e.req_id!r}: tokens must be a flat sequence of ids")
+                bad = None
+                if int(toks.min()) < 0 or int(toks.max()) >= self.vocab_size:
+                    bad = int(toks[(toks < 0) | (toks >= self.vocab_size)][0])
+            if bad is not None:
+                raise ValueError(f"request {e.req_id!r}: token id {bad} is outside the vocabulary of {self.vocab_size}")
+            arrays.append(toks)
             if any(not 0 <= int(w) < n for w in e.want):
                 raise ValueError(f"request {e.req_id!r}: a wanted place is outside its {n} tokens")
             if self.length(e.req_id) + n > self.max_model_len:
@@ -122,7 +134,7 @@ class ModelRunner:
                 raise OutOfSlots(f"{new} new requests but only {self.cache.free_slots()} free request slots")
             raise OutOfPages(f"the step needs more pages than the {self.cache.free_pages()} that are free")
         segs = []
-        for e in entries:
+        for e, toks in zip(entries, arrays):
             first = not self.cache.has(e.req_id)
             if first:
                 self.cache.admit(e.req_id)
@@ -130,7 +142,7 @@ class ModelRunner:
             assert ok, "reservation was checked for the whole step"
             if not build:
                 continue
-            segs.append(dict(tokens=[int(t) for t in e.tokens], pos0=self.cache.length(e.req_id),
+            segs.append(dict(tokens=toks, pos0=self.cache.length(e.req_id),
                              slot=self.cache.slot(e.req_id), want=[int(w) for w in e.want], first=first,
                              rid=(e.req_id, self.cache.epoch(e.req_id))))
         if not build:
