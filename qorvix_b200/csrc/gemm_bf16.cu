@@ -32,6 +32,7 @@ struct GemmArgs {
   int kblocks_per_split;
   int splits;
   const uint8_t* packed;   // the weight matrix as 16 KB tiles (see qv_pack_weight_tiles), or null
+  int bn;                  // persistent kernel: columns of a tile (a multiple of 16, at most its BN)
 };
 
 // BN: columns of the accumulator (rows of the narrow operand per tile).  SWAP: the wide operand
@@ -306,6 +307,46 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
   }
 }
 
+// One row's 32 accumulator columns from `col` on go to C: as they are (the first `ncols` of them),
+// or, with the fused activation, as the 16 values silu(gate) * up of the features col/2 ...
+template <typename TC, bool SWIGLU>
+__device__ __forceinline__ void store_chunk(TC* C, int ldc, int row, int col, int ncols, const uint32_t* r) {
+  if (SWIGLU) {
+    TC* dst = C + (size_t)row * ldc + (col >> 1);
+    float a[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) a[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r[16 + j]));
+    if (sizeof(TC) == 2 && (((uintptr_t)dst) & 15) == 0) {
+      uint32_t w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = pack2_bf16(a[2 * j], a[2 * j + 1]);
+      ((uint4*)dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      ((uint4*)dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) store_out<TC>(dst + j, a[j]);
+    }
+  } else {
+    TC* dst = C + (size_t)row * ldc + col;
+    if (sizeof(TC) == 2 && ncols >= 32 && (((uintptr_t)dst) & 15) == 0) {
+      uint4* d4 = (uint4*)dst;
+#pragma unroll
+      for (int v = 0; v < 4; ++v)
+        d4[v] = make_uint4(pack2_bf16(__uint_as_float(r[v * 8]), __uint_as_float(r[v * 8 + 1])),
+                           pack2_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3])),
+                           pack2_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5])),
+                           pack2_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7])));
+    } else if (sizeof(TC) == 4 && ncols >= 32 && (((uintptr_t)dst) & 15) == 0) {
+      float4* d4 = (float4*)dst;
+#pragma unroll
+      for (int v = 0; v < 8; ++v)
+        d4[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+    } else {
+      for (int j = 0; j < 32 && j < ncols; ++j) store_out<TC>(dst + j, __uint_as_float(r[j]));
+    }
+  }
+}
+
 // ---------------------------------------------------------------- many tokens: persistent kernel
 // One CTA per SM walks over 128 x BN output tiles (tile = blockIdx.x, + gridDim.x, ...; token tiles
 // fastest, so that CTAs running at the same time share a weight tile in L2).  The accumulator is
@@ -330,7 +371,8 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int M = args.rows_wide, N = args.rows_narrow;
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int bn = args.bn;                            // columns of a tile: at most BN, the ring's room
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
   const int total_tiles = tiles_m * tiles_n;
   const int num_kb = (args.K + BK - 1) / BK;
 
@@ -352,20 +394,25 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
 
   if (warp == 0) {
     if (lane == 0) {
-      // Arms stage s and requests the BN weight rows from n0 for k block kb: one tensor tile, or,
-      // from a packed matrix, BN/128 of its 16 KB tiles (a last tile that does not exist is left out;
-      // its columns are never stored).
-      const int w_tiles = (N + BM - 1) / BM;
+      // Arms stage s and requests the bn weight rows from n0 for k block kb: one tensor tile, or,
+      // from a packed matrix, the rows' share of each 16 KB tile they lie in (eight rows are 1 KB
+      // of a tile, so rows from a multiple of 16 are a contiguous piece that lands on a swizzle
+      // boundary; rows past the last tile are left out: their columns are never stored).
+      const int w_rows = ((N + BM - 1) / BM) * BM;
       auto load_w = [&](int s, int kb, int n0) {
         uint8_t* dst = tiles + s * STAGE_BYTES + A_BYTES;
         if (args.packed) {
-          const int t0 = n0 / BM;
-          const int nt = (w_tiles - t0) < BN / BM ? (w_tiles - t0) : BN / BM;
-          mbar_expect_tx(&full[s], A_BYTES + nt * A_BYTES);
-          for (int j = 0; j < nt; ++j)
-            bulk_load_1d(dst + j * A_BYTES, args.packed + ((size_t)(t0 + j) * num_kb + kb) * (size_t)A_BYTES, &full[s], A_BYTES);
+          const int end = n0 + bn < w_rows ? n0 + bn : w_rows;
+          mbar_expect_tx(&full[s], A_BYTES + (end - n0) * (BK * 2));
+          for (int row = n0; row < end;) {
+            const int t = row / BM, r0 = row % BM;
+            const int n = (end - t * BM < BM ? end - t * BM : BM) - r0;
+            bulk_load_1d(dst + (row - n0) * (BK * 2), args.packed + ((size_t)t * num_kb + kb) * (size_t)A_BYTES + r0 * (BK * 2),
+                         &full[s], n * (BK * 2));
+            row += n;
+          }
         } else {
-          mbar_expect_tx(&full[s], STAGE_BYTES);
+          mbar_expect_tx(&full[s], A_BYTES + bn * (BK * 2));
           tma_load_2d(dst, &map_w, &full[s], kb * BK, n0);
         }
       };
@@ -373,7 +420,7 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
       int it = 0;
       bool first = true;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * bn;
         int kb = 0;
         if (first) {
           const int pre = num_kb < STAGES ? num_kb : STAGES;
@@ -398,7 +445,7 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(BM, BN);
+      const uint32_t idesc = umma_idesc(BM, bn);
       int it = 0, local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
@@ -431,7 +478,7 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
     int local = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
       const int b = local & 1;
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * bn;
       // every thread polls: the arrivals below need all 128 of them, timed out or not
       const bool ok = mbar_wait(&acc_full[b], (local >> 1) & 1, args.err, 3);
       tc_fence_after();
@@ -439,46 +486,12 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN);
       if (ok) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c0 = 0; c0 < bn; c0 += 32) {
           uint32_t r[32];
-          tmem_ld32(taddr + c0, r);
+          tmem_ld32(taddr + c0, r);                  // a last chunk of 16 columns reads on into unused ones
           tmem_wait_ld();
           if (row >= M || n0 + c0 >= N) continue;
-          if (SWIGLU) {
-            TC* dst = C + (size_t)row * args.ldc + ((n0 + c0) >> 1);
-            float a[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) a[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r[16 + j]));
-            if (sizeof(TC) == 2 && (((uintptr_t)dst) & 15) == 0) {
-              uint32_t w[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) w[j] = pack2_bf16(a[2 * j], a[2 * j + 1]);
-              ((uint4*)dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-              ((uint4*)dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) store_out<TC>(dst + j, a[j]);
-            }
-          } else {
-            TC* dst = C + (size_t)row * args.ldc + n0 + c0;
-            const int ncols = N - (n0 + c0);
-            if (sizeof(TC) == 2 && ncols >= 32 && (((uintptr_t)dst) & 15) == 0) {
-              uint4* d4 = (uint4*)dst;
-#pragma unroll
-              for (int v = 0; v < 4; ++v)
-                d4[v] = make_uint4(pack2_bf16(__uint_as_float(r[v * 8]), __uint_as_float(r[v * 8 + 1])),
-                                   pack2_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3])),
-                                   pack2_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5])),
-                                   pack2_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7])));
-            } else if (sizeof(TC) == 4 && ncols >= 32 && (((uintptr_t)dst) & 15) == 0) {
-              float4* d4 = (float4*)dst;
-#pragma unroll
-              for (int v = 0; v < 8; ++v)
-                d4[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-            } else {
-              for (int j = 0; j < 32 && j < ncols; ++j) store_out<TC>(dst + j, __uint_as_float(r[j]));
-            }
-          }
+          store_chunk<TC, SWIGLU>(C, args.ldc, row, n0 + c0, (N - (n0 + c0)) < (bn - c0) ? (N - (n0 + c0)) : (bn - c0), r);
         }
       }
       tc_fence_before();
@@ -491,6 +504,209 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- many tokens: CTA pairs
+// The two CTAs of a cluster share one 256 x 256 tile: each loads its 128 token rows and 128 of the
+// 256 weight rows (32 KB per k block of 64 instead of the 48 KB a 128 x 256 tile takes for the same
+// MMA work per SM), and tcgen05.mma.cta_group::2, issued by the pair's first CTA, multiplies them out of both
+// CTAs' shared memory into both CTAs' tensor memory (128 rows x 256 columns each, double-buffered).
+// The second CTA's MMA warp tells the first when its stage has landed; commits free a stage and
+// hand over an accumulator in both CTAs at once; each CTA's epilogue warps store their own rows.
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster.  Without
+// .release.cluster: that form made every arrive wait about 0.8 us for a cluster-wide fence, and the
+// arrivals here publish nothing the arriving thread wrote itself (a stage that the copy engine
+// filled; an accumulator that tcgen05.ld has drained, ordered by tcgen05.fence::before_thread_sync).
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+      "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}"
+      ::"r"(smem_u32(bar)), "r"(rank) : "memory");
+}
+__device__ __forceinline__ void umma2_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives, when the MMAs issued so far are done, on the barrier at this offset in both CTAs of the pair
+__device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
+
+template <int STAGES, typename TC, bool SWIGLU>
+__global__ void __launch_bounds__(192) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                           const __grid_constant__ CUtensorMap map_w,
+                                                           const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int BN = 256;                            // columns of the pair's tile; each CTA loads half the weight rows
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int STAGE_BYTES = 2 * A_BYTES;           // 128 token rows + 128 weight rows
+  constexpr int TMEM_COLS = 2 * BN;
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + STAGES * STAGE_BYTES);
+  uint64_t* peer_full = full + STAGES;               // first CTA: the second CTA's stage has landed
+  uint64_t* empty = peer_full + STAGES;
+  uint64_t* acc_full = empty + STAGES;               // [2]
+  uint64_t* acc_empty = acc_full + 2;                // [2], first CTA: both CTAs' epilogues arrive here
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const int M = args.rows_wide, N = args.rows_narrow;
+  const int pairs_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN - 1) / BN;
+  const int total_tiles = pairs_m * tiles_n;
+  const int num_kb = (args.K + BK - 1) / BK;
+  const int first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&peer_full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 256); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  cluster_sync_all();                                // both CTAs' barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int w_tiles = (N + BM - 1) / BM;
+      // Arms stage s and requests this CTA's 128 weight rows of k block kb (rows past the last
+      // packed tile are left out: their columns are never stored).
+      auto load_w = [&](int s, int kb, int nrow0) {
+        uint8_t* dst = tiles + s * STAGE_BYTES + A_BYTES;
+        if (args.packed) {
+          const int t = nrow0 / BM;
+          mbar_expect_tx(&full[s], t < w_tiles ? 2 * A_BYTES : A_BYTES);
+          if (t < w_tiles) bulk_load_1d(dst, args.packed + ((size_t)t * num_kb + kb) * (size_t)A_BYTES, &full[s], A_BYTES);
+        } else {
+          mbar_expect_tx(&full[s], 2 * A_BYTES);
+          tma_load_2d(dst, &map_w, &full[s], kb * BK, nrow0);
+        }
+      };
+      int it = 0;
+      bool first = true;
+      for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
+        const int m0 = (tile % pairs_m) * 2 * BM + (int)rank * BM;
+        const int nrow0 = (tile / pairs_m) * BN + (int)rank * BM;
+        int kb = 0;
+        if (first) {                                 // the first stages' weight tiles do not depend on the kernel ahead
+          const int pre = num_kb < STAGES ? num_kb : STAGES;
+          for (int k = 0; k < pre; ++k) load_w(k, k, nrow0);
+          pdl_wait();
+          for (int k = 0; k < pre; ++k) tma_load_2d(tiles + k * STAGE_BYTES, &map_x, &full[k], k * BK, m0);
+          kb = pre;
+          it = pre;
+          first = false;
+        }
+        bool ok = true;
+        for (; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, args.err, 1)) { ok = false; break; }
+          load_w(s, kb, nrow0);
+          tma_load_2d(tiles + s * STAGE_BYTES, &map_x, &full[s], kb * BK, m0);
+        }
+        if (!ok) break;
+      }
+      if (first) pdl_wait();
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc(2 * BM, BN);
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++local) {
+        const int b = local & 1;
+        // both CTAs' epilogues must have drained this accumulator (two tiles ago)
+        ok = mbar_wait(&acc_empty[b], ((local >> 1) & 1) ^ 1, args.err, 4);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&full[s], ph, args.err, 2) && mbar_wait(&peer_full[s], ph, args.err, 5);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
+          const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk)
+            umma2_f16(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          umma2_commit_both(&empty[s]);
+        }
+        umma2_commit_both(&acc_full[b]);
+      }
+    } else if (lane == 0) {
+      // second CTA: pass each landed stage on to the first CTA's MMA thread
+      int it = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(&full[s], (it / STAGES) & 1, args.err, 6);
+          if (!ok) break;
+          mbar_arrive_remote(&peer_full[s], 0);
+        }
+      }
+    }
+  } else {
+    pdl_wait();                                      // C may still be in use by the kernel ahead
+    const int q = warp & 3;
+    TC* C = (TC*)args.C;
+    int local = 0;
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++local) {
+      const int b = local & 1;
+      const int m0 = (tile % pairs_m) * 2 * BM + (int)rank * BM, n0 = (tile / pairs_m) * BN;
+      // every thread polls: the arrivals below need all of them, timed out or not
+      const bool ok = mbar_wait(&acc_full[b], (local >> 1) & 1, args.err, 3);
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN);
+      if (ok) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c0, r);
+          tmem_wait_ld();
+          if (row >= M || n0 + c0 >= N) continue;
+          store_chunk<TC, SWIGLU>(C, args.ldc, row, n0 + c0, N - (n0 + c0), r);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_remote(&acc_empty[b], 0);          // the first CTA's barrier counts both CTAs' 128 threads
+      if (!ok) break;
+    }
+    tc_fence_before();
+  }
+  // neither CTA may leave while the other can still arrive on its barriers or its MMAs read its memory
+  tc_fence_before();
+  __syncwarp();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -526,12 +742,59 @@ int launch_persistent(const CUtensorMap& mx, const CUtensorMap& mw, const GemmAr
   return qv_launch(gemm_tc_persistent_kernel<BN, STAGES, TC, SWIGLU>, dim3(ctas), dim3(192), (size_t)smem, st, mx, mw, args);
 }
 
+template <int STAGES, typename TC, bool SWIGLU>
+int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& args, int total_tiles, cudaStream_t st) {
+  constexpr int smem = STAGES * (2 * BM * BK * 2) + 1024 + 256;
+  static bool configured = false;
+  static int clusters = 0;
+  auto kernel = gemm_tc_pair_kernel<STAGES, TC, SWIGLU>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    // how many pairs the device holds at once (an SM without a free neighbour in its GPC stays out)
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2 * 74); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters <= 0) { cudaGetLastError(); return QV_ERR_UNSUPPORTED; }
+    configured = true;
+  }
+  const int n = total_tiles < clusters ? total_tiles : clusters;
+  return qv_launch_cluster(kernel, dim3(2 * n), dim3(192), (size_t)smem, st, dim3(2, 1, 1), mx, mw, args);
+}
+
 }  // namespace
 
-// Which kernel serves more than 64 tokens: 0 (default) the persistent one with 128 x 256 tiles,
-// 1 the one-tile-per-CTA kernel with 128 x 128 tiles (kept for comparison and tests).
+// Which kernel serves more than 64 tokens: 0 (default) the persistent one-CTA kernel (128 x 256 or
+// 128 x 128 tiles); 1 the one-tile-per-CTA kernel with 128 x 128 tiles; 3 CTA pairs on 256 x 256 tiles
+// where there are more than 128 tokens.  1 and 3 are kept for comparison and tests: the pairs halve
+// the weight bytes an SM takes in, but at these sizes the MMA rate under the power cap, not the
+// fill, sets the pace, and they measure 2-6 % behind (8 % ahead only for 4,096 x 6,144 x 4,096).
 static int g_prefill_variant = 0;
 extern "C" void qv_gemm_bf16_set_prefill_variant(int v) { g_prefill_variant = v; }
+
+// Columns of the persistent kernel's tiles: 0 (default) chooses per product, else the given width
+// (a multiple of 16, of 32 with the fused activation, at most 256; for comparison and tests).
+static int g_prefill_bn = 0;
+extern "C" void qv_gemm_bf16_set_prefill_bn(int v) { g_prefill_bn = v; }
+
+// The tile width of a product.  A k block of a 128 x bn tile costs a fixed part worth about 500
+// columns beside its bn columns (measured: the shared-memory fill, not the MMA, sets the pace), so
+// the widest tile wins unless half-width tiles still fit in one wave of CTAs, which then finishes
+// sooner (4096 x 14336 at 512 tokens: 76.9 us at 128 columns, 88.1 us at 256).
+static int choose_tile_width(int tiles_m, int N, int step) {
+  (void)step;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  return tiles_m * ((N + 127) / 128) <= sms ? 128 : 256;
+}
 
 // C (bf16 or f32) [M,N] = A (bf16) [M,K] * W (bf16) [N,K]^T.  Returns QV_ERR_UNSUPPORTED for shapes
 // the tensor-core path does not take (the caller then uses the CUDA-core kernel):
@@ -547,7 +810,7 @@ static int gemm_bf16_entry(void* C, const void* A, const void* W, const void* pa
   if (c_dt != QV_DT_BF16 && c_dt != QV_DT_F32) return QV_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   GemmArgs args;
-  args.C = C; args.err = err; args.packed = nullptr;
+  args.C = C; args.err = err; args.packed = nullptr; args.bn = 0;
   args.K = K; args.ldc = ldc;
   const int total_kb = (K + BK - 1) / BK;
   CUtensorMap mw, mn;
@@ -588,12 +851,28 @@ static int gemm_bf16_entry(void* C, const void* A, const void* W, const void* pa
   if (!W && !packed) return QV_ERR_UNSUPPORTED;
   args.packed = (const uint8_t*)packed;
   args.rows_wide = M; args.rows_narrow = N; args.kblocks_per_split = total_kb; args.splits = 1;
-  if (g_prefill_variant == 0) {
-    // persistent kernel, 128 x 256 tiles, accumulator double-buffered in tensor memory
+  if (g_prefill_variant == 0 || g_prefill_variant == 3) {
+    const int step = epilogue == 1 ? 32 : 16;
+    int bn = g_prefill_bn > 0 ? g_prefill_bn : choose_tile_width((M + BM - 1) / BM, N, step);
+    if (g_prefill_variant == 3 && M > BM) {
+      // CTA pairs, 256 x 256 tiles
+      if (!make_map(&mw, A, M, K, lda, BM)) return QV_ERR_UNSUPPORTED;
+      if (packed) mn = mw;
+      else if (!make_map(&mn, W, N, K, ldw, BM)) return QV_ERR_UNSUPPORTED;
+      const int pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+      int rc;
+      if (epilogue == 1) rc = launch_pair<6, bf16, true>(mw, mn, args, pair_tiles, st);
+      else if (c_dt == QV_DT_BF16) rc = launch_pair<6, bf16, false>(mw, mn, args, pair_tiles, st);
+      else rc = launch_pair<6, float, false>(mw, mn, args, pair_tiles, st);
+      if (rc != QV_ERR_UNSUPPORTED) return rc;
+    }
+    // persistent kernel, 128 x bn tiles, accumulator double-buffered in tensor memory
+    if (bn < step || bn > 256 || bn % step) return QV_ERR_UNSUPPORTED;
+    args.bn = bn;
     if (!make_map(&mw, A, M, K, lda, BM)) return QV_ERR_UNSUPPORTED;
     if (packed) mn = mw;
-    else if (!make_map(&mn, W, N, K, ldw, 256)) return QV_ERR_UNSUPPORTED;
-    const int total_tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
+    else if (!make_map(&mn, W, N, K, ldw, bn)) return QV_ERR_UNSUPPORTED;
+    const int total_tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
     if (epilogue == 1) return launch_persistent<256, 4, bf16, true>(mw, mn, args, total_tiles, st);
     if (c_dt == QV_DT_BF16) return launch_persistent<256, 4, bf16, false>(mw, mn, args, total_tiles, st);
     return launch_persistent<256, 4, float, false>(mw, mn, args, total_tiles, st);

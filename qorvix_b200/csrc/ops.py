@@ -30,7 +30,13 @@ def _ptr(t):
     return c_void_p(0) if t is None else c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current stream's handle (the raw getter costs a fraction of building a Stream object)."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -226,9 +232,16 @@ def gemm_bf16_packed(c, a, packed, N: int, force_splits: int = 0, swiglu: bool =
 
 
 def gemm_bf16_set_prefill_variant(variant: int) -> None:
-    """0 (default): more than 64 tokens run on the persistent kernel (128 x 256 tiles, double-buffered
-    accumulator); 1: on the one-tile-per-CTA kernel (128 x 128 tiles)."""
+    """0 (default): more than 64 tokens run on the persistent kernel (128 x 256 or 128 x 128 tiles,
+    double-buffered accumulator); 1: on the one-tile-per-CTA kernel (128 x 128 tiles); 3: on CTA pairs
+    (tcgen05.mma.cta_group::2, 256 x 256 tiles) where there are more than 128 tokens."""
     load_library("gemm_bf16").qv_gemm_bf16_set_prefill_variant(c_int(variant))
+
+
+def gemm_bf16_set_prefill_tile_width(bn: int) -> None:
+    """Columns of the persistent kernel's tiles: 0 (default) lets each product choose, else a multiple
+    of 16 (32 with the fused activation) up to 256.  For comparison and tests."""
+    load_library("gemm_bf16").qv_gemm_bf16_set_prefill_bn(c_int(bn))
 
 
 def check_kernel_errors() -> None:
@@ -349,11 +362,19 @@ def decode_variant(T: int, Hkv: int) -> int:
 
 def decode_splits(T: int, Hkv: int, max_ctx: int) -> int:
     """How many slices of the keys each (token, kv head) is cut into: about three CTAs per SM for the
-    per-thread-load kernel, two (each with 64 KB of keys and values in flight) and at least 256 keys
-    a slice for the bulk-copy kernel; a function of the step's shape only (a captured step keeps it)."""
+    per-thread-load kernel; for the bulk-copy kernel (two CTAs per SM, each with 64 KB of keys and
+    values in flight, at least 256 keys a slice) the count whose waves of CTAs take the least time.
+    A function of the step's shape only (a captured step keeps it)."""
     pairs = max(1, T * Hkv)
     if decode_variant(T, Hkv) == 0:
-        return max(1, min(16, (2 * 148) // pairs, max_ctx // 256))
+        # 296 CTAs run at once; a CTA's time is its slice of the keys plus a fixed part worth about
+        # 256 keys.  The count that needs the least time over all waves, the smaller one on a tie.
+        best, best_cost = 1, None
+        for s in range(1, max(1, min(16, max_ctx // 256)) + 1):
+            cost = -(-pairs * s // 296) * (-(-max_ctx // s) + 256)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = s, cost
+        return best
     return max(1, min(16, -(-3 * 148 // pairs), -(-max_ctx // 64)))
 
 

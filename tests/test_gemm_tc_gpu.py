@@ -27,7 +27,8 @@ def check(M, N, K, out_dtype, force_splits=0, lda=None):
     assert err <= tol * max(1.0, ref.abs().max().item()), f"M={M} N={N} K={K}: max err {err}"
 
 
-@pytest.mark.parametrize("variant", [0, 1])        # 0: persistent 128x256 kernel; 1: one 128x128 tile per CTA
+# 0: persistent kernel; 1: one 128x128 tile per CTA; 3: CTA pairs (tcgen05.mma.cta_group::2) on 256x256 tiles
+@pytest.mark.parametrize("variant", [0, 1, 3])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 256), (256, 384, 4096), (200, 1000, 328),
                                    (2048, 6144, 4096), (65, 136, 72), (300, 331, 1000), (4000, 2000, 136)])
@@ -37,6 +38,25 @@ def test_many_tokens(M, N, K, out_dtype, variant):
         check(M, N, K, out_dtype)
     finally:
         ops.gemm_bf16_set_prefill_variant(0)
+
+
+@pytest.mark.parametrize("bn", [16, 48, 112, 128, 144, 240, 256])
+@pytest.mark.parametrize("M,N,K", [(300, 1000, 520), (129, 272, 64), (512, 5120, 1024), (200, 336, 136)])
+def test_many_tokens_at_every_tile_width(M, N, K, bn):
+    """The persistent kernel's tile width is a run-time value (a product picks 128 or 256): any multiple of
+    16 gives the same product, from packed tiles (pieces of one to three tiles per stage) and from rows."""
+    ops.gemm_bf16_set_prefill_tile_width(bn)
+    try:
+        check(M, N, K, torch.float32)
+        a, w = rnd(M, K, seed=M + K), rnd(N, K, seed=N + 1, scale=0.05)
+        c = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        assert ops.gemm_bf16_packed(c, a, ops.pack_weight(w), N)
+        torch.cuda.synchronize()
+        ops.check_kernel_errors()
+        ref = a.double() @ w.double().t()
+        assert (c.double() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    finally:
+        ops.gemm_bf16_set_prefill_tile_width(0)
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
@@ -75,7 +95,16 @@ def test_strided_activations_and_refused_shapes():
 
 @pytest.mark.parametrize("M,f,K", [(8, 256, 128), (3, 14336, 256), (40, 512, 4096), (64, 1008, 72), (128, 64, 64),
                                    (300, 1008, 328), (2048, 1024, 512)])
-def test_fused_swiglu_epilogue(M, f, K):
+@pytest.mark.parametrize("variant", [0, 3])
+def test_fused_swiglu_epilogue(M, f, K, variant):
+    ops.gemm_bf16_set_prefill_variant(variant)
+    try:
+        _fused_swiglu_epilogue(M, f, K)
+    finally:
+        ops.gemm_bf16_set_prefill_variant(0)
+
+
+def _fused_swiglu_epilogue(M, f, K):
     g, u = rnd(f, K, seed=5, scale=0.1), rnd(f, K, seed=6, scale=0.1)
     w = torch.stack([g.view(f // 16, 16, K), u.view(f // 16, 16, K)], dim=1).reshape(2 * f, K).contiguous()
     a = rnd(M, K, seed=7)
