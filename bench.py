@@ -38,6 +38,22 @@ LLAMA31_8B = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden_
                   tie_word_embeddings=False, hidden_act="silu")
 
 
+LLAMA32_1B = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden_size=2048, intermediate_size=8192,
+                  num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+                  max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=500000.0,
+                  rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                    original_max_position_embeddings=8192),
+                  tie_word_embeddings=True, hidden_act="silu")
+
+LLAMA2_13B = dict(architectures=["LlamaForCausalLM"], vocab_size=32000, hidden_size=5120, intermediate_size=13824,
+                  num_hidden_layers=40, num_attention_heads=40, num_key_value_heads=40, head_dim=128,
+                  max_position_embeddings=4096, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False,
+                  hidden_act="silu")
+
+SHAPES = {"llama31_8b": ("Llama-3.1-8B shape", LLAMA31_8B), "llama32_1b": ("Llama-3.2-1B shape", LLAMA32_1B),
+          "llama2_13b": ("Llama-2-13B shape", LLAMA2_13B)}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.isfile(path):
@@ -114,6 +130,9 @@ def main() -> int:
     ap.add_argument("--ctx", type=int, default=1024)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--shape", default="llama31_8b", choices=sorted(SHAPES), help="the other shapes the baseline names")
+    ap.add_argument("--mixed", action="store_true",
+                    help="also time mixed steps: a 512-token prompt portion beside 32 decoded tokens at 2,048-token contexts")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -132,7 +151,8 @@ def main() -> int:
     from qorvix_b200.weights import random_tensors
 
     pk = peaks()
-    raw = dict(LLAMA31_8B)
+    model_name, shape = SHAPES[args.shape]
+    raw = dict(shape)
     full_layers = raw["num_hidden_layers"]
     if args.layers:
         raw["num_hidden_layers"] = args.layers
@@ -140,11 +160,13 @@ def main() -> int:
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     B, ctx, K, W = args.batch, args.ctx, args.steps, args.warmup
-    pool_tokens = max(64 * (ctx + K + W + 64), args.prefill_tokens + 64, B * (ctx + 2 * (K + W) + 64))
+    max_len = min(8192, cfg.max_position_embeddings)
+    pool_tokens = max(64 * (ctx + K + W + 64), args.prefill_tokens + 64, B * (ctx + 2 * (K + W) + 64 + (-(-B * ctx // 4096) + B)),
+                      34 * (2048 + 256) if args.mixed else 0, 0 if args.skip_points else B * (max_len + 64))
     t0 = time.time()
     tensors = dict(random_tensors(cfg, seed=0, device=dev, dtype=torch.bfloat16))
     llm = LLM(config=cfg, tensors=tensors, dtype="bfloat16", max_tokens=pool_tokens, max_concurrent=64,
-              max_batch_tokens=4096, max_model_len=8192, device=dev)
+              max_batch_tokens=4096, max_model_len=max_len, device=dev)
     del tensors
     runner = llm.runner
     torch.cuda.synchronize()
@@ -215,12 +237,41 @@ def main() -> int:
         for b in (1, 64):
             ms, _ = decode_device(b, ctx, max(16, K // 2), W)
             points[f"decode_b{b}"] = b / (ms / 1e3)
-        ms, _ = decode_device(B, 8192 - 64, max(16, K // 2), W)      # the longest context the configuration names
-        points[f"decode_b{B}_ctx8192"] = B / (ms / 1e3)
+        ms, _ = decode_device(B, max_len - 64, max(16, K // 2), W)   # the longest context the configuration names
+        points[f"decode_b{B}_ctx{max_len}"] = B / (ms / 1e3)
+    if args.mixed:
+        # 32 requests decode at 2,048-token contexts while a 2,048-token prompt comes in 512 tokens a step
+        ids = list(range(2000, 2032))
+        for i in ids:
+            runner.step([StepEntry(i, prompt(2047), [])])
+        times = []
+        for rep in range(2):
+            p = prompt(2048)
+            for c in range(0, 2048, 512):
+                entries = [StepEntry(i, [1], [0]) for i in ids] + [StepEntry("mixed", p[c:c + 512], [511] if c == 1536 else [])]
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                runner.step(entries, end=["mixed"] if c == 1536 else [])
+                e1.record()
+                torch.cuda.synchronize()
+                if rep:
+                    times.append(e0.elapsed_time(e1))
+        for i in ids:
+            runner.release(i)
+        ms = statistics.median(times)
+        L_, H_, hd_ = cfg.num_hidden_layers, cfg.num_attention_heads, cfg.head_dim
+        flops = 544 * gemm_flops_per_token(cfg) + L_ * 4 * H_ * hd_ * (512 * 1024 + 32 * 2048) + 2 * 33 * cfg.vocab_size * cfg.hidden_size
+        nbytes = weight_bytes(cfg) + (32 * 2048 + 1024) * L_ * 2 * cfg.num_key_value_heads * hd_ * 2
+        points["mixed_512_prompt_32_decode"] = {"tokens_per_s": 544 / (ms / 1e3), "ms": ms,
+                                                "flops_ms_at_peak": flops / (pk["bf16_tflops"] * 1e12) * 1e3,
+                                                "bytes_ms_at_peak": nbytes / (pk["hbm_gbs"] * 1e9) * 1e3}
 
     # ---- end to end through the public API: host tokens in, sampled ids out, every step
     sched = llm.new_scheduler()
-    sp = SamplingParams.greedy_params(max_new_tokens=W + K + 8, ignore_eos=True)
+    # requests that are prefilled first decode while the others' prompts still come in: room for those rounds too
+    prefill_rounds = -(-B * ctx // 4096) + B
+    sp = SamplingParams.greedy_params(max_new_tokens=W + K + 8 + prefill_rounds, ignore_eos=True)
     for _ in range(B):
         sched.submit(prompt(ctx - 1), sp)
     while not sched.decoding():
@@ -242,16 +293,16 @@ def main() -> int:
            "ms_per_step": e2e_s / K * 1e3}
 
     out = {
-        "metric": "decode tok/s at batch 8, 1,024-token contexts (Llama-3.1-8B shape, random weights)",
+        "metric": f"decode tok/s at batch {B}, {ctx:,}-token contexts ({model_name}, random weights)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": step_ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": "Llama-3.1-8B shape", "layers": cfg.num_hidden_layers, "layers_full": full_layers,
+        "config": {"model": model_name, "layers": cfg.num_hidden_layers, "layers_full": full_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "global_batch": B, "seq_len": ctx, "max_model_len": 8192, "page_size": runner.page_size,
+                   "global_batch": B, "seq_len": ctx, "max_model_len": max_len, "page_size": runner.page_size,
                    "prefill_tokens": T, "parallelism": "single GPU", "weights": "random N(0,0.02) bf16",
-                   "l2": "inputs larger than L2 (weights 15 GB per step)", "load_s": round(load_s, 1)},
+                   "l2": f"inputs larger than L2 (weights {weight_bytes(cfg) / 1e9:.1f} GB per step)", "load_s": round(load_s, 1)},
         "clocks": clk, "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline, "points": points,
     }
     print(json.dumps(out))
