@@ -26,18 +26,63 @@ def dt_code(dtype: torch.dtype) -> int:
     raise KernelError(f"kernels take float32 or bfloat16, not {dtype}")
 
 
+# Every entry point's C signature.  With the types declared once, a call passes plain Python
+# numbers (None for a null pointer) and ctypes builds no wrapper object per argument.
+_V, _I, _F, _L = c_void_p, c_int, c_float, c_longlong
+_ARGTYPES = {
+    "qv_error_string": [_I],
+    "qv_embed": [_V, _V, _V, _I, _I, _I, _I, _V],
+    "qv_add_rmsnorm": [_V, _V, _V, _V, _V, _I, _I, _F, _I, _I, _I, _V],
+    "qv_rope_kv_write": [_V, _I, _V, _V, _I, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _V],
+    "qv_swiglu": [_V, _V, _I, _I, _I, _I, _V],
+    "qv_cast": [_V, _V, _L, _I, _I, _V],
+    "qv_gemm_simt": [_V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V],
+    "qv_gemm_bf16_tc": [_V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _V, _I, _I, _V],
+    "qv_packed_weight_bytes": [_I, _I],
+    "qv_pack_weight_tiles": [_V, _V, _I, _I, _I, _V],
+    "qv_gemm_bf16_packed": [_V, _V, _V, _I, _I, _I, _I, _I, _I, _V, _I, _I, _V],
+    "qv_gemm_bf16_set_prefill_variant": [_I],
+    "qv_gemm_bf16_set_prefill_bn": [_I],
+    "qv_attention_generic": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V],
+    "qv_attn_prefill_bf16": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V],
+    "qv_attn_prefill_tc": [_V, _I, _V, _I, _I, _V, _L, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _F, _V, _V],
+    "qv_attn_set_decode_variant": [_I],
+    "qv_attn_set_error_word": [_V],
+    "qv_attn_decode_bf16": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V, _V],
+    "qv_argmax": [_V, _V, _I, _I, _L, _V],
+    "qv_sample": [_V, _V, _I, _I, _L, _V, _V, _V, _V, _V, _V, _I, _V, _V, _V, _V],
+}
+_RESTYPES = {"qv_error_string": ctypes.c_char_p, "qv_packed_weight_bytes": c_longlong}
+_typed_libs = {}
+
+
+def _lib(name: str):
+    """The library `name` (compiled and loaded on first use) with its entry points' types declared."""
+    lib = _typed_libs.get(name)
+    if lib is None:
+        lib = load_library(name)
+        for fn, types in _ARGTYPES.items():
+            if hasattr(lib, fn):
+                f = getattr(lib, fn)
+                f.argtypes = types
+                f.restype = _RESTYPES.get(fn, c_int)
+        _typed_libs[name] = lib
+    return lib
+
+
 def _ptr(t):
-    return c_void_p(0) if t is None else c_void_p(t.data_ptr())
+    return None if t is None else t.data_ptr()
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_get_device = getattr(torch._C, "_cuda_getDevice", None)
 
 
 def _stream():
-    """The current stream's handle (the raw getter costs a fraction of building a Stream object)."""
-    if _raw_stream is not None:
-        return c_void_p(_raw_stream(torch.cuda.current_device()))
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current stream's handle (the raw getters cost a fraction of building a Stream object)."""
+    if _raw_stream is not None and _get_device is not None:
+        return _raw_stream(_get_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
 def _need_cuda(*tensors):
@@ -63,9 +108,8 @@ def _check(rc: int, what: str):
     global _launches
     _launches += 1
     if rc != 0:
-        lib = load_library("elementwise")
-        lib.qv_error_string.restype = ctypes.c_char_p
-        msg = lib.qv_error_string(c_int(rc)).decode()
+        lib = _lib("elementwise")
+        msg = lib.qv_error_string(rc).decode()
         raise KernelError(f"{what}: {msg} (code {rc})")
 
 
@@ -83,8 +127,8 @@ def embed(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
     T, d = out.shape
     assert out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous()
     assert table.shape[1] == d and ids.numel() >= T
-    rc = load_library("elementwise").qv_embed(_ptr(out), _ptr(table), _ptr(ids), c_int(T), c_int(d),
-                                              c_int(table.shape[0]), c_int(dt_code(table.dtype)), _stream())
+    rc = _lib("elementwise").qv_embed(
+        _ptr(out), _ptr(table), _ptr(ids), T, d, table.shape[0], dt_code(table.dtype), _stream())
     _check(rc, "embed")
 
 
@@ -104,10 +148,9 @@ def add_rmsnorm(out, residual, delta, weight, eps: float, row_idx=None, write_re
     else:
         assert residual.shape[0] >= rows
     ddt = dt_code(delta.dtype) if delta is not None else dt_code(out.dtype)
-    rc = load_library("elementwise").qv_add_rmsnorm(
-        _ptr(out), _ptr(residual), _ptr(delta), _ptr(weight), _ptr(row_idx), c_int(rows), c_int(d),
-        c_float(eps), c_int(1 if (write_residual and delta is not None) else 0), c_int(ddt),
-        c_int(dt_code(out.dtype)), _stream())
+    rc = _lib("elementwise").qv_add_rmsnorm(
+        _ptr(out), _ptr(residual), _ptr(delta), _ptr(weight), _ptr(row_idx), rows, d, eps, 1 if (write_residual and
+        delta is not None) else 0, ddt, dt_code(out.dtype), _stream())
     _check(rc, "add_rmsnorm")
 
 
@@ -125,11 +168,10 @@ def rope_kv_write(qkv, cache_layer, cos_sin, tok_pos, tok_seg, block_table, H, H
     if cache_layer is not None:
         assert cache_layer.dtype == qkv.dtype and cache_layer.is_contiguous()
         assert tuple(cache_layer.shape[1:]) == (2, Hkv, page, hd)
-    rc = load_library("elementwise").qv_rope_kv_write(
-        _ptr(qkv), c_int(qkv.stride(0)), _ptr(cache_layer), _ptr(cos_sin),
-        c_int(cos_sin.shape[0] if cos_sin is not None else 1),
-        _ptr(tok_pos), _ptr(tok_seg), _ptr(block_table), c_int(block_table.shape[-1]), c_int(T),
-        c_int(H), c_int(Hkv), c_int(hd), c_int(rot), c_int(page), c_int(dt_code(qkv.dtype)), _stream())
+    rc = _lib("elementwise").qv_rope_kv_write(
+        _ptr(qkv), qkv.stride(0), _ptr(cache_layer), _ptr(cos_sin), cos_sin.shape[0] if cos_sin is not None else 1,
+        _ptr(tok_pos), _ptr(tok_seg), _ptr(block_table), block_table.shape[-1], T, H, Hkv, hd, rot, page,
+        dt_code(qkv.dtype), _stream())
     _check(rc, "rope_kv_write")
 
 
@@ -139,16 +181,16 @@ def swiglu(out, gu, interleaved: bool = False) -> None:
     _need_cuda(out, gu)
     T, f = out.shape
     assert gu.shape == (T, 2 * f) and gu.is_contiguous() and out.is_contiguous() and gu.dtype == out.dtype
-    rc = load_library("elementwise").qv_swiglu(_ptr(out), _ptr(gu), c_int(T), c_int(f), c_int(1 if interleaved else 0),
-                                               c_int(dt_code(out.dtype)), _stream())
+    rc = _lib("elementwise").qv_swiglu(
+        _ptr(out), _ptr(gu), T, f, 1 if interleaved else 0, dt_code(out.dtype), _stream())
     _check(rc, "swiglu")
 
 
 def cast(out, src) -> None:
     _need_cuda(out, src)
     assert out.numel() == src.numel() and out.is_contiguous() and src.is_contiguous()
-    rc = load_library("elementwise").qv_cast(_ptr(out), _ptr(src), c_longlong(src.numel()),
-                                             c_int(dt_code(src.dtype)), c_int(dt_code(out.dtype)), _stream())
+    rc = _lib("elementwise").qv_cast(
+        _ptr(out), _ptr(src), src.numel(), dt_code(src.dtype), dt_code(out.dtype), _stream())
     _check(rc, "cast")
 
 
@@ -161,10 +203,9 @@ def gemm_simt(c, a, w, accumulate=False) -> None:
     N = w.shape[0]
     assert w.shape[1] == K and c.shape == (M, N)
     assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
-    rc = load_library("gemm_simt").qv_gemm_simt(
-        _ptr(c), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(w.stride(0)),
-        c_int(c.stride(0)), c_int(dt_code(a.dtype)), c_int(dt_code(w.dtype)), c_int(dt_code(c.dtype)),
-        c_int(1 if accumulate else 0), _stream())
+    rc = _lib("gemm_simt").qv_gemm_simt(
+        _ptr(c), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), dt_code(a.dtype),
+        dt_code(w.dtype), dt_code(c.dtype), 1 if accumulate else 0, _stream())
     _check(rc, "gemm_simt")
 
 
@@ -192,10 +233,9 @@ def gemm_bf16_tc(c, a, w, force_splits: int = 0, swiglu: bool = False) -> bool:
     assert c.shape == ((M, N // 2) if swiglu else (M, N))
     assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
     st = _tc_buffers(a.device)
-    rc = load_library("gemm_bf16").qv_gemm_bf16_tc(
-        _ptr(c), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(w.stride(0)),
-        c_int(c.stride(0)), c_int(dt_code(c.dtype)), _ptr(st["err"]), c_int(force_splits),
-        c_int(1 if swiglu else 0), _stream())
+    rc = _lib("gemm_bf16").qv_gemm_bf16_tc(
+        _ptr(c), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), dt_code(c.dtype),
+        _ptr(st["err"]), force_splits, 1 if swiglu else 0, _stream())
     if rc == -2:
         return False
     _check(rc, "gemm_bf16_tc")
@@ -208,10 +248,9 @@ def pack_weight(w: torch.Tensor) -> torch.Tensor:
     _need_cuda(w)
     assert w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1
     N, K = w.shape
-    lib = load_library("gemm_bf16")
-    lib.qv_packed_weight_bytes.restype = c_longlong
-    out = torch.empty(lib.qv_packed_weight_bytes(c_int(N), c_int(K)) // 2, device=w.device, dtype=torch.bfloat16)
-    _check(lib.qv_pack_weight_tiles(_ptr(out), _ptr(w), c_int(N), c_int(K), c_int(w.stride(0)), _stream()), "pack_weight_tiles")
+    lib = _lib("gemm_bf16")
+    out = torch.empty(lib.qv_packed_weight_bytes(N, K) // 2, device=w.device, dtype=torch.bfloat16)
+    _check(lib.qv_pack_weight_tiles(_ptr(out), _ptr(w), N, K, w.stride(0), _stream()), "pack_weight_tiles")
     return out
 
 
@@ -222,9 +261,9 @@ def gemm_bf16_packed(c, a, packed, N: int, force_splits: int = 0, swiglu: bool =
     assert a.dtype == torch.bfloat16 and packed.dtype == torch.bfloat16
     assert c.shape == ((M, N // 2) if swiglu else (M, N)) and a.stride(1) == 1 and c.stride(1) == 1
     st = _tc_buffers(a.device)
-    rc = load_library("gemm_bf16").qv_gemm_bf16_packed(
-        _ptr(c), _ptr(a), _ptr(packed), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(c.stride(0)),
-        c_int(dt_code(c.dtype)), _ptr(st["err"]), c_int(force_splits), c_int(1 if swiglu else 0), _stream())
+    rc = _lib("gemm_bf16").qv_gemm_bf16_packed(
+        _ptr(c), _ptr(a), _ptr(packed), M, N, K, a.stride(0), c.stride(0), dt_code(c.dtype), _ptr(st["err"]),
+        force_splits, 1 if swiglu else 0, _stream())
     if rc == -2:
         return False
     _check(rc, "gemm_bf16_packed")
@@ -235,13 +274,13 @@ def gemm_bf16_set_prefill_variant(variant: int) -> None:
     """0 (default): more than 64 tokens run on the persistent kernel (128 x 256 or 128 x 128 tiles,
     double-buffered accumulator); 1: on the one-tile-per-CTA kernel (128 x 128 tiles); 3: on CTA pairs
     (tcgen05.mma.cta_group::2, 256 x 256 tiles) where there are more than 128 tokens."""
-    load_library("gemm_bf16").qv_gemm_bf16_set_prefill_variant(c_int(variant))
+    _lib("gemm_bf16").qv_gemm_bf16_set_prefill_variant(variant)
 
 
 def gemm_bf16_set_prefill_tile_width(bn: int) -> None:
     """Columns of the persistent kernel's tiles: 0 (default) lets each product choose, else a multiple
     of 16 (32 with the fused activation) up to 256.  For comparison and tests."""
-    load_library("gemm_bf16").qv_gemm_bf16_set_prefill_bn(c_int(bn))
+    _lib("gemm_bf16").qv_gemm_bf16_set_prefill_bn(bn)
 
 
 def check_kernel_errors() -> None:
@@ -263,10 +302,9 @@ def attention_generic(out, q, cache_layer, tok_pos, tok_seg, block_table, H, Hkv
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == cache_layer.dtype
     assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (2, Hkv, page, hd)
     _i32(tok_pos, "tok_pos"); _i32(tok_seg, "tok_seg"); _i32(block_table, "block_table")
-    rc = load_library("attention_generic").qv_attention_generic(
-        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(cache_layer), _ptr(tok_pos),
-        _ptr(tok_seg), _ptr(block_table), c_int(block_table.shape[-1]), c_int(T), c_int(H), c_int(Hkv),
-        c_int(hd), c_int(page), c_int(window), c_float(scale), c_int(dt_code(q.dtype)), _stream())
+    rc = _lib("attention_generic").qv_attention_generic(
+        _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_layer), _ptr(tok_pos), _ptr(tok_seg),
+        _ptr(block_table), block_table.shape[-1], T, H, Hkv, hd, page, window, scale, dt_code(q.dtype), _stream())
     _check(rc, "attention_generic")
 
 
@@ -317,10 +355,9 @@ def attention_prefill_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_tab
     assert q.stride(1) == 1 and out.stride(1) == 1 and cache_layer.is_contiguous()
     assert tuple(cache_layer.shape[1:]) == (2, Hkv, page, hd)
     _i32(seg_q_start, "seg_q_start"); _i32(seg_pos0, "seg_pos0"); _i32(block_table, "block_table")
-    rc = load_library("attention_bf16").qv_attn_prefill_bf16(
-        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(cache_layer), _ptr(seg_q_start), _ptr(seg_pos0),
-        _ptr(block_table), c_int(block_table.shape[-1]), c_int(S), c_int(max_q_len), c_int(H), c_int(Hkv), c_int(hd),
-        c_int(page), c_int(window), c_float(scale), c_int(variant), _stream())
+    rc = _lib("attention_bf16").qv_attn_prefill_bf16(
+        _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_layer), _ptr(seg_q_start), _ptr(seg_pos0),
+        _ptr(block_table), block_table.shape[-1], S, max_q_len, H, Hkv, hd, page, window, scale, variant, _stream())
     if rc == -2:
         return False
     _check(rc, "attention_prefill_bf16")
@@ -337,11 +374,10 @@ def attention_prefill_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table
     assert tuple(cache_layer.shape[1:]) == (2, Hkv, page, hd)
     _i32(seg_q_start, "seg_q_start"); _i32(seg_pos0, "seg_pos0"); _i32(block_table, "block_table")
     st = _tc_buffers(q.device)
-    rc = load_library("attention_tc").qv_attn_prefill_tc(
-        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), c_int(q.shape[0]), _ptr(cache_layer),
-        c_longlong(cache_layer.shape[0]), _ptr(seg_q_start), _ptr(seg_pos0), _ptr(block_table),
-        c_int(block_table.shape[-1]), c_int(S), c_int(max_q_len), c_int(H), c_int(Hkv), c_int(hd), c_int(page),
-        c_int(window), c_float(scale), _ptr(st["err"]), _stream())
+    rc = _lib("attention_tc").qv_attn_prefill_tc(
+        _ptr(out), out.stride(0), _ptr(q), q.stride(0), q.shape[0], _ptr(cache_layer), cache_layer.shape[0],
+        _ptr(seg_q_start), _ptr(seg_pos0), _ptr(block_table), block_table.shape[-1], S, max_q_len, H, Hkv, hd, page,
+        window, scale, _ptr(st["err"]), _stream())
     if rc == -2:
         return False
     _check(rc, "attention_prefill_tc")
@@ -390,16 +426,16 @@ def attention_decode_bf16(out, q, cache_layer, tok_pos, tok_seg, block_table, H,
     partial = None
     if splits > 1:
         partial = torch.empty(T * H * splits * (hd + 2), dtype=torch.float32, device=q.device)
-    lib = load_library("attention_bf16")
-    lib.qv_attn_set_decode_variant(c_int(decode_variant(T, Hkv)))
+    lib = _lib("attention_bf16")
+    lib.qv_attn_set_decode_variant(decode_variant(T, Hkv))
     if not getattr(lib, "_qv_err_set", False):
         # the word that the kernel's bounded waits report into (see check_kernel_errors)
         lib.qv_attn_set_error_word(_ptr(_tc_buffers(q.device)["err"]))
         lib._qv_err_set = True
-    rc = lib.qv_attn_decode_bf16(
-        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(cache_layer), _ptr(tok_pos), _ptr(tok_seg),
-        _ptr(block_table), c_int(block_table.shape[-1]), c_int(T), c_int(H), c_int(Hkv), c_int(hd), c_int(page),
-        c_int(window), c_float(scale), c_int(splits), _ptr(partial), _stream())
+    rc = lib.qv_attn_decode_bf16(_ptr(
+        out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_layer), _ptr(tok_pos), _ptr(tok_seg),
+        _ptr(block_table), block_table.shape[-1], T, H, Hkv, hd, page, window, scale, splits, _ptr(partial),
+        _stream())
     if rc == -2:
         return False
     _check(rc, "attention_decode_bf16")
@@ -463,8 +499,8 @@ def argmax(out_ids, logits) -> None:
     _need_cuda(out_ids, logits)
     _i32(out_ids, "out_ids")
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out_ids.numel() >= logits.shape[0]
-    rc = load_library("sampling").qv_argmax(_ptr(out_ids), _ptr(logits), c_int(logits.shape[0]),
-                                            c_int(logits.shape[1]), c_longlong(logits.stride(0)), _stream())
+    rc = _lib("sampling").qv_argmax(
+        _ptr(out_ids), _ptr(logits), logits.shape[0], logits.shape[1], logits.stride(0), _stream())
     _check(rc, "argmax")
 
 
@@ -485,8 +521,8 @@ def sample(out_ids, logits, temperature, top_k, top_p, min_p, uniform, recent=No
         recent_n = recent.shape[1]
         for t in (rep_pen, freq_pen, pres_pen):
             assert t is not None and t.dtype == torch.float32 and t.numel() >= rows
-    rc = load_library("sampling").qv_sample(
-        _ptr(out_ids), _ptr(logits), c_int(rows), c_int(V), c_longlong(logits.stride(0)), _ptr(temperature),
-        _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform), _ptr(recent), c_int(recent_n), _ptr(rep_pen),
-        _ptr(freq_pen), _ptr(pres_pen), _stream())
+    rc = _lib("sampling").qv_sample(
+        _ptr(out_ids), _ptr(logits), rows, V, logits.stride(0), _ptr(temperature), _ptr(top_k), _ptr(top_p),
+        _ptr(min_p), _ptr(uniform), _ptr(recent), recent_n, _ptr(rep_pen), _ptr(freq_pen), _ptr(pres_pen),
+        _stream())
     _check(rc, "sample")
