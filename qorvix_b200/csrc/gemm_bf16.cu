@@ -35,6 +35,18 @@ struct GemmArgs {
   int bn;                  // persistent kernel: columns of a tile (a multiple of 16, at most its BN)
 };
 
+// What the fused rotary epilogue of the QKV product needs: C's columns are H query heads, Hkv key
+// heads and Hkv value heads of hd dims; query and key heads are rotated (all hd dims, in split-half
+// pairs) by the angles of the token's position, keys and values go to the token's slot in its page.
+struct RopeArgs {
+  const float2* cos_sin;   // [table_rows][hd / 2] of (cos, sin)
+  const int* tok_pos;
+  const int* tok_seg;
+  const int* block_table;  // [segments][max_blocks]
+  bf16* cache;             // the layer's pages: [page][2][Hkv][page_size][hd]
+  int table_rows, max_blocks, H, Hkv, hd, page_size;
+};
+
 // BN: columns of the accumulator (rows of the narrow operand per tile).  SWAP: the wide operand
 // is the weight matrix (features) and the narrow one the tokens, so the tile is C^T.
 // SWIGLU: the weight rows come in groups of 32 (16 gate rows, then the 16 up rows of the same
@@ -347,16 +359,78 @@ __device__ __forceinline__ void store_chunk(TC* C, int ldc, int row, int col, in
   }
 }
 
+// The fused rotary epilogue for one token row of a tile: heads of hd (64 or 128) columns from column
+// n0 of C.  Every thread of the warp runs the tensor-memory loads; only rows of real tokens store.
+template <int HD>
+__device__ __forceinline__ void rope_store_row(const RopeArgs& ra, bf16* C, int ldc, uint32_t taddr, int row, bool live,
+                                               int n0, int bn, int N) {
+  constexpr int HALF = HD / 2;
+  const float2* cs = nullptr;
+  bf16* kdst = nullptr;
+  if (live) {
+    const int pos = ra.tok_pos[row];
+    cs = ra.cos_sin + (size_t)(pos < ra.table_rows ? pos : ra.table_rows - 1) * HALF;
+    const int pg = ra.block_table[(size_t)ra.tok_seg[row] * ra.max_blocks + pos / ra.page_size];
+    kdst = ra.cache + (size_t)pg * ((size_t)2 * ra.Hkv * ra.page_size * HD) + (size_t)(pos % ra.page_size) * HD;
+  }
+#pragma unroll 1
+  for (int h0 = 0; h0 < bn && n0 + h0 < N; h0 += HD) {
+    const int head = (n0 + h0) / HD;
+    if (head < ra.H + ra.Hkv) {
+      bf16* dst = nullptr;
+      if (live) dst = head < ra.H ? C + (size_t)row * ldc + (size_t)head * HD : kdst + (size_t)(head - ra.H) * ra.page_size * HD;
+#pragma unroll 1
+      for (int c = 0; c < HALF; c += 32) {
+        uint32_t lo[32], hi[32];
+        tmem_ld32(taddr + h0 + c, lo);
+        tmem_ld32(taddr + h0 + HALF + c, hi);
+        tmem_wait_ld();
+        if (!live) continue;
+        uint32_t olo[16], ohi[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float4 t = *(const float4*)(cs + c + i);     // (cos, sin) of two neighbouring pairs
+          const float a0 = __uint_as_float(lo[i]), a1 = __uint_as_float(lo[i + 1]);
+          const float b0 = __uint_as_float(hi[i]), b1 = __uint_as_float(hi[i + 1]);
+          olo[i >> 1] = pack2_bf16(a0 * t.x - b0 * t.y, a1 * t.z - b1 * t.w);
+          ohi[i >> 1] = pack2_bf16(a0 * t.y + b0 * t.x, a1 * t.w + b1 * t.z);
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          ((uint4*)(dst + c))[v] = make_uint4(olo[4 * v], olo[4 * v + 1], olo[4 * v + 2], olo[4 * v + 3]);
+          ((uint4*)(dst + HALF + c))[v] = make_uint4(ohi[4 * v], ohi[4 * v + 1], ohi[4 * v + 2], ohi[4 * v + 3]);
+        }
+      }
+    } else {
+      bf16* dst = nullptr;
+      if (live) dst = kdst + (size_t)ra.Hkv * ra.page_size * HD + (size_t)(head - ra.H - ra.Hkv) * ra.page_size * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(taddr + h0 + c, r);
+        tmem_wait_ld();
+        if (!live) continue;
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+          ((uint4*)(dst + c))[v] = make_uint4(pack2_bf16(__uint_as_float(r[v * 8]), __uint_as_float(r[v * 8 + 1])),
+                                              pack2_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3])),
+                                              pack2_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5])),
+                                              pack2_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7])));
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- many tokens: persistent kernel
 // One CTA per SM walks over 128 x BN output tiles (tile = blockIdx.x, + gridDim.x, ...; token tiles
 // fastest, so that CTAs running at the same time share a weight tile in L2).  The accumulator is
 // double-buffered in tensor memory (2 x BN columns): while the four epilogue warps drain tile i,
 // the MMA warp already accumulates tile i+1, and the TMA warp runs ahead of both through the
 // shared-memory ring.
-template <int BN, int STAGES, typename TC, bool SWIGLU>
+template <int BN, int STAGES, typename TC, bool SWIGLU, bool ROPE = false>
 __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                  const __grid_constant__ CUtensorMap map_w,
-                                                                 const GemmArgs args) {
+                                                                 const GemmArgs args, const RopeArgs rope) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int A_BYTES = BM * BK * 2;
   constexpr int B_BYTES = BN * BK * 2;
@@ -484,7 +558,10 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN);
-      if (ok) {
+      if (ok && ROPE) {
+        if (rope.hd == 128) rope_store_row<128>(rope, (bf16*)args.C, args.ldc, taddr, row, row < M, n0, bn, N);
+        else rope_store_row<64>(rope, (bf16*)args.C, args.ldc, taddr, row, row < M, n0, bn, N);
+      } else if (ok) {
 #pragma unroll 1
         for (int c0 = 0; c0 < bn; c0 += 32) {
           uint32_t r[32];
@@ -724,13 +801,14 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mn, const GemmArgs& args, d
   return qv_launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, grid, dim3(192), (size_t)smem, st, dim3(1, 1, grid.z), mw, mn, args);
 }
 
-template <int BN, int STAGES, typename TC, bool SWIGLU>
-int launch_persistent(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& args, int total_tiles, cudaStream_t st) {
+template <int BN, int STAGES, typename TC, bool SWIGLU, bool ROPE = false>
+int launch_persistent(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& args, int total_tiles, cudaStream_t st,
+                      const RopeArgs& rope = RopeArgs()) {
   constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
   static bool configured = false;
   static int sms = 0;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, TC, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, TC, SWIGLU, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -739,7 +817,7 @@ int launch_persistent(const CUtensorMap& mx, const CUtensorMap& mw, const GemmAr
     configured = true;
   }
   const int ctas = total_tiles < sms ? total_tiles : sms;
-  return qv_launch(gemm_tc_persistent_kernel<BN, STAGES, TC, SWIGLU>, dim3(ctas), dim3(192), (size_t)smem, st, mx, mw, args);
+  return qv_launch(gemm_tc_persistent_kernel<BN, STAGES, TC, SWIGLU, ROPE>, dim3(ctas), dim3(192), (size_t)smem, st, mx, mw, args, rope);
 }
 
 template <int STAGES, typename TC, bool SWIGLU>
@@ -885,6 +963,40 @@ static int gemm_bf16_entry(void* C, const void* A, const void* W, const void* pa
   if (epilogue == 1) return launch<128, 3, false, bf16, true>(mw, mn, args, grid, st);
   if (c_dt == QV_DT_BF16) return launch<128, 3, false, bf16>(mw, mn, args, grid, st);
   return launch<128, 3, false, float>(mw, mn, args, grid, st);
+}
+
+// The QKV projection of more than 64 tokens with the rotation of query and key heads and the write
+// of keys and values into the paged cache done in the product's epilogue (from the float32
+// accumulators; the separate pass over the product's output is saved).  C [M, (H + 2 Hkv) hd] gets
+// the rotated query heads; its key and value columns are left unwritten.  Head sizes 64 and 128 with
+// all dims rotated; QV_ERR_UNSUPPORTED otherwise (the caller then runs the product and the rotation
+// as two kernels).
+extern "C" int qv_gemm_bf16_qkv_rope(void* C, const void* A, const void* packed, int M, int K, int lda, int ldc, int* err,
+                                     const float* cos_sin, int table_rows, const int* tok_pos, const int* tok_seg,
+                                     const int* block_table, int max_blocks, void* cache, int H, int Hkv, int hd, int page_size,
+                                     void* stream) {
+  if (M <= 64 || g_prefill_variant != 0 || !packed || !cache || !cos_sin) return QV_ERR_UNSUPPORTED;
+  if ((hd != 64 && hd != 128) || H <= 0 || Hkv <= 0 || page_size <= 0 || table_rows <= 0) return QV_ERR_UNSUPPORTED;
+  const long long n_ll = (long long)(H + 2 * Hkv) * hd;
+  if (n_ll > 0x7fffffffLL) return QV_ERR_TOO_LARGE;
+  const int N = (int)n_ll;
+  if (K < 8 || (K & 7) || (lda & 7) || (ldc & 7) || ldc < N) return QV_ERR_UNSUPPORTED;
+  if (((uintptr_t)A & 15) || ((uintptr_t)C & 15) || ((uintptr_t)packed & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)cos_sin & 15))
+    return QV_ERR_UNSUPPORTED;
+  GemmArgs args;
+  args.C = C; args.err = err; args.packed = (const uint8_t*)packed;
+  args.K = K; args.ldc = ldc;
+  args.rows_wide = M; args.rows_narrow = N; args.kblocks_per_split = (K + BK - 1) / BK; args.splits = 1;
+  args.bn = g_prefill_bn > 0 ? g_prefill_bn : choose_tile_width((M + BM - 1) / BM, N, 16);
+  if (args.bn > 256 || args.bn % hd) return QV_ERR_UNSUPPORTED;      // whole heads per tile
+  RopeArgs ra;
+  ra.cos_sin = (const float2*)cos_sin; ra.tok_pos = tok_pos; ra.tok_seg = tok_seg; ra.block_table = block_table;
+  ra.cache = (bf16*)cache; ra.table_rows = table_rows; ra.max_blocks = max_blocks;
+  ra.H = H; ra.Hkv = Hkv; ra.hd = hd; ra.page_size = page_size;
+  CUtensorMap mx;
+  if (!make_map(&mx, A, M, K, lda, BM)) return QV_ERR_UNSUPPORTED;
+  const int total_tiles = ((M + BM - 1) / BM) * ((N + args.bn - 1) / args.bn);
+  return launch_persistent<256, 4, bf16, false, true>(mx, mx, args, total_tiles, (cudaStream_t)stream, ra);
 }
 
 extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,

@@ -41,6 +41,7 @@ _ARGTYPES = {
     "qv_packed_weight_bytes": [_I, _I],
     "qv_pack_weight_tiles": [_V, _V, _I, _I, _I, _V],
     "qv_gemm_bf16_packed": [_V, _V, _V, _I, _I, _I, _I, _I, _I, _V, _I, _I, _V],
+    "qv_gemm_bf16_qkv_rope": [_V, _V, _V, _I, _I, _I, _I, _V, _V, _I, _V, _V, _V, _I, _V, _I, _I, _I, _I, _V],
     "qv_gemm_bf16_set_prefill_variant": [_I],
     "qv_gemm_bf16_set_prefill_bn": [_I],
     "qv_attention_generic": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V],
@@ -267,6 +268,32 @@ def gemm_bf16_packed(c, a, packed, N: int, force_splits: int = 0, swiglu: bool =
     if rc == -2:
         return False
     _check(rc, "gemm_bf16_packed")
+    return True
+
+
+def gemm_qkv_rope(qkv, x, packed, cache_layer, cos_sin, tok_pos, tok_seg, block_table, H, Hkv, hd, page) -> bool:
+    """The QKV projection of a step of more than 64 tokens with the rotation of q and k and the cache
+    write of k and v in the product's epilogue: qkv[:, :H*hd] gets the rotated queries, the key and value
+    columns of qkv are not written.  False (nothing written) when the sizes are not ones it takes: head
+    sizes other than 64 and 128, a partial rotation, few tokens, no packed weights."""
+    if x.dtype != torch.bfloat16 or qkv.dtype != torch.bfloat16 or packed is None or cos_sin is None:
+        return False
+    M, K = x.shape
+    if M <= 64 or cos_sin.shape[1] * 2 != hd or cache_layer.dtype != torch.bfloat16:
+        return False
+    _need_cuda(qkv, x, packed, cache_layer, cos_sin, tok_pos, tok_seg, block_table)
+    assert x.stride(1) == 1 and qkv.stride(1) == 1 and qkv.shape == (M, (H + 2 * Hkv) * hd)
+    assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (2, Hkv, page, hd)
+    assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
+    _i32(tok_pos, "tok_pos"); _i32(tok_seg, "tok_seg"); _i32(block_table, "block_table")
+    st = _tc_buffers(x.device)
+    rc = _lib("gemm_bf16").qv_gemm_bf16_qkv_rope(
+        _ptr(qkv), _ptr(x), _ptr(packed), M, K, x.stride(0), qkv.stride(0), _ptr(st["err"]), _ptr(cos_sin),
+        cos_sin.shape[0], _ptr(tok_pos), _ptr(tok_seg), _ptr(block_table), block_table.shape[-1], _ptr(cache_layer),
+        H, Hkv, hd, page, _stream())
+    if rc == -2:
+        return False
+    _check(rc, "gemm_qkv_rope")
     return True
 
 

@@ -44,20 +44,28 @@ class Attention(Mixer):
         T = x.shape[0]
         H, Hkv, hd = self.H, self.Hkv, self.hd
         own_kv = self.spec.kv_from is None
-        qkv = self.qkv_proj(x, out_dtype=self.rt.dtype)                     # [T, (H+2Hkv)*hd] or [T, H*hd]
         table = self.position.table() if self.position is not None else None
         bt = ctx.block_tables[cache.group]
-        if own_kv:
-            if table is not None:
-                ops.rope_kv_write(qkv, cache.tensor, table, ctx.tok_pos, ctx.tok_seg, bt, H, Hkv, hd,
-                                  table.shape[1] * 2, cache.page_size)
-            else:
-                if self.position is not None:
-                    self.position.apply(qkv, ctx, H, Hkv, hd)
-                ops.rope_kv_write(qkv, cache.tensor, None, ctx.tok_pos, ctx.tok_seg, bt,
-                                  H, Hkv, hd, 0, cache.page_size)
-        elif self.position is not None:
-            self.position.apply(qkv, ctx, H, 0, hd)
+        qkv = None
+        if own_kv and table is not None and T > 64 and self.rt.dtype == torch.bfloat16 and self.qkv_proj.packed is not None:
+            # many tokens: rotation and cache write in the projection's epilogue, where the kernel takes the sizes
+            qkv = torch.empty((T, (H + 2 * Hkv) * hd), device=x.device, dtype=self.rt.dtype)
+            if not ops.gemm_qkv_rope(qkv, x, self.qkv_proj.packed, cache.tensor, table, ctx.tok_pos, ctx.tok_seg, bt,
+                                     H, Hkv, hd, cache.page_size):
+                qkv = None
+        if qkv is None:
+            qkv = self.qkv_proj(x, out_dtype=self.rt.dtype)                 # [T, (H+2Hkv)*hd] or [T, H*hd]
+            if own_kv:
+                if table is not None:
+                    ops.rope_kv_write(qkv, cache.tensor, table, ctx.tok_pos, ctx.tok_seg, bt, H, Hkv, hd,
+                                      table.shape[1] * 2, cache.page_size)
+                else:
+                    if self.position is not None:
+                        self.position.apply(qkv, ctx, H, Hkv, hd)
+                    ops.rope_kv_write(qkv, cache.tensor, None, ctx.tok_pos, ctx.tok_seg, bt,
+                                      H, Hkv, hd, 0, cache.page_size)
+            elif self.position is not None:
+                self.position.apply(qkv, ctx, H, 0, hd)
         out = torch.empty((T, H * hd), device=x.device, dtype=self.rt.dtype)
         ops.attention(out, qkv[:, : H * hd], cache.tensor, ctx, bt, H, Hkv, hd, cache.page_size,
                       self.window, self.scale)

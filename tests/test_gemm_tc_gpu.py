@@ -169,3 +169,49 @@ def test_packed_weights_with_the_fused_swiglu_epilogue():
     assert ops.gemm_bf16_packed(o_tiles, a, ops.pack_weight(w), 2 * f, swiglu=True)
     ops.check_kernel_errors()
     assert torch.equal(o_rows, o_tiles)
+
+
+@pytest.mark.parametrize("H,Hkv,hd,T,d", [(4, 2, 128, 300, 256), (6, 2, 64, 129, 192), (8, 8, 64, 700, 512), (32, 8, 128, 2048, 1024)])
+def test_qkv_product_with_rotation_and_cache_write_in_its_epilogue(H, Hkv, hd, T, d):
+    """The fused product against the product followed by the rotary kernel: rotated queries in the
+    output, rotated keys and plain values in each token's page slot; tokens of several requests at
+    different positions, pages handed out in a shuffled order."""
+    page = 16
+    N = (H + 2 * Hkv) * hd
+    w = rnd(N, d, seed=11, scale=0.05)
+    x = rnd(T, d, seed=12)
+    g = torch.Generator().manual_seed(13)
+    lens = [T // 3, T - T // 3 - 5, 5]                       # three requests, the tokens of each contiguous
+    starts = [7, 0, 100]                                     # position of each request's first token in the step
+    pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).to(torch.int32)
+    seg = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).to(torch.int32)
+    blocks = [-(-(s + n) // page) for s, n in zip(starts, lens)]
+    perm = torch.randperm(sum(blocks), generator=g).to(torch.int32)
+    bt = torch.zeros(3, max(blocks), dtype=torch.int32)
+    o = 0
+    for i, nb in enumerate(blocks):
+        bt[i, :nb] = perm[o:o + nb]
+        o += nb
+    P = int(max(s + n for s, n in zip(starts, lens)))
+    ang = torch.arange(P, dtype=torch.float64)[:, None] * torch.exp(-torch.arange(hd // 2, dtype=torch.float64) * 0.3)[None, :]
+    table = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float().contiguous().to(DEV)
+    pos, seg, bt = pos.to(DEV), seg.to(DEV), bt.to(DEV)
+    cache_a = torch.zeros(sum(blocks) + 1, 2, Hkv, page, hd, device=DEV, dtype=torch.bfloat16)
+    cache_b = torch.zeros_like(cache_a)
+    qkv_a = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(qkv_a, x, w)
+    ops.rope_kv_write(qkv_a, cache_a, table, pos, seg, bt, H, Hkv, hd, hd, page)
+    qkv_b = torch.full((T, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    assert ops.gemm_qkv_rope(qkv_b, x, ops.pack_weight(w), cache_b, table, pos, seg, bt, H, Hkv, hd, page)
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    # the fused path rotates the float32 sums, the other one their bfloat16 roundings: equal within that rounding
+    scale = float(qkv_a[:, : H * hd].float().abs().max())
+    assert float((qkv_a[:, : H * hd].float() - qkv_b[:, : H * hd].float()).abs().max()) <= 2e-2 * scale
+    assert float((cache_a.float() - cache_b.float()).abs().max()) <= 2e-2 * max(1.0, float(cache_a.float().abs().max()))
+    assert float(cache_b.float().abs().sum()) > 0
+    # pages that no token of the step lies in stay untouched
+    touched = torch.zeros(sum(blocks) + 1, dtype=torch.bool)
+    for t in range(T):
+        touched[int(bt[int(seg[t]), int(pos[t]) // page])] = True
+    assert float(cache_b[~touched.to(DEV)].float().abs().sum()) == 0.0
