@@ -271,15 +271,22 @@ def gemm_bf16_packed(c, a, packed, N: int, force_splits: int = 0, swiglu: bool =
     return True
 
 
+def fused_rope_enabled(tokens: int) -> bool:
+    """Whether the QKV projection of a step of `tokens` tokens takes the rotation and the cache write
+    into its epilogue: above 64 tokens, unless QORVIX_FUSED_ROPE=0 (for comparison)."""
+    import os
+    return tokens > 64 and os.environ.get("QORVIX_FUSED_ROPE", "1") != "0"
+
+
 def gemm_qkv_rope(qkv, x, packed, cache_layer, cos_sin, tok_pos, tok_seg, block_table, H, Hkv, hd, page) -> bool:
-    """The QKV projection of a step of more than 64 tokens with the rotation of q and k and the cache
-    write of k and v in the product's epilogue: qkv[:, :H*hd] gets the rotated queries, the key and value
-    columns of qkv are not written.  False (nothing written) when the sizes are not ones it takes: head
-    sizes other than 64 and 128, a partial rotation, few tokens, no packed weights."""
+    """The QKV projection of more than 64 tokens with the rotation of q and k and the cache write of k
+    and v in the product's epilogue: qkv[:, :H*hd] gets the rotated queries, the key and value columns
+    of qkv are not written.  False (nothing written) when the sizes are not ones it takes: head sizes
+    other than 64 and 128, a partial rotation, no packed weights, 64 tokens or fewer."""
     if x.dtype != torch.bfloat16 or qkv.dtype != torch.bfloat16 or packed is None or cos_sin is None:
         return False
     M, K = x.shape
-    if M <= 64 or cos_sin.shape[1] * 2 != hd or cache_layer.dtype != torch.bfloat16:
+    if cos_sin.shape[1] * 2 != hd or cache_layer.dtype != torch.bfloat16:
         return False
     _need_cuda(qkv, x, packed, cache_layer, cos_sin, tok_pos, tok_seg, block_table)
     assert x.stride(1) == 1 and qkv.stride(1) == 1 and qkv.shape == (M, (H + 2 * Hkv) * hd)

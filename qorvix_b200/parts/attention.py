@@ -47,8 +47,9 @@ class Attention(Mixer):
         table = self.position.table() if self.position is not None else None
         bt = ctx.block_tables[cache.group]
         qkv = None
-        if own_kv and table is not None and T > 64 and self.rt.dtype == torch.bfloat16 and self.qkv_proj.packed is not None:
-            # many tokens: rotation and cache write in the projection's epilogue, where the kernel takes the sizes
+        if (own_kv and table is not None and self.rt.dtype == torch.bfloat16 and self.qkv_proj.packed is not None
+                and ops.fused_rope_enabled(T)):
+            # rotation and cache write in the projection's epilogue, where the kernel takes the sizes
             qkv = torch.empty((T, (H + 2 * Hkv) * hd), device=x.device, dtype=self.rt.dtype)
             if not ops.gemm_qkv_rope(qkv, x, self.qkv_proj.packed, cache.tensor, table, ctx.tok_pos, ctx.tok_seg, bt,
                                      H, Hkv, hd, cache.page_size):

@@ -171,7 +171,8 @@ def test_packed_weights_with_the_fused_swiglu_epilogue():
     assert torch.equal(o_rows, o_tiles)
 
 
-@pytest.mark.parametrize("H,Hkv,hd,T,d", [(4, 2, 128, 300, 256), (6, 2, 64, 129, 192), (8, 8, 64, 700, 512), (32, 8, 128, 2048, 1024)])
+@pytest.mark.parametrize("H,Hkv,hd,T,d", [(4, 2, 128, 300, 256), (6, 2, 64, 129, 192), (8, 8, 64, 700, 512), (32, 8, 128, 2048, 1024),
+                                         (3, 1, 64, 65, 136)])
 def test_qkv_product_with_rotation_and_cache_write_in_its_epilogue(H, Hkv, hd, T, d):
     """The fused product against the product followed by the rotary kernel: rotated queries in the
     output, rotated keys and plain values in each token's page slot; tokens of several requests at
@@ -181,7 +182,7 @@ def test_qkv_product_with_rotation_and_cache_write_in_its_epilogue(H, Hkv, hd, T
     w = rnd(N, d, seed=11, scale=0.05)
     x = rnd(T, d, seed=12)
     g = torch.Generator().manual_seed(13)
-    lens = [T // 3, T - T // 3 - 5, 5]                       # three requests, the tokens of each contiguous
+    lens = [T // 3, T - T // 3 - 3, 3]                       # three requests, the tokens of each contiguous
     starts = [7, 0, 100]                                     # position of each request's first token in the step
     pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).to(torch.int32)
     seg = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).to(torch.int32)
