@@ -430,12 +430,17 @@ def decode_variant(T: int, Hkv: int) -> int:
     return 0 if T * Hkv >= 32 else 1
 
 
-def decode_splits(T: int, Hkv: int, max_ctx: int) -> int:
+def decode_splits(T: int, Hkv: int, max_ctx: int, known: bool = True) -> int:
     """How many slices of the keys each (token, kv head) is cut into: about three CTAs per SM for the
     per-thread-load kernel; for the bulk-copy kernel (two CTAs per SM, each with 64 KB of keys and
-    values in flight, at least 256 keys a slice) the count whose waves of CTAs take the least time.
+    values in flight, at least 256 keys a slice) the count whose waves of CTAs take the least time
+    when max_ctx is the step's real longest context (`known`), else the count that fills one wave.
     A function of the step's shape only (a captured step keeps it)."""
     pairs = max(1, T * Hkv)
+    if decode_variant(T, Hkv) == 0 and not known:
+        # a captured step is replayed at contexts from a few keys up to max_ctx: one wave of CTAs, no
+        # more (more slices than that pay only at long contexts and cost up to a third at short ones)
+        return max(1, min(16, (2 * 148) // pairs, max_ctx // 256))
     if decode_variant(T, Hkv) == 0:
         # 296 CTAs run at once; a CTA's time is its slice of the keys plus a fixed part worth about
         # 256 keys.  The count that needs the least time over all waves, the smaller one on a tie.
@@ -503,7 +508,7 @@ def attention(out, q, cache_layer, ctx, block_table, H, Hkv, hd, page, window, s
     if q.dtype == torch.bfloat16:
         T = q.shape[0]
         if ctx.max_q_len == 1:
-            splits = decode_splits(T, Hkv, ctx.max_ctx_len)
+            splits = decode_splits(T, Hkv, ctx.max_ctx_len, known=not ctx.captured)
             if attention_decode_bf16(out, q, cache_layer, ctx.tok_pos, ctx.tok_seg, block_table, H, Hkv, hd, page,
                                      window, scale, splits):
                 return
@@ -514,7 +519,7 @@ def attention(out, q, cache_layer, ctx, block_table, H, Hkv, hd, page, window, s
             S = ctx.num_segments
             if n1 >= 4 and n1 < S:
                 rest_q = max(ctx.seg_len[n1:])
-                splits = decode_splits(n1, Hkv, ctx.max_ctx_len)
+                splits = decode_splits(n1, Hkv, ctx.max_ctx_len, known=not ctx.captured)
                 ok = attention_decode_bf16(out[:n1], q[:n1], cache_layer, ctx.tok_pos, ctx.tok_seg, block_table, H, Hkv,
                                            hd, page, window, scale, splits)
                 if ok and _attention_portions_bf16(out, q, cache_layer, ctx.seg_q_start[n1:], ctx.seg_pos0[n1:],
