@@ -4,9 +4,13 @@
 // tcgen05.ld for the epilogue.  The reference multiplies one row at a time on the CUDA cores
 // (cuda/src/cuda_backend.cu:291-312); this kernel is its replacement for both phases:
 //
-//   * many tokens (prefill): the token rows are the 128-row MMA operand, 128 weight rows the
-//     other; one CTA per 128x128 tile, two CTAs per SM so one tile's epilogue overlaps the
-//     other's main loop.
+//   * many tokens (prefill): the token rows are the 128-row MMA operand, 256 (or 128) weight
+//     rows the other; a persistent kernel, one CTA per SM walking over the tiles, with the
+//     accumulator double-buffered in tensor memory so that one tile's epilogue overlaps the next
+//     tile's main loop.  The epilogue may apply SwiGLU (gate/up projection) or rotate the query and
+//     key heads and write keys and values into the paged cache (QKV projection).  Two more
+//     kernels are kept for comparison: one 128x128 tile per CTA, and clusters of two CTAs on
+//     256x256 tiles (tcgen05.mma.cta_group::2).
 //   * few tokens (decode, M <= 64): operands are swapped.  128 weight rows are the 128-row MMA
 //     operand and the tokens (padded to 16/32/64) the narrow one, so every weight byte is
 //     streamed from HBM exactly once through a deep TMA ring.  Matrices with few row tiles are
