@@ -51,6 +51,20 @@ struct RopeArgs {
   int table_rows = 0, max_blocks = 0, H = 0, Hkv = 0, hd = 0, page_size = 0;
 };
 
+// The norm that follows or precedes a product of few tokens, folded into it (few-token kernel only).
+// After an output projection: the product is added into the float32 residual stream, C gets the
+// updated stream times the next norm's weight (bfloat16), and ssq_out the sums of squares of the
+// updated stream per tile of 128 features, [tiles][64 tokens].  Before a projection that reads such
+// a C: each token's sums are scaled by rsqrt(mean of squares + eps), which completes the RMS norm.
+struct NormArgs {
+  float* residual = nullptr;       // [tokens][ld_res]; null: the product is stored as it is
+  const float* norm_w = nullptr;
+  float* ssq_out = nullptr;
+  const float* ssq_in = nullptr;   // null: no scaling
+  int ld_res = 0, tiles_in = 0;
+  float inv_d = 0.f, eps = 0.f;
+};
+
 // BN: columns of the accumulator (rows of the narrow operand per tile).  SWAP: the wide operand
 // is the weight matrix (features) and the narrow one the tokens, so the tile is C^T.
 // SWIGLU: the weight rows come in groups of 32 (16 gate rows, then the 16 up rows of the same
@@ -61,7 +75,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(
 template <int BN, int STAGES, bool SWAP, typename TC, bool SWIGLU>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_wide,
                                                       const __grid_constant__ CUtensorMap map_narrow,
-                                                      const GemmArgs args) {
+                                                      const GemmArgs args, const NormArgs norm) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int A_BYTES = BM * BK * 2;
   constexpr int B_BYTES = BN * BK * 2;
@@ -73,6 +87,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
   uint64_t* accum = empty + STAGES;
   uint32_t* tmem_slot = (uint32_t*)(accum + 1);
   int* ok_slots = (int*)(tmem_slot + 1);  // one per epilogue warp
+  float* rs_s = (float*)(ok_slots + 4);   // [64] a token's rsqrt(mean of squares + eps), with NormArgs::ssq_in
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wide0 = blockIdx.x * BM;
@@ -154,6 +169,17 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     // epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31
     pdl_wait();                 // C may still be in use by the kernel ahead
     const int q = warp & 3;
+    if (SWAP && norm.ssq_in != nullptr && (args.splits == 1 || split == 0)) {
+      // while the main loop runs: each token's scale from the sums of squares the kernel ahead left
+      const int te = q * 32 + lane;
+      if (te < BN) {
+        const int t = narrow0 + te;
+        float ss = 0.f;
+        if (t < args.rows_narrow)
+          for (int k = 0; k < norm.tiles_in; ++k) ss += norm.ssq_in[k * 64 + t];
+        rs_s[te] = rsqrtf(ss * norm.inv_d + norm.eps);
+      }
+    }
     // one lane per warp polls; the four warps then agree, so that either all of them take the
     // barriers below or none does
     int ok_i = 1;
@@ -236,7 +262,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
               const int feat = ((wide0 + q * 32) >> 1) + (lane & 15);
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                const float mine = __uint_as_float(r[j]);
+                const float mine = __uint_as_float(r[j]) * (norm.ssq_in ? rs_s[c0 + j] : 1.f);
                 const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
                 const int t = narrow0 + c0 + j;
                 if (lane < 16 && frow && t < ntok) store_out<TC>(C + (size_t)t * args.ldc + feat, silu_mul(mine, other));
@@ -245,7 +271,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const int t = narrow0 + c0 + j;
-                if (t < ntok) store_out<TC>(C + (size_t)t * args.ldc + wide_row, __uint_as_float(r[j]));
+                if (t < ntok) store_out<TC>(C + (size_t)t * args.ldc + wide_row, __uint_as_float(r[j]) * (norm.ssq_in ? rs_s[c0 + j] : 1.f));
               }
             }
           }
@@ -282,14 +308,18 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
       const float* red = (const float*)tiles;
       const uint32_t red_addr = smem_u32(red);
       TC* C = (TC*)args.C;
-      if (wide_row < args.rows_wide) {
+      const bool valid = wide_row < args.rows_wide;
+      const bool to_stream = norm.residual != nullptr;        // add into the residual stream, hand on the next norm's input
+      float* part_s = (float*)tiles + BN * BM;                // after this CTA's own partial sums
+      const float wn = (to_stream && valid) ? norm.norm_w[wide_row] : 0.f;
+      if (valid || to_stream) {
         for (int j0 = 0; j0 < BN && narrow0 + j0 < ntok; j0 += 16) {
           float acc[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) acc[j] = red[(j0 + j) * BM + row];
+          for (int j = 0; j < 16; ++j) acc[j] = valid ? red[(j0 + j) * BM + row] : 0.f;
           // the other CTAs' partial sums, three CTAs' worth of loads in flight together (one trip
           // through distributed shared memory for up to four splits), added in split order
-          for (int s0 = 1; s0 < args.splits; s0 += 3) {
+          for (int s0 = 1; valid && s0 < args.splits; s0 += 3) {
             float v[3][16];
 #pragma unroll
             for (int q = 0; q < 3; ++q) {
@@ -308,10 +338,42 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll
               for (int j = 0; j < 16; ++j) acc[j] += v[q][j];
           }
+          if (norm.ssq_in != nullptr) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (narrow0 + j0 + j < ntok) store_out<TC>(C + (size_t)(narrow0 + j0 + j) * args.ldc + wide_row, acc[j]);
+            for (int j = 0; j < 16; ++j) acc[j] *= rs_s[j0 + j];
+          }
+          if (to_stream) {
+            float rv[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              rv[j] = (valid && narrow0 + j0 + j < ntok) ? norm.residual[(size_t)(narrow0 + j0 + j) * norm.ld_res + wide_row] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = narrow0 + j0 + j;
+              float sq = 0.f;
+              if (valid && t < ntok) {
+                const float r = rv[j] + acc[j];
+                norm.residual[(size_t)t * norm.ld_res + wide_row] = r;
+                store_out<TC>(C + (size_t)t * args.ldc + wide_row, r * wn);
+                sq = r * r;
+              }
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+              if (lane == 0) part_s[(warp & 3) * BN + j0 + j] = sq;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (narrow0 + j0 + j < ntok) store_out<TC>(C + (size_t)(narrow0 + j0 + j) * args.ldc + wide_row, acc[j]);
+          }
         }
+      }
+      if (to_stream) {
+        // the tile's sum of squares per token, the four warps' parts added in a fixed order
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int te = (warp & 3) * 32 + lane;
+        if (te < BN && narrow0 + te < ntok)
+          norm.ssq_out[(size_t)blockIdx.x * 64 + narrow0 + te] = part_s[te] + part_s[BN + te] + part_s[2 * BN + te] + part_s[3 * BN + te];
       }
     }
     asm volatile("barrier.cluster.arrive.release;" ::: "memory");
@@ -793,8 +855,9 @@ __global__ void __launch_bounds__(192) gemm_tc_pair_kernel(const __grid_constant
 
 // ---------------------------------------------------------------- host side
 template <int BN, int STAGES, bool SWAP, typename TC, bool SWIGLU = false>
-int launch(const CUtensorMap& mw, const CUtensorMap& mn, const GemmArgs& args, dim3 grid, cudaStream_t st) {
-  constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+int launch(const CUtensorMap& mw, const CUtensorMap& mn, const GemmArgs& args, dim3 grid, cudaStream_t st,
+           const NormArgs& norm = NormArgs()) {
+  constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 512;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -802,7 +865,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mn, const GemmArgs& args, d
     configured = true;
   }
   // split-K CTAs of a tile (grid.z of them) are one cluster
-  return qv_launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, grid, dim3(192), (size_t)smem, st, dim3(1, 1, grid.z), mw, mn, args);
+  return qv_launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, grid, dim3(192), (size_t)smem, st, dim3(1, 1, grid.z), mw, mn, args, norm);
 }
 
 template <int BN, int STAGES, typename TC, bool SWIGLU, bool ROPE = false>
@@ -1011,6 +1074,53 @@ extern "C" int qv_gemm_bf16_qkv_rope(void* C, const void* A, const void* packed,
   if (!make_map(&mx, A, M, K, lda, BM)) return QV_ERR_UNSUPPORTED;
   const int total_tiles = ((M + BM - 1) / BM) * ((N + args.bn - 1) / args.bn);
   return launch_persistent<256, 4, bf16, false, true>(mx, mx, args, total_tiles, (cudaStream_t)stream, ra);
+}
+
+// A product of up to 64 tokens with the neighbouring RMS norm folded in (see NormArgs).  With
+// `residual`: C [M,N] (bfloat16) = (residual += A W^T) * norm_w and ssq_out [ceil(N/128)][64] gets the
+// sums of squares; the product must be one that is split along K (its first CTA holds whole sums).
+// With `ssq_in` (tiles_in x 64, of a stream of 1/inv_d features): every token's sums are scaled by
+// rsqrt(mean of squares + eps) before they are stored (or, epilogue 1, before SwiGLU).
+// QV_ERR_UNSUPPORTED, with nothing written, for anything else.
+extern "C" int qv_gemm_bf16_norm(void* C, const void* A, const void* packed, int M, int N, int K, int lda, int ldc, int c_dt,
+                                 int* err, int epilogue, float* residual, int ld_res, const float* norm_w, float* ssq_out,
+                                 const float* ssq_in, int tiles_in, float inv_d, float eps, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 64 || !packed || (epilogue != 0 && epilogue != 1)) return QV_ERR_UNSUPPORTED;
+  if (epilogue == 1 && (c_dt != QV_DT_BF16 || (N & 31))) return QV_ERR_UNSUPPORTED;
+  if (c_dt != QV_DT_BF16 && c_dt != QV_DT_F32) return QV_ERR_UNSUPPORTED;
+  if (K < 8 || (K & 7) || (lda & 7)) return QV_ERR_UNSUPPORTED;
+  if (((uintptr_t)A & 15) || ((uintptr_t)packed & 15)) return QV_ERR_UNSUPPORTED;
+  if (residual && (!norm_w || !ssq_out || epilogue != 0 || c_dt != QV_DT_BF16 || ld_res < N)) return QV_ERR_UNSUPPORTED;
+  if (ssq_in && (tiles_in <= 0 || !(inv_d > 0.f))) return QV_ERR_UNSUPPORTED;
+  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  const int tiles = (N + BM - 1) / BM, total_kb = (K + BK - 1) / BK;
+  int per = 0;
+  const int splits = swap_splits(tiles, total_kb, epilogue, 0, &per);
+  if (residual && splits < 2) return QV_ERR_UNSUPPORTED;
+  GemmArgs args;
+  args.C = C; args.err = err; args.packed = (const uint8_t*)packed; args.bn = 0;
+  args.K = K; args.ldc = ldc;
+  args.rows_wide = N; args.rows_narrow = M; args.kblocks_per_split = per; args.splits = splits;
+  NormArgs na;
+  na.residual = residual; na.norm_w = norm_w; na.ssq_out = ssq_out; na.ssq_in = ssq_in;
+  na.ld_res = ld_res; na.tiles_in = tiles_in; na.inv_d = inv_d; na.eps = eps;
+  CUtensorMap mn;
+  if (!make_map(&mn, A, M, K, lda, bn)) return QV_ERR_UNSUPPORTED;
+  dim3 grid(tiles, 1, splits);
+  cudaStream_t st = (cudaStream_t)stream;
+#define NORM_LAUNCH(BN_, ST_)                                                                     \
+  (c_dt == QV_DT_BF16 ? launch<BN_, ST_, true, bf16>(mn, mn, args, grid, st, na) : launch<BN_, ST_, true, float>(mn, mn, args, grid, st, na))
+  if (epilogue == 1) {
+    if (bn == 16) return launch<16, 6, true, bf16, true>(mn, mn, args, grid, st, na);
+    if (bn == 32) return launch<32, 5, true, bf16, true>(mn, mn, args, grid, st, na);
+    return launch<64, 4, true, bf16, true>(mn, mn, args, grid, st, na);
+  }
+  const bool one_wave = tiles * splits <= 148;
+  if (bn == 16) return one_wave ? NORM_LAUNCH(16, 12) : NORM_LAUNCH(16, 6);
+  if (bn == 32) return one_wave ? NORM_LAUNCH(32, 10) : NORM_LAUNCH(32, 5);
+  return one_wave ? NORM_LAUNCH(64, 8) : NORM_LAUNCH(64, 4);
+#undef NORM_LAUNCH
 }
 
 extern "C" int qv_gemm_bf16_tc(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,

@@ -42,6 +42,7 @@ _ARGTYPES = {
     "qv_pack_weight_tiles": [_V, _V, _I, _I, _I, _V],
     "qv_gemm_bf16_packed": [_V, _V, _V, _I, _I, _I, _I, _I, _I, _V, _I, _I, _V],
     "qv_gemm_bf16_qkv_rope": [_V, _V, _V, _I, _I, _I, _I, _V, _V, _I, _V, _V, _V, _I, _V, _I, _I, _I, _I, _V],
+    "qv_gemm_bf16_norm": [_V, _V, _V, _I, _I, _I, _I, _I, _I, _V, _I, _V, _I, _V, _V, _V, _I, _F, _F, _V],
     "qv_gemm_bf16_set_prefill_variant": [_I],
     "qv_gemm_bf16_set_prefill_bn": [_I],
     "qv_attention_generic": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V],
@@ -268,6 +269,38 @@ def gemm_bf16_packed(c, a, packed, N: int, force_splits: int = 0, swiglu: bool =
     if rc == -2:
         return False
     _check(rc, "gemm_bf16_packed")
+    return True
+
+
+def gemm_bf16_norm(c, a, packed, N: int, swiglu: bool = False, residual=None, norm_weight=None, ssq_out=None,
+                   ssq_in=None, stream_width: int = 0, eps: float = 0.0) -> bool:
+    """A product of up to 64 tokens with the neighbouring RMS norm folded in.
+    residual (float32 [M, N]) given: residual += a w^T; c (bfloat16) = residual * norm_weight; ssq_out
+    (float32 [ceil(N/128), 64]) = sums of squares of the updated rows per tile of 128 features.
+    ssq_in (such sums of a stream of `stream_width` features) given: row t of a w^T is scaled by
+    rsqrt(sum(ssq_in[:, t]) / stream_width + eps) before it is stored (or goes through SwiGLU).
+    False, with nothing written, when the kernel does not take the product."""
+    _need_cuda(c, a, packed, residual, norm_weight, ssq_out, ssq_in)
+    M, K = a.shape
+    if M > 64 or a.dtype != torch.bfloat16 or packed is None:
+        return False
+    assert c.shape == ((M, N // 2) if swiglu else (M, N)) and a.stride(1) == 1 and c.stride(1) == 1
+    tiles_in = 0
+    if residual is not None:
+        assert residual.dtype == torch.float32 and residual.stride(1) == 1 and tuple(residual.shape) == (M, N)
+        assert norm_weight.dtype == torch.float32 and norm_weight.numel() == N
+        assert ssq_out.dtype == torch.float32 and ssq_out.is_contiguous() and tuple(ssq_out.shape) == (-(-N // 128), 64)
+    if ssq_in is not None:
+        assert ssq_in.dtype == torch.float32 and ssq_in.is_contiguous() and ssq_in.shape[1] == 64 and stream_width > 0
+        tiles_in = ssq_in.shape[0]
+    st = _tc_buffers(a.device)
+    rc = _lib("gemm_bf16").qv_gemm_bf16_norm(
+        _ptr(c), _ptr(a), _ptr(packed), M, N, K, a.stride(0), c.stride(0), dt_code(c.dtype), _ptr(st["err"]),
+        1 if swiglu else 0, _ptr(residual), residual.stride(0) if residual is not None else 0, _ptr(norm_weight),
+        _ptr(ssq_out), _ptr(ssq_in), tiles_in, 1.0 / stream_width if stream_width else 0.0, eps, _stream())
+    if rc == -2:
+        return False
+    _check(rc, "gemm_bf16_norm")
     return True
 
 

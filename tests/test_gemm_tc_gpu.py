@@ -216,3 +216,51 @@ def test_qkv_product_with_rotation_and_cache_write_in_its_epilogue(H, Hkv, hd, T
     for t in range(T):
         touched[int(bt[int(seg[t]), int(pos[t]) // page])] = True
     assert float(cache_b[~touched.to(DEV)].float().abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 512, 4096), (1, 4096, 4096), (33, 1000, 2048), (64, 264, 1024)])
+def test_few_tokens_product_added_to_the_stream_with_the_next_norms_input(M, N, K):
+    """residual += a w^T in the split-K product's epilogue; c = residual * norm weight; per tile of 128
+    features the sums of squares of the updated rows."""
+    a, w = rnd(M, K, seed=31), rnd(N, K, seed=32, scale=0.05)
+    g = torch.Generator().manual_seed(33)
+    base = torch.randn(M, N, generator=g).to(DEV)
+    nw = (1 + 0.1 * torch.randn(N, generator=g)).to(DEV)
+    res = base.clone()
+    c = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    tiles = -(-N // 128)
+    ssq = torch.full((tiles, 64), float("nan"), device=DEV)
+    assert ops.gemm_bf16_norm(c, a, ops.pack_weight(w), N, residual=res, norm_weight=nw, ssq_out=ssq)
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    ref = base.double() + a.double() @ w.double().t()
+    assert (res.double() - ref).abs().max().item() <= 2e-3 * max(1.0, ref.abs().max().item())
+    want_c = ref * nw.double()
+    assert (c.double() - want_c).abs().max().item() <= 2e-2 * max(1.0, want_c.abs().max().item())
+    pad = torch.zeros(M, tiles * 128, dtype=torch.float64, device=DEV)
+    pad[:, :N] = res.double() ** 2                            # of the stream as the kernel left it
+    want_ssq = pad.view(M, tiles, 128).sum(-1).t()            # [tiles, M]
+    assert (ssq[:, :M].double() - want_ssq).abs().max().item() <= 1e-4 * max(1.0, want_ssq.abs().max().item())
+
+
+@pytest.mark.parametrize("M,N,K,swiglu", [(8, 512, 4096, False), (8, 12800, 256, False), (40, 1024, 512, True), (3, 28672, 4096, True),
+                                          (64, 6144, 4096, False)])
+def test_few_tokens_product_scaled_by_the_norm_of_its_input(M, N, K, swiglu):
+    """Each token's sums times rsqrt(mean of squares + eps), the mean given as per-tile sums of squares."""
+    a, w = rnd(M, K, seed=41), rnd(N, K, seed=42, scale=0.05)
+    g = torch.Generator().manual_seed(43)
+    tiles_in, width, eps = 5, 600, 1e-5
+    ssq = (torch.rand(tiles_in, 64, generator=g) * 100).to(DEV)
+    rs = torch.rsqrt(ssq[:, :M].double().sum(0) / width + eps)            # [M]
+    prod = (a.double() @ w.double().t()) * rs[:, None]
+    if swiglu:
+        gate = prod.view(M, N // 32, 2, 16)[:, :, 0].reshape(M, N // 2)
+        up = prod.view(M, N // 32, 2, 16)[:, :, 1].reshape(M, N // 2)
+        ref = gate / (1 + torch.exp(-gate)) * up
+    else:
+        ref = prod
+    c = torch.full(tuple(ref.shape), float("nan"), device=DEV, dtype=torch.bfloat16)
+    assert ops.gemm_bf16_norm(c, a, ops.pack_weight(w), N, swiglu=swiglu, ssq_in=ssq, stream_width=width, eps=eps)
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    assert (c.double() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
