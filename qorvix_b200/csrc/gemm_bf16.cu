@@ -88,6 +88,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
   uint32_t* tmem_slot = (uint32_t*)(accum + 1);
   int* ok_slots = (int*)(tmem_slot + 1);  // one per epilogue warp
   float* rs_s = (float*)(ok_slots + 4);   // [64] a token's rsqrt(mean of squares + eps), with NormArgs::ssq_in
+  float* rs_part = rs_s + 64;             // [128] the threads' shares of the sums behind rs_s
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wide0 = blockIdx.x * BM;
@@ -114,6 +115,10 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_launch_dependents();
+  // NormArgs::residual: the stream's values for the first 16 tokens and the norm's weight, fetched by
+  // the first CTA's epilogue threads while the main loop runs
+  float stream0[16];
+  float norm_w0 = 0.f;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -170,15 +175,38 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     pdl_wait();                 // C may still be in use by the kernel ahead
     const int q = warp & 3;
     if (SWAP && norm.ssq_in != nullptr && (args.splits == 1 || split == 0)) {
-      // while the main loop runs: each token's scale from the sums of squares the kernel ahead left
+      // While the main loop runs: each token's scale from the sums of squares the kernel ahead left.
+      // The 128 threads share the loads (128 / BN threads a token, each every (128 / BN)-th tile, four
+      // loads in flight a thread), then one thread a token adds the parts in a fixed order.
+      constexpr int PER = 128 / BN;
       const int te = q * 32 + lane;
-      if (te < BN) {
-        const int t = narrow0 + te;
-        float ss = 0.f;
-        if (t < args.rows_narrow)
-          for (int k = 0; k < norm.tiles_in; ++k) ss += norm.ssq_in[k * 64 + t];
-        rs_s[te] = rsqrtf(ss * norm.inv_d + norm.eps);
+      const int tok = te % BN, part = te / BN;
+      const int t = narrow0 + tok;
+      float ss = 0.f;
+      if (t < args.rows_narrow) {
+        for (int k = part; k < norm.tiles_in; k += 4 * PER) {
+          float v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) v[u] = k + u * PER < norm.tiles_in ? norm.ssq_in[(k + u * PER) * 64 + t] : 0.f;
+          ss += (v[0] + v[1]) + (v[2] + v[3]);
+        }
       }
+      rs_part[te] = ss;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (te < BN) {
+        float tot = 0.f;
+#pragma unroll
+        for (int u = 0; u < PER; ++u) tot += rs_part[u * BN + te];
+        rs_s[te] = rsqrtf(tot * norm.inv_d + norm.eps);
+      }
+    }
+    if (SWAP && norm.residual != nullptr && split == 0) {
+      const int wr = wide0 + q * 32 + lane;
+      const bool v = wr < args.rows_wide;
+      norm_w0 = v ? norm.norm_w[wr] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        stream0[j] = (v && narrow0 + j < args.rows_narrow) ? norm.residual[(size_t)(narrow0 + j) * norm.ld_res + wr] : 0.f;
     }
     // one lane per warp polls; the four warps then agree, so that either all of them take the
     // barriers below or none does
@@ -311,7 +339,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
       const bool valid = wide_row < args.rows_wide;
       const bool to_stream = norm.residual != nullptr;        // add into the residual stream, hand on the next norm's input
       float* part_s = (float*)tiles + BN * BM;                // after this CTA's own partial sums
-      const float wn = (to_stream && valid) ? norm.norm_w[wide_row] : 0.f;
+      const float wn = norm_w0;
       if (valid || to_stream) {
         for (int j0 = 0; j0 < BN && narrow0 + j0 < ntok; j0 += 16) {
           float acc[16];
@@ -344,9 +372,14 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
           }
           if (to_stream) {
             float rv[16];
+            if (j0 == 0) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              rv[j] = (valid && narrow0 + j0 + j < ntok) ? norm.residual[(size_t)(narrow0 + j0 + j) * norm.ld_res + wide_row] : 0.f;
+              for (int j = 0; j < 16; ++j) rv[j] = stream0[j];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                rv[j] = (valid && narrow0 + j0 + j < ntok) ? norm.residual[(size_t)(narrow0 + j0 + j) * norm.ld_res + wide_row] : 0.f;
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int t = narrow0 + j0 + j;
@@ -857,7 +890,7 @@ __global__ void __launch_bounds__(192) gemm_tc_pair_kernel(const __grid_constant
 template <int BN, int STAGES, bool SWAP, typename TC, bool SWIGLU = false>
 int launch(const CUtensorMap& mw, const CUtensorMap& mn, const GemmArgs& args, dim3 grid, cudaStream_t st,
            const NormArgs& norm = NormArgs()) {
-  constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 512;
+  constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

@@ -304,6 +304,13 @@ def gemm_bf16_norm(c, a, packed, N: int, swiglu: bool = False, residual=None, no
     return True
 
 
+def folded_norm_enabled(tokens: int) -> bool:
+    """Whether the RMS norms of a step of `tokens` tokens ride in the epilogues of the products around
+    them: up to 64 tokens, unless QORVIX_FOLDED_NORM=0 (for comparison)."""
+    import os
+    return tokens <= 64 and os.environ.get("QORVIX_FOLDED_NORM", "1") != "0"
+
+
 def fused_rope_enabled(tokens: int) -> bool:
     """Whether the QKV projection of a step of `tokens` tokens takes the rotation and the cache write
     into its epilogue: above 64 tokens, unless QORVIX_FUSED_ROPE=0 (for comparison)."""

@@ -58,6 +58,10 @@ class TextModel:
             return self.lm_head(fused.run(residual), out_dtype=torch.float32)
         pending = None
         for run, li in enumerate(self.order):
+            # which norm reads the stream after this block (a block that can prepares that norm's input);
+            # none after the last block: the final norm gathers the wanted rows
+            nxt = self.blocks[self.order[run + 1]] if run + 1 < len(self.order) else None
+            ctx.next_norm = nxt.first_norm() if hasattr(nxt, "first_norm") else None
             residual, pending = self.blocks[li].forward(residual, pending, ctx, cache.layer_view(run))
         if ctx.num_wanted == 0:
             return None

@@ -9,7 +9,7 @@ import torch
 
 from ..cache.spec import PagedKVSpec
 from ..csrc import ops
-from .base import Mixer
+from .base import Mixer, PreNormed
 from .linear import Linear
 from .registry import build_part, register_part
 
@@ -40,37 +40,58 @@ class Attention(Mixer):
     def reads_cache_of(self):
         return self.spec.kv_from
 
-    def forward(self, x, ctx, cache):
-        T = x.shape[0]
+    folds_norms = True             # forward() takes a PreNormed x, residual= and next_norm=
+
+    def forward(self, x, ctx, cache, residual=None, next_norm=None):
+        """x: the normed rows [T, d], or a PreNormed (few tokens: the norm's scale is then applied to the
+        projection's sums).  With residual and next_norm the output projection adds the output to the
+        stream itself and the PreNormed input of next_norm is returned instead of the output."""
         H, Hkv, hd = self.H, self.Hkv, self.hd
         own_kv = self.spec.kv_from is None
         table = self.position.table() if self.position is not None else None
         bt = ctx.block_tables[cache.group]
         qkv = None
-        if (own_kv and table is not None and self.rt.dtype == torch.bfloat16 and self.qkv_proj.packed is not None
-                and ops.fused_rope_enabled(T)):
-            # rotation and cache write in the projection's epilogue, where the kernel takes the sizes
-            qkv = torch.empty((T, (H + 2 * Hkv) * hd), device=x.device, dtype=self.rt.dtype)
-            if not ops.gemm_qkv_rope(qkv, x, self.qkv_proj.packed, cache.tensor, table, ctx.tok_pos, ctx.tok_seg, bt,
-                                     H, Hkv, hd, cache.page_size):
-                qkv = None
+        if isinstance(x, PreNormed):
+            qkv = torch.empty((x.scaled.shape[0], self.qkv_proj.out_features), device=x.scaled.device, dtype=self.rt.dtype)
+            if self.qkv_proj.forward_prenormed(x, qkv):
+                self._rotate_and_write(qkv, ctx, cache, table, bt)
+            else:
+                qkv, x = None, x.materialise()
         if qkv is None:
-            qkv = self.qkv_proj(x, out_dtype=self.rt.dtype)                 # [T, (H+2Hkv)*hd] or [T, H*hd]
-            if own_kv:
-                if table is not None:
-                    ops.rope_kv_write(qkv, cache.tensor, table, ctx.tok_pos, ctx.tok_seg, bt, H, Hkv, hd,
-                                      table.shape[1] * 2, cache.page_size)
-                else:
-                    if self.position is not None:
-                        self.position.apply(qkv, ctx, H, Hkv, hd)
-                    ops.rope_kv_write(qkv, cache.tensor, None, ctx.tok_pos, ctx.tok_seg, bt,
-                                      H, Hkv, hd, 0, cache.page_size)
-            elif self.position is not None:
-                self.position.apply(qkv, ctx, H, 0, hd)
-        out = torch.empty((T, H * hd), device=x.device, dtype=self.rt.dtype)
+            T = x.shape[0]
+            if (own_kv and table is not None and self.rt.dtype == torch.bfloat16 and self.qkv_proj.packed is not None
+                    and ops.fused_rope_enabled(T)):
+                # rotation and cache write in the projection's epilogue, where the kernel takes the sizes
+                qkv = torch.empty((T, (H + 2 * Hkv) * hd), device=x.device, dtype=self.rt.dtype)
+                if not ops.gemm_qkv_rope(qkv, x, self.qkv_proj.packed, cache.tensor, table, ctx.tok_pos, ctx.tok_seg, bt,
+                                         H, Hkv, hd, cache.page_size):
+                    qkv = None
+            if qkv is None:
+                qkv = self.qkv_proj(x, out_dtype=self.rt.dtype)             # [T, (H+2Hkv)*hd] or [T, H*hd]
+                self._rotate_and_write(qkv, ctx, cache, table, bt)
+        out = torch.empty((qkv.shape[0], H * hd), device=qkv.device, dtype=self.rt.dtype)
         ops.attention(out, qkv[:, : H * hd], cache.tensor, ctx, bt, H, Hkv, hd, cache.page_size,
                       self.window, self.scale)
+        if residual is not None and next_norm is not None:
+            pre = self.o_proj.forward_to_stream(out, residual, next_norm)
+            if pre is not None:
+                return pre
         return self.o_proj(out, out_dtype=self.rt.dtype)
+
+    def _rotate_and_write(self, qkv, ctx, cache, table, bt):
+        """Rotates q and k in place and writes k and v into the request's pages (own cache), or rotates q only."""
+        H, Hkv, hd = self.H, self.Hkv, self.hd
+        if self.spec.kv_from is None:
+            if table is not None:
+                ops.rope_kv_write(qkv, cache.tensor, table, ctx.tok_pos, ctx.tok_seg, bt, H, Hkv, hd,
+                                  table.shape[1] * 2, cache.page_size)
+            else:
+                if self.position is not None:
+                    self.position.apply(qkv, ctx, H, Hkv, hd)
+                ops.rope_kv_write(qkv, cache.tensor, None, ctx.tok_pos, ctx.tok_seg, bt,
+                                  H, Hkv, hd, 0, cache.page_size)
+        elif self.position is not None:
+            self.position.apply(qkv, ctx, H, 0, hd)
 
 
 register_part("mixer", "attention", Attention)

@@ -4,6 +4,11 @@ Mixer         forward(x[T,d], ctx, cache) -> [T,d] in the compute dtype; cache_s
               it keeps per request (cache.spec.PagedKVSpec / FixedStateSpec / None);
               reads_cache_of() names another layer whose cache it reads instead.
 FeedForward   forward(x[T,d], ctx) -> [T,d].
+              A mixer or feed-forward with the attribute folds_norms = True also takes x as a
+              PreNormed and the keywords residual=<float32 stream>, next_norm=<the RMS norm that reads
+              the stream next>; it may then add its output to the stream itself and return a
+              PreNormed for that norm (few tokens: the norm's two passes over the stream ride in the
+              epilogues of the products around it).
 Norm          add_norm(residual, delta, rows=None): residual (float32) += delta (delta may be None), returns
               the normed rows in the compute dtype; with rows (int32 row indices) only those rows of
               residual + delta are normed and the residual is left as it is.  The sum and the norm
@@ -33,6 +38,22 @@ class Runtime:
 
     def empty(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, device=self.device, dtype=dtype or self.dtype)
+
+
+@dataclass
+class PreNormed:
+    """The input of an RMS norm as the product ahead of it left it: `scaled` is the float32 residual
+    stream times the norm's weight (compute dtype, not yet divided by the root mean square) and `ssq`
+    the stream's sums of squares per tile of 128 features, [tiles, 64 tokens].  The residual stream
+    already holds the product, so nothing is pending.  A consumer either scales the sums of its own
+    product by rsqrt(mean of squares + eps) or calls materialise() for the normed rows."""
+    scaled: torch.Tensor
+    ssq: torch.Tensor
+    norm: object
+    residual: torch.Tensor
+
+    def materialise(self) -> torch.Tensor:
+        return self.norm.add_norm(self.residual, None)
 
 
 class Mixer:

@@ -8,6 +8,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
+from .base import PreNormed
 
 
 class Linear:
@@ -39,6 +40,27 @@ class Linear:
         return out
 
     __call__ = forward
+
+    def forward_prenormed(self, pre, out: torch.Tensor, swiglu: bool = False) -> bool:
+        """out = rmsnorm(stream) W^T from a PreNormed (the root mean square applied to the product's
+        sums); False, nothing written, when the kernel does not take the product."""
+        if self.packed is None:
+            return False
+        return ops.gemm_bf16_norm(out, pre.scaled, self.packed, self.out_features, swiglu=swiglu, ssq_in=pre.ssq,
+                                  stream_width=pre.norm.size, eps=pre.norm.eps)
+
+    def forward_to_stream(self, x: torch.Tensor, residual: torch.Tensor, norm):
+        """residual += x W^T in the product's epilogue; returns the PreNormed input of `norm` (an RMS
+        norm over the stream), or None, nothing written, when the kernel does not take the product."""
+        M, N = x.shape[0], self.out_features
+        if (self.packed is None or M > 64 or x.dtype != torch.bfloat16 or residual.dtype != torch.float32
+                or tuple(residual.shape) != (M, N) or residual.stride(1) != 1 or norm.size != N):
+            return None
+        scaled = torch.empty((M, N), device=x.device, dtype=x.dtype)
+        ssq = torch.empty((-(-N // 128), 64), device=x.device, dtype=torch.float32)
+        if not ops.gemm_bf16_norm(scaled, x, self.packed, N, residual=residual, norm_weight=norm.weight, ssq_out=ssq):
+            return None
+        return PreNormed(scaled=scaled, ssq=ssq, norm=norm, residual=residual)
 
 
 def _keep_rows() -> bool:

@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import FeedForward
+from .base import FeedForward, PreNormed
 from .linear import Linear
 from .registry import register_part
 
@@ -31,13 +31,28 @@ class SwiGLU(FeedForward):
         del g, u
         self.down = Linear(source.get(spec.down_proj))
 
-    def forward(self, x, ctx):
-        act = torch.empty((x.shape[0], self.f), device=x.device, dtype=self.rt.dtype)
-        if self.interleaved:
-            ops.gemm_swiglu(act, x, self.gate_up.weight, self.gate_up.packed, self.gate_up.out_features)
-        else:
-            gu = self.gate_up(x, out_dtype=self.rt.dtype)
-            ops.swiglu(act, gu)
+    folds_norms = True             # forward() takes a PreNormed x, residual= and next_norm=
+
+    def forward(self, x, ctx, residual=None, next_norm=None):
+        """x: the normed rows [T, d], or a PreNormed (few tokens: the norm's scale is then applied to the
+        gate/up sums before the activation).  With residual and next_norm the down projection adds the
+        output to the stream itself and the PreNormed input of next_norm is returned instead."""
+        act = None
+        if isinstance(x, PreNormed):
+            act = torch.empty((x.scaled.shape[0], self.f), device=x.scaled.device, dtype=self.rt.dtype)
+            if not (self.interleaved and self.gate_up.forward_prenormed(x, act, swiglu=True)):
+                act, x = None, x.materialise()
+        if act is None:
+            act = torch.empty((x.shape[0], self.f), device=x.device, dtype=self.rt.dtype)
+            if self.interleaved:
+                ops.gemm_swiglu(act, x, self.gate_up.weight, self.gate_up.packed, self.gate_up.out_features)
+            else:
+                gu = self.gate_up(x, out_dtype=self.rt.dtype)
+                ops.swiglu(act, gu)
+        if residual is not None and next_norm is not None:
+            pre = self.down.forward_to_stream(act, residual, next_norm)
+            if pre is not None:
+                return pre
         return self.down(act, out_dtype=self.rt.dtype)
 
 

@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import Norm
+from .base import Norm, PreNormed
 from .registry import register_part
 
 
@@ -20,6 +20,8 @@ class RMSNorm(Norm):
     def add_norm(self, residual, delta, rows=None):
         """residual[T,d] float32 (+= delta in place when rows is None).  rows: int32 row
         indices; then only those rows are normed and the residual is left as it is."""
+        if isinstance(delta, PreNormed):
+            delta = None                    # the product is in the stream already
         n = residual.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.size), device=residual.device, dtype=self.rt.dtype)
         ops.add_rmsnorm(out, residual, delta, self.weight, self.eps, row_idx=rows)

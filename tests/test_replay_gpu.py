@@ -3,7 +3,7 @@ import pytest
 import torch
 
 from helpers import TINY, PlainModel, assert_close_logits, make_model_dir, random_tokens
-from qorvix_b200 import ModelRunner, StepEntry
+from qorvix_b200 import LlamaConfig, ModelRunner, StepEntry
 
 pytestmark = pytest.mark.gpu
 
@@ -226,6 +226,36 @@ def test_logits_keep_the_callers_order_when_portions_come_before_decoded_tokens(
                      pm.logits(dec[names[1]])[-1:], pm.logits(dec[names[3]])[-1:]])
     assert_close_logits(out, ref, dtype, "caller's order", sharp=True)
     r.cache.check_invariants()
+
+
+def test_norms_folded_into_the_products_around_them(monkeypatch):
+    """Steps of up to 64 tokens in bfloat16 at sizes where the few-token products are split along K:
+    the output projections add into the residual stream and prepare the next norm's input, the
+    projections after the norm scale their sums.  Against the plain implementation, and against the
+    same engine with the norm kernel (QORVIX_FOLDED_NORM=0)."""
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", vocab_size=300, hidden_size=512, intermediate_size=1024, num_hidden_layers=3, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=128, max_position_embeddings=256, rms_norm_eps=1e-5, rope_theta=10000.0,
+                      rope_scaling=None, tie_word_embeddings=False)
+    d = make_model_dir(cfg, seed=21, sharpen=4.0)
+    pm = PlainModel(d)
+    a, b = random_tokens(300, 60, 31), random_tokens(300, 41, 32)
+    ref_a, ref_b = pm.logits(a), pm.logits(b)
+    results = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("QORVIX_FOLDED_NORM", mode)
+        r = ModelRunner(d, dtype="bfloat16", max_tokens=512, page_size=16, max_requests=4)
+        got_a = [r.step([StepEntry("a", a[:33], list(range(33)))])]                       # a portion of few tokens
+        out = r.step([StepEntry("a", a[33:50], list(range(17))), StepEntry("b", b[:30], list(range(30)))])
+        got_a.append(out[:17]); got_b = [out[17:]]
+        for i in range(10):                                                               # captured decode steps
+            out = r.step([StepEntry("a", [a[50 + i]], [0]), StepEntry("b", [b[30 + i]], [0])])
+            got_a.append(out[:1]); got_b.append(out[1:])
+        got_b.append(r.step([StepEntry("b", [b[40]], [0])]))
+        results[mode] = (torch.cat(got_a), torch.cat(got_b))
+        assert_close_logits(results[mode][0], ref_a, "bfloat16", f"request a, folded norms {mode}", sharp=True)
+        assert_close_logits(results[mode][1], ref_b, "bfloat16", f"request b, folded norms {mode}", sharp=True)
+    # the two routes round differently, so they are close to each other but not equal: both ran
+    assert not torch.equal(results["1"][0], results["0"][0])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
