@@ -306,9 +306,13 @@ def gemm_bf16_norm(c, a, packed, N: int, swiglu: bool = False, residual=None, no
 
 def folded_norm_enabled(tokens: int) -> bool:
     """Whether the RMS norms of a step of `tokens` tokens ride in the epilogues of the products around
-    them: up to 64 tokens, unless QORVIX_FOLDED_NORM=0 (for comparison)."""
+    them: up to 16 tokens (one chunk of the epilogue, whose stream values are fetched while the main loop
+    runs; at 64 tokens the longer epilogues cost more than the two launches they save: 11.0k against
+    11.9k tokens/s at batch 64), unless QORVIX_FOLDED_NORM=0 (never) or =64 (up to 64 tokens; for
+    comparison)."""
     import os
-    return tokens <= 64 and os.environ.get("QORVIX_FOLDED_NORM", "1") != "0"
+    mode = os.environ.get("QORVIX_FOLDED_NORM", "1")
+    return mode != "0" and tokens <= (64 if mode == "64" else 16)
 
 
 def fused_rope_enabled(tokens: int) -> bool:
