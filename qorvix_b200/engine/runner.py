@@ -194,15 +194,8 @@ class ModelRunner:
             # A mixed step runs its single-token entries first: the attention kernels then serve the
             # decoded tokens and the prompt portions each with the kernel made for them.  The logits
             # go back in the order the caller gave.
-            order = sorted(range(len(entries)), key=lambda i: len(entries[i].tokens) != 1)
-            back = None
-            if order != list(range(len(entries))):
-                first_row, row = {}, 0
-                for i in order:
-                    first_row[i] = row
-                    row += len(entries[i].want)
-                back = [first_row[i] + k for i, e in enumerate(entries) for k in range(len(e.want))]
-                entries = [entries[i] for i in order]
+            order, back = single_token_entries_first(entries)
+            entries = [entries[i] for i in order]
             ctx = self.prepare(entries)
             logits = self.model.forward(ctx, self.cache)
             if logits is not None and back is not None and back != list(range(len(back))):
@@ -218,6 +211,21 @@ class ModelRunner:
     def release(self, req_id) -> None:
         if self.cache.has(req_id):
             self.cache.release(req_id)
+
+
+def single_token_entries_first(entries: Sequence[StepEntry]):
+    """The order in which a step's entries run (single-token entries first, otherwise as given) and,
+    when that order differs from the caller's, for every wanted row in the caller's order its row in
+    the step's output (else None)."""
+    order = sorted(range(len(entries)), key=lambda i: len(entries[i].tokens) != 1)
+    if order == list(range(len(entries))):
+        return order, None
+    first_row, row = {}, 0
+    for i in order:
+        first_row[i] = row
+        row += len(entries[i].want)
+    back = [first_row[i] + k for i, e in enumerate(entries) for k in range(len(e.want))]
+    return order, back
 
 
 def _require_cuda(device: torch.device) -> None:
