@@ -48,3 +48,90 @@ def test_switches(monkeypatch):
     assert ops.folded_norm_enabled(64) and not ops.folded_norm_enabled(65)
     monkeypatch.setenv("QORVIX_FUSED_ROPE", "0")
     assert not ops.fused_rope_enabled(2048)
+
+
+def _stub_rmsnorm(calls, name):
+    """An RMSNorm object without a device: add_norm only records what it is given."""
+    import torch
+    from qorvix_b200.parts.rmsnorm import RMSNorm
+    n = object.__new__(RMSNorm)
+    n.size, n.eps, n.weight = 8, 1e-5, torch.ones(8)
+
+    def add_norm(residual, delta, rows=None):
+        calls.append((name, "add_norm", type(delta).__name__))
+        return torch.zeros(residual.shape[0], 8)
+    n.add_norm = add_norm
+    return n
+
+
+def test_pre_norm_block_hands_a_prepared_norm_input_only_to_parts_that_take_it(monkeypatch):
+    """The routing of PreNormed between the parts of a block, with stub parts (no kernels run)."""
+    import torch
+    from qorvix_b200.parts.base import PreNormed
+    from qorvix_b200.parts.block import PreNormBlock
+    monkeypatch.delenv("QORVIX_FOLDED_NORM", raising=False)
+    calls = []
+    n1, n2, n_after = _stub_rmsnorm(calls, "n1"), _stub_rmsnorm(calls, "n2"), _stub_rmsnorm(calls, "after")
+
+    class FoldingMixer:
+        folds_norms = True
+
+        def forward(self, x, ctx, cache, residual=None, next_norm=None):
+            calls.append(("mixer", type(x).__name__, next_norm))
+            return PreNormed(scaled=torch.zeros(2, 8), ssq=torch.zeros(1, 64), norm=next_norm, residual=residual)
+
+    class FoldingFfn:
+        folds_norms = True
+
+        def forward(self, x, ctx, residual=None, next_norm=None):
+            calls.append(("ffn", type(x).__name__, next_norm))
+            return PreNormed(scaled=torch.zeros(2, 8), ssq=torch.zeros(1, 64), norm=next_norm, residual=residual)
+
+    class PlainFfn:
+        def forward(self, x, ctx):
+            calls.append(("plain_ffn", type(x).__name__, None))
+            return torch.zeros(2, 8)
+
+    class Ctx:
+        next_norm = None
+
+    def block(mixer, ffn):
+        b = object.__new__(PreNormBlock)
+        b.mixer_norm, b.mixer, b.ffn_norm, b.feed_forward = n1, mixer, n2, ffn
+        return b
+
+    residual = torch.zeros(2, 8)
+    ctx = Ctx()
+    ctx.next_norm = n_after
+    # both parts fold: the mixer prepares the ffn norm's input, the ffn takes it as it is and prepares the next block's
+    _, pending = block(FoldingMixer(), FoldingFfn()).forward(residual, None, ctx, None)
+    assert calls == [("n1", "add_norm", "NoneType"), ("mixer", "Tensor", n2), ("ffn", "PreNormed", n_after)]
+    assert isinstance(pending, PreNormed) and pending.norm is n_after
+    # a block that gets a PreNormed made for its first norm hands it to a folding mixer without running the norm
+    calls.clear()
+    block(FoldingMixer(), FoldingFfn()).forward(residual, PreNormed(torch.zeros(2, 8), torch.zeros(1, 64), n1, residual), ctx, None)
+    assert calls[0] == ("mixer", "PreNormed", n2)
+    # a feed-forward that does not fold gets normed rows: its norm is run on the PreNormed (the stream is complete)
+    calls.clear()
+    _, pending = block(FoldingMixer(), PlainFfn()).forward(residual, None, ctx, None)
+    assert calls == [("n1", "add_norm", "NoneType"), ("mixer", "Tensor", n2), ("n2", "add_norm", "PreNormed"),
+                     ("plain_ffn", "Tensor", None)]
+    assert isinstance(pending, torch.Tensor)
+    # many tokens: nothing is folded, the parts are called the plain way (no keywords)
+    calls.clear()
+    big = torch.zeros(100, 8)
+
+    class CountingMixer:
+        folds_norms = True
+
+        def forward(self, x, ctx, cache, **kw):
+            calls.append(("mixer_kw", sorted(kw)))
+            return torch.zeros(100, 8)
+
+    block(CountingMixer(), PlainFfn()).forward(big, None, ctx, None)
+    assert ("mixer_kw", []) in calls
+    # no RMS norm after the block (another kind of norm, or the final norm): the last part is told so
+    calls.clear()
+    ctx.next_norm = object()
+    block(FoldingMixer(), FoldingFfn()).forward(residual, None, ctx, None)
+    assert calls[-1] == ("ffn", "PreNormed", None)
