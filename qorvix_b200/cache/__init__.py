@@ -1,3 +1,2 @@
-from .manager import CacheManager, LayerCacheView, OutOfPages, OutOfSlots
-from .page_pool import PageError, PagePool
+from .manager import CacheManager, LayerCacheView, OutOfPages, OutOfSlots, PageError
 from .spec import FixedStateSpec, PagedKVSpec

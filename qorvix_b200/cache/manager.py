@@ -26,9 +26,12 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 import torch
 
 from . import native
-from .page_pool import PageError
 from .spec import FixedStateSpec, PagedKVSpec
 
+
+
+class PageError(RuntimeError):
+    """The bookkeeping of pages is inconsistent (a page lost, held twice or freed twice)."""
 
 class OutOfPages(RuntimeError):
     pass

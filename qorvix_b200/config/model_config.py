@@ -58,8 +58,18 @@ class RopeScaling:
 
 @dataclass(frozen=True)
 class ModelConfig:
-    """What every architecture's configuration has in common."""
+    """What every architecture's configuration has in common: its name, and what the entry points
+    (command line, LLM) read of any model: the vocabulary's size and the ids that end a generation."""
     architecture: str
+    vocab_size: int = 0
+    eos_token_id: Optional[Any] = None
+
+    @property
+    def eos_token_ids(self) -> tuple:
+        e = self.eos_token_id
+        if e is None:
+            return ()
+        return tuple(int(x) for x in e) if isinstance(e, (list, tuple)) else (int(e),)
 
 
 @dataclass(frozen=True)
@@ -139,13 +149,6 @@ class LlamaConfig(ModelConfig):
         d["rope_scaling"] = self.rope_scaling.to_dict() if self.rope_scaling else None
         d["model_type"] = "llama"
         return d
-
-    @property
-    def eos_token_ids(self) -> tuple:
-        e = self.eos_token_id
-        if e is None:
-            return ()
-        return tuple(int(x) for x in e) if isinstance(e, (list, tuple)) else (int(e),)
 
 
 def read_config_json(model_dir) -> dict:

@@ -36,7 +36,6 @@ LIBRARIES = {
     "gemm_bf16": "gemm_bf16.cu",
     "attention_bf16": "attention_bf16.cu",
     "attention_tc": "attention_tc.cu",
-    "decode_fused": "decode_fused.cu",
     "host_runtime": "host_runtime.cpp",          # host-side cache bookkeeping: plain C++, no CUDA
 }
 HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC"]

@@ -8,9 +8,7 @@
 //     rows the other; a persistent kernel, one CTA per SM walking over the tiles, with the
 //     accumulator double-buffered in tensor memory so that one tile's epilogue overlaps the next
 //     tile's main loop.  The epilogue may apply SwiGLU (gate/up projection) or rotate the query and
-//     key heads and write keys and values into the paged cache (QKV projection).  Two more
-//     kernels are kept for comparison: one 128x128 tile per CTA, and clusters of two CTAs on
-//     256x256 tiles (tcgen05.mma.cta_group::2).
+//     key heads and write keys and values into the paged cache (QKV projection).
 //   * few tokens (decode, M <= 64): operands are swapped.  128 weight rows are the 128-row MMA
 //     operand and the tokens (padded to 16/32/64) the narrow one, so every weight byte is
 //     streamed from HBM exactly once through a deep TMA ring.  Matrices with few row tiles are
@@ -65,14 +63,14 @@ struct NormArgs {
   float inv_d = 0.f, eps = 0.f;
 };
 
-// BN: columns of the accumulator (rows of the narrow operand per tile).  SWAP: the wide operand
-// is the weight matrix (features) and the narrow one the tokens, so the tile is C^T.
+// Few tokens.  BN: columns of the accumulator (token rows per tile, padded).  The wide operand is
+// the weight matrix (features) and the narrow one the tokens, so the tile is C^T.
 // SWIGLU: the weight rows come in groups of 32 (16 gate rows, then the 16 up rows of the same
 // features); the epilogue writes silu(gate) * up, so C has half as many features as W has rows.
 // bfloat16 output: the fast exponential's error (a few float32 ulp) vanishes in the rounding
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
-template <int BN, int STAGES, bool SWAP, typename TC, bool SWIGLU>
+template <int BN, int STAGES, typename TC, bool SWIGLU>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_wide,
                                                       const __grid_constant__ CUtensorMap map_narrow,
                                                       const GemmArgs args, const NormArgs norm) {
@@ -124,14 +122,14 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     if (lane == 0) {
       // Weights are never written by a kernel, so the first stages' weight tiles are requested
       // before waiting for the kernel ahead in the stream; the activation tiles after.
-      const CUtensorMap* w_map = SWAP ? &map_wide : &map_narrow;
-      const CUtensorMap* x_map = SWAP ? &map_narrow : &map_wide;
-      const int w_row0 = SWAP ? wide0 : narrow0, x_row0 = SWAP ? narrow0 : wide0;
-      const int w_off = SWAP ? 0 : A_BYTES, x_off = SWAP ? A_BYTES : 0;
+      const CUtensorMap* w_map = &map_wide;
+      const CUtensorMap* x_map = &map_narrow;
+      const int w_row0 = wide0, x_row0 = narrow0;
+      const int w_off = 0, x_off = A_BYTES;
       const int pre = num_kb < STAGES ? num_kb : STAGES;
       // a packed weight matrix is read tile by tile with contiguous 16 KB copies; its tiles are 128
       // rows, so the weight side of this kernel's tile must be 128 rows too (the host sees to that)
-      const uint8_t* wp = args.packed ? args.packed + ((size_t)(SWAP ? blockIdx.x : blockIdx.y) * total_kb + kb0) * (size_t)A_BYTES : nullptr;
+      const uint8_t* wp = args.packed ? args.packed + ((size_t)blockIdx.x * total_kb + kb0) * (size_t)A_BYTES : nullptr;
       for (int kb = 0; kb < pre; ++kb) {
         mbar_expect_tx(&full[kb], STAGE_BYTES);
         if (wp) bulk_load_1d(tiles + kb * STAGE_BYTES + w_off, wp + (size_t)kb * A_BYTES, &full[kb], A_BYTES);
@@ -174,7 +172,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     // epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31
     pdl_wait();                 // C may still be in use by the kernel ahead
     const int q = warp & 3;
-    if (SWAP && norm.ssq_in != nullptr && (args.splits == 1 || split == 0)) {
+    if (norm.ssq_in != nullptr && (args.splits == 1 || split == 0)) {
       // While the main loop runs: each token's scale from the sums of squares the kernel ahead left.
       // The 128 threads share the loads (128 / BN threads a token, each every (128 / BN)-th tile, four
       // loads in flight a thread), then one thread a token adds the parts in a fixed order.
@@ -200,7 +198,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
         rs_s[te] = rsqrtf(tot * norm.inv_d + norm.eps);
       }
     }
-    if (SWAP && norm.residual != nullptr && split == 0) {
+    if (norm.residual != nullptr && split == 0) {
       const int wr = wide0 + q * 32 + lane;
       const bool v = wr < args.rows_wide;
       norm_w0 = v ? norm.norm_w[wr] : 0.f;
@@ -222,107 +220,52 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
     TC* C = (TC*)args.C;
     if (ok && num_kb > 0) {
-      if (!SWAP) {
-        // thread = token row wide_row; columns = features narrow0 + c
+      // thread = feature wide_row; columns = tokens narrow0 + c
+      const bool frow = wide_row < args.rows_wide;
+      const int ntok = args.rows_narrow;
+      if (args.splits == 1) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(taddr + c0, r);
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
           tmem_wait_ld();
           if (SWIGLU) {
-            if (wide_row < args.rows_wide && narrow0 + c0 < args.rows_narrow) {
-              // columns 0..15 of this chunk are gate, 16..31 up, of features (narrow0 + c0)/2 + j
-              TC* dst = C + (size_t)wide_row * args.ldc + ((narrow0 + c0) >> 1);
-              float a[16];
+            // lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same features
+            const int feat = ((wide0 + q * 32) >> 1) + (lane & 15);
 #pragma unroll
-              for (int j = 0; j < 16; ++j) a[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r[16 + j]));
-              if (sizeof(TC) == 2 && (((uintptr_t)dst) & 15) == 0) {
-                uint32_t w[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  __nv_bfloat162 h = __floats2bfloat162_rn(a[2 * j], a[2 * j + 1]);
-                  w[j] = *(uint32_t*)&h;
-                }
-                ((uint4*)dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                ((uint4*)dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) store_out<TC>(dst + j, a[j]);
-              }
+            for (int j = 0; j < 16; ++j) {
+              const float mine = __uint_as_float(r[j]) * (norm.ssq_in ? rs_s[c0 + j] : 1.f);
+              const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+              const int t = narrow0 + c0 + j;
+              if (lane < 16 && frow && t < ntok) store_out<TC>(C + (size_t)t * args.ldc + feat, silu_mul(mine, other));
             }
-          } else if (wide_row < args.rows_wide) {
-            TC* dst = C + (size_t)wide_row * args.ldc + narrow0 + c0;
-            const int ncols = args.rows_narrow - (narrow0 + c0);
-            if (sizeof(TC) == 2 && ncols >= 32 && (((uintptr_t)dst) & 15) == 0) {
-              uint4* d4 = (uint4*)dst;
+          } else if (frow) {
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint32_t w[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
-                  w[j] = *(uint32_t*)&h;
-                }
-                d4[v] = make_uint4(w[0], w[1], w[2], w[3]);
-              }
-            } else if (sizeof(TC) == 4 && ncols >= 32 && (((uintptr_t)dst) & 15) == 0) {
-              float4* d4 = (float4*)dst;
-#pragma unroll
-              for (int v = 0; v < 8; ++v)
-                d4[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-            } else {
-              for (int j = 0; j < 32 && j < ncols; ++j) store_out<TC>(dst + j, __uint_as_float(r[j]));
+            for (int j = 0; j < 16; ++j) {
+              const int t = narrow0 + c0 + j;
+              if (t < ntok) store_out<TC>(C + (size_t)t * args.ldc + wide_row, __uint_as_float(r[j]) * (norm.ssq_in ? rs_s[c0 + j] : 1.f));
             }
           }
         }
       } else {
-        // thread = feature wide_row; columns = tokens narrow0 + c
-        const bool frow = wide_row < args.rows_wide;
-        const int ntok = args.rows_narrow;
-        if (args.splits == 1) {
+        // split-K: this CTA's partial sums go to its own shared memory (the stage ring is free
+        // now), column-major so that a warp's 32 rows are 32 consecutive floats; the cluster's
+        // first CTA adds them up below
+        float* red = (float*)tiles;
 #pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 16) {
-            uint32_t r[16];
-            tmem_ld16(taddr + c0, r);
-            tmem_wait_ld();
-            if (SWIGLU) {
-              // lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same features
-              const int feat = ((wide0 + q * 32) >> 1) + (lane & 15);
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_wait_ld();
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const float mine = __uint_as_float(r[j]) * (norm.ssq_in ? rs_s[c0 + j] : 1.f);
-                const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
-                const int t = narrow0 + c0 + j;
-                if (lane < 16 && frow && t < ntok) store_out<TC>(C + (size_t)t * args.ldc + feat, silu_mul(mine, other));
-              }
-            } else if (frow) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int t = narrow0 + c0 + j;
-                if (t < ntok) store_out<TC>(C + (size_t)t * args.ldc + wide_row, __uint_as_float(r[j]) * (norm.ssq_in ? rs_s[c0 + j] : 1.f));
-              }
-            }
-          }
-        } else {
-          // split-K: this CTA's partial sums go to its own shared memory (the stage ring is free
-          // now), column-major so that a warp's 32 rows are 32 consecutive floats; the cluster's
-          // first CTA adds them up below
-          float* red = (float*)tiles;
-#pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 16) {
-            uint32_t r[16];
-            tmem_ld16(taddr + c0, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) red[(c0 + j) * BM + q * 32 + lane] = __uint_as_float(r[j]);
-          }
+          for (int j = 0; j < 16; ++j) red[(c0 + j) * BM + q * 32 + lane] = __uint_as_float(r[j]);
         }
       }
     }
     tc_fence_before();
   }
   __syncthreads();
-  if (SWAP && args.splits > 1) {
+  if (args.splits > 1) {
     // The CTAs of one tile (one per split) form a cluster.  After the cluster barrier every
     // partial tile is visible through distributed shared memory; the first CTA adds them in
     // split order 0, 1, 2, ... and stores the result, and a second barrier keeps the others'
@@ -683,222 +626,30 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
   }
 }
 
-// ---------------------------------------------------------------- many tokens: CTA pairs
-// The two CTAs of a cluster share one 256 x 256 tile: each loads its 128 token rows and 128 of the
-// 256 weight rows (32 KB per k block of 64 instead of the 48 KB a 128 x 256 tile takes for the same
-// MMA work per SM), and tcgen05.mma.cta_group::2, issued by the pair's first CTA, multiplies them out of both
-// CTAs' shared memory into both CTAs' tensor memory (128 rows x 256 columns each, double-buffered).
-// The second CTA's MMA warp tells the first when its stage has landed; commits free a stage and
-// hand over an accumulator in both CTAs at once; each CTA's epilogue warps store their own rows.
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster.  Without
-// .release.cluster: that form made every arrive wait about 0.8 us for a cluster-wide fence, and the
-// arrivals here publish nothing the arriving thread wrote itself (a stage that the copy engine
-// filled; an accumulator that tcgen05.ld has drained, ordered by tcgen05.fence::before_thread_sync).
-__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
-  asm volatile(
-      "{\n\t.reg .b32 ra;\n\t"
-      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
-      "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}"
-      ::"r"(smem_u32(bar)), "r"(rank) : "memory");
-}
-__device__ __forceinline__ void umma2_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-// arrives, when the MMAs issued so far are done, on the barrier at this offset in both CTAs of the pair
-__device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
-}
-
-template <int STAGES, typename TC, bool SWIGLU>
-__global__ void __launch_bounds__(192) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x,
-                                                           const __grid_constant__ CUtensorMap map_w,
-                                                           const GemmArgs args) {
-  extern __shared__ uint8_t smem_raw[];
-  constexpr int BN = 256;                            // columns of the pair's tile; each CTA loads half the weight rows
-  constexpr int A_BYTES = BM * BK * 2;
-  constexpr int STAGE_BYTES = 2 * A_BYTES;           // 128 token rows + 128 weight rows
-  constexpr int TMEM_COLS = 2 * BN;
-  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = (uint64_t*)(tiles + STAGES * STAGE_BYTES);
-  uint64_t* peer_full = full + STAGES;               // first CTA: the second CTA's stage has landed
-  uint64_t* empty = peer_full + STAGES;
-  uint64_t* acc_full = empty + STAGES;               // [2]
-  uint64_t* acc_empty = acc_full + 2;                // [2], first CTA: both CTAs' epilogues arrive here
-  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_rank();
-  const int M = args.rows_wide, N = args.rows_narrow;
-  const int pairs_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN - 1) / BN;
-  const int total_tiles = pairs_m * tiles_n;
-  const int num_kb = (args.K + BK - 1) / BK;
-  const int first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&peer_full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 256); }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  cluster_sync_all();                                // both CTAs' barriers exist before anything arrives on them
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  pdl_launch_dependents();
-
-  if (warp == 0) {
-    if (lane == 0) {
-      const int w_tiles = (N + BM - 1) / BM;
-      // Arms stage s and requests this CTA's 128 weight rows of k block kb (rows past the last
-      // packed tile are left out: their columns are never stored).
-      auto load_w = [&](int s, int kb, int nrow0) {
-        uint8_t* dst = tiles + s * STAGE_BYTES + A_BYTES;
-        if (args.packed) {
-          const int t = nrow0 / BM;
-          mbar_expect_tx(&full[s], t < w_tiles ? 2 * A_BYTES : A_BYTES);
-          if (t < w_tiles) bulk_load_1d(dst, args.packed + ((size_t)t * num_kb + kb) * (size_t)A_BYTES, &full[s], A_BYTES);
-        } else {
-          mbar_expect_tx(&full[s], 2 * A_BYTES);
-          tma_load_2d(dst, &map_w, &full[s], kb * BK, nrow0);
-        }
-      };
-      int it = 0;
-      bool first = true;
-      for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
-        const int m0 = (tile % pairs_m) * 2 * BM + (int)rank * BM;
-        const int nrow0 = (tile / pairs_m) * BN + (int)rank * BM;
-        int kb = 0;
-        if (first) {                                 // the first stages' weight tiles do not depend on the kernel ahead
-          const int pre = num_kb < STAGES ? num_kb : STAGES;
-          for (int k = 0; k < pre; ++k) load_w(k, k, nrow0);
-          pdl_wait();
-          for (int k = 0; k < pre; ++k) tma_load_2d(tiles + k * STAGE_BYTES, &map_x, &full[k], k * BK, m0);
-          kb = pre;
-          it = pre;
-          first = false;
-        }
-        bool ok = true;
-        for (; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&empty[s], ph ^ 1, args.err, 1)) { ok = false; break; }
-          load_w(s, kb, nrow0);
-          tma_load_2d(tiles + s * STAGE_BYTES, &map_x, &full[s], kb * BK, m0);
-        }
-        if (!ok) break;
-      }
-      if (first) pdl_wait();
-    }
-  } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = umma_idesc(2 * BM, BN);
-      int it = 0, local = 0;
-      bool ok = true;
-      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++local) {
-        const int b = local & 1;
-        // both CTAs' epilogues must have drained this accumulator (two tiles ago)
-        ok = mbar_wait(&acc_empty[b], ((local >> 1) & 1) ^ 1, args.err, 4);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          ok = mbar_wait(&full[s], ph, args.err, 2) && mbar_wait(&peer_full[s], ph, args.err, 5);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
-          const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
-#pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk)
-            umma2_f16(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
-          umma2_commit_both(&empty[s]);
-        }
-        umma2_commit_both(&acc_full[b]);
-      }
-    } else if (lane == 0) {
-      // second CTA: pass each landed stage on to the first CTA's MMA thread
-      int it = 0;
-      bool ok = true;
-      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          ok = mbar_wait(&full[s], (it / STAGES) & 1, args.err, 6);
-          if (!ok) break;
-          mbar_arrive_remote(&peer_full[s], 0);
-        }
-      }
-    }
-  } else {
-    pdl_wait();                                      // C may still be in use by the kernel ahead
-    const int q = warp & 3;
-    TC* C = (TC*)args.C;
-    int local = 0;
-    for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++local) {
-      const int b = local & 1;
-      const int m0 = (tile % pairs_m) * 2 * BM + (int)rank * BM, n0 = (tile / pairs_m) * BN;
-      // every thread polls: the arrivals below need all of them, timed out or not
-      const bool ok = mbar_wait(&acc_full[b], (local >> 1) & 1, args.err, 3);
-      tc_fence_after();
-      const int row = m0 + q * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN);
-      if (ok) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(taddr + c0, r);
-          tmem_wait_ld();
-          if (row >= M || n0 + c0 >= N) continue;
-          store_chunk<TC, SWIGLU>(C, args.ldc, row, n0 + c0, N - (n0 + c0), r);
-        }
-      }
-      tc_fence_before();
-      mbar_arrive_remote(&acc_empty[b], 0);          // the first CTA's barrier counts both CTAs' 128 threads
-      if (!ok) break;
-    }
-    tc_fence_before();
-  }
-  // neither CTA may leave while the other can still arrive on its barriers or its MMAs read its memory
-  tc_fence_before();
-  __syncwarp();
-  cluster_sync_all();
-  if (warp == 1) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
-  }
-}
-
 // ---------------------------------------------------------------- host side
-template <int BN, int STAGES, bool SWAP, typename TC, bool SWIGLU = false>
+// Streaming multiprocessors of the current device, asked once.
+int device_sms() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+template <int BN, int STAGES, typename TC, bool SWIGLU = false>
 int launch(const CUtensorMap& mw, const CUtensorMap& mn, const GemmArgs& args, dim3 grid, cudaStream_t st,
            const NormArgs& norm = NormArgs()) {
   constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, TC, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   // split-K CTAs of a tile (grid.z of them) are one cluster
-  return qv_launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, TC, SWIGLU>, grid, dim3(192), (size_t)smem, st, dim3(1, 1, grid.z), mw, mn, args, norm);
+  return qv_launch_cluster(gemm_tc_kernel<BN, STAGES, TC, SWIGLU>, grid, dim3(192), (size_t)smem, st, dim3(1, 1, grid.z), mw, mn, args, norm);
 }
 
 template <int BN, int STAGES, typename TC, bool SWIGLU, bool ROPE = false>
@@ -910,49 +661,14 @@ int launch_persistent(const CUtensorMap& mx, const CUtensorMap& mw, const GemmAr
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, TC, SWIGLU, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (sms <= 0) sms = 148;
+    sms = device_sms();
     configured = true;
   }
   const int ctas = total_tiles < sms ? total_tiles : sms;
   return qv_launch(gemm_tc_persistent_kernel<BN, STAGES, TC, SWIGLU, ROPE>, dim3(ctas), dim3(192), (size_t)smem, st, mx, mw, args, rope);
 }
 
-template <int STAGES, typename TC, bool SWIGLU>
-int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& args, int total_tiles, cudaStream_t st) {
-  constexpr int smem = STAGES * (2 * BM * BK * 2) + 1024 + 256;
-  static bool configured = false;
-  static int clusters = 0;
-  auto kernel = gemm_tc_pair_kernel<STAGES, TC, SWIGLU>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    // how many pairs the device holds at once (an SM without a free neighbour in its GPC stays out)
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(2 * 74); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = smem;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
-    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters <= 0) { cudaGetLastError(); return QV_ERR_UNSUPPORTED; }
-    configured = true;
-  }
-  const int n = total_tiles < clusters ? total_tiles : clusters;
-  return qv_launch_cluster(kernel, dim3(2 * n), dim3(192), (size_t)smem, st, dim3(2, 1, 1), mx, mw, args);
-}
-
 }  // namespace
-
-// Which kernel serves more than 64 tokens: 0 (default) the persistent one-CTA kernel (128 x 256 or
-// 128 x 128 tiles); 1 the one-tile-per-CTA kernel with 128 x 128 tiles; 3 CTA pairs on 256 x 256 tiles
-// where there are more than 128 tokens.  1 and 3 are kept for comparison and tests: the pairs halve
-// the weight bytes an SM takes in, but at these sizes the MMA rate under the power cap, not the
-// fill, sets the pace, and they measure 2-6 % behind (8 % ahead only for 4,096 x 6,144 x 4,096).
-static int g_prefill_variant = 0;
-extern "C" void qv_gemm_bf16_set_prefill_variant(int v) { g_prefill_variant = v; }
 
 // Columns of the persistent kernel's tiles: 0 (default) chooses per product, else the given width
 // (a multiple of 16, of 32 with the fused activation, at most 256; for comparison and tests).
@@ -965,13 +681,7 @@ extern "C" void qv_gemm_bf16_set_prefill_bn(int v) { g_prefill_bn = v; }
 // sooner (4096 x 14336 at 512 tokens: 76.9 us at 128 columns, 88.1 us at 256).
 static int choose_tile_width(int tiles_m, int N, int step) {
   (void)step;
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-  }
-  return tiles_m * ((N + 127) / 128) <= sms ? 128 : 256;
+  return tiles_m * ((N + 127) / 128) <= device_sms() ? 128 : 256;
 }
 
 // K splits of the few-token kernel and the k blocks of each.
@@ -979,10 +689,10 @@ static int swap_splits(int tiles, int total_kb, int epilogue, int force_splits, 
   int splits = 1;
   if (epilogue == 1) splits = 1;                  // the fused activation needs whole sums
   else if (force_splits > 0) splits = force_splits;
-  else if (tiles < 96) {                          // too few CTAs to pull full bandwidth: split along K
+  else if (tiles < (2 * device_sms()) / 3) {      // too few CTAs to pull full bandwidth: split along K
     // a power of two, at most 4: clusters of 8 CTAs do not all find room at once (measured: a
-    // 2048 x 8192 product takes 22.5 us at 8 splits, 13.2 us at 4), and at most ~200 CTAs in all
-    while (splits < 4 && tiles * splits * 2 <= 200 && total_kb / (splits * 2) >= 4) splits *= 2;
+    // 2048 x 8192 product takes 22.5 us at 8 splits, 13.2 us at 4), and at most 4/3 CTAs per SM in all
+    while (splits < 4 && tiles * splits * 2 <= device_sms() + device_sms() / 3 && total_kb / (splits * 2) >= 4) splits *= 2;
   }
   if (splits > total_kb) splits = total_kb;
   const int per = (total_kb + splits - 1) / splits;
@@ -1020,13 +730,13 @@ static int gemm_bf16_entry(void* C, const void* A, const void* W, const void* pa
     else if (!W || !make_map(&mw, W, N, K, ldw, BM)) return QV_ERR_UNSUPPORTED;
     dim3 grid(tiles, 1, splits);
 #define SWAP_LAUNCH(BN_, ST_)                                                                     \
-  (c_dt == QV_DT_BF16 ? launch<BN_, ST_, true, bf16>(mw, mn, args, grid, st) : launch<BN_, ST_, true, float>(mw, mn, args, grid, st))
+  (c_dt == QV_DT_BF16 ? launch<BN_, ST_, bf16>(mw, mn, args, grid, st) : launch<BN_, ST_, float>(mw, mn, args, grid, st))
     if (epilogue == 1) {
-      if (bn == 16) return launch<16, 6, true, bf16, true>(mw, mn, args, grid, st);
-      if (bn == 32) return launch<32, 5, true, bf16, true>(mw, mn, args, grid, st);
-      return launch<64, 4, true, bf16, true>(mw, mn, args, grid, st);
+      if (bn == 16) return launch<16, 6, bf16, true>(mw, mn, args, grid, st);
+      if (bn == 32) return launch<32, 5, bf16, true>(mw, mn, args, grid, st);
+      return launch<64, 4, bf16, true>(mw, mn, args, grid, st);
     }
-    const bool one_wave = tiles * splits <= 148;     // every CTA resident at once, one per SM: deeper rings
+    const bool one_wave = tiles * splits <= device_sms();     // every CTA resident at once, one per SM: deeper rings
     if (bn == 16) return one_wave ? SWAP_LAUNCH(16, 12) : SWAP_LAUNCH(16, 6);
     if (bn == 32) return one_wave ? SWAP_LAUNCH(32, 10) : SWAP_LAUNCH(32, 5);
     return one_wave ? SWAP_LAUNCH(64, 8) : SWAP_LAUNCH(64, 4);
@@ -1036,40 +746,18 @@ static int gemm_bf16_entry(void* C, const void* A, const void* W, const void* pa
   if (!W && !packed) return QV_ERR_UNSUPPORTED;
   args.packed = (const uint8_t*)packed;
   args.rows_wide = M; args.rows_narrow = N; args.kblocks_per_split = total_kb; args.splits = 1;
-  if (g_prefill_variant == 0 || g_prefill_variant == 3) {
-    const int step = epilogue == 1 ? 32 : 16;
-    int bn = g_prefill_bn > 0 ? g_prefill_bn : choose_tile_width((M + BM - 1) / BM, N, step);
-    if (g_prefill_variant == 3 && M > BM) {
-      // CTA pairs, 256 x 256 tiles
-      if (!make_map(&mw, A, M, K, lda, BM)) return QV_ERR_UNSUPPORTED;
-      if (packed) mn = mw;
-      else if (!make_map(&mn, W, N, K, ldw, BM)) return QV_ERR_UNSUPPORTED;
-      const int pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
-      int rc;
-      if (epilogue == 1) rc = launch_pair<6, bf16, true>(mw, mn, args, pair_tiles, st);
-      else if (c_dt == QV_DT_BF16) rc = launch_pair<6, bf16, false>(mw, mn, args, pair_tiles, st);
-      else rc = launch_pair<6, float, false>(mw, mn, args, pair_tiles, st);
-      if (rc != QV_ERR_UNSUPPORTED) return rc;
-    }
-    // persistent kernel, 128 x bn tiles, accumulator double-buffered in tensor memory
-    if (bn < step || bn > 256 || bn % step) return QV_ERR_UNSUPPORTED;
-    args.bn = bn;
-    if (!make_map(&mw, A, M, K, lda, BM)) return QV_ERR_UNSUPPORTED;
-    if (packed) mn = mw;
-    else if (!make_map(&mn, W, N, K, ldw, bn)) return QV_ERR_UNSUPPORTED;
-    const int total_tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
-    if (epilogue == 1) return launch_persistent<256, 4, bf16, true>(mw, mn, args, total_tiles, st);
-    if (c_dt == QV_DT_BF16) return launch_persistent<256, 4, bf16, false>(mw, mn, args, total_tiles, st);
-    return launch_persistent<256, 4, float, false>(mw, mn, args, total_tiles, st);
-  }
+  const int step = epilogue == 1 ? 32 : 16;
+  const int bn = g_prefill_bn > 0 ? g_prefill_bn : choose_tile_width((M + BM - 1) / BM, N, step);
+  // persistent kernel, 128 x bn tiles, accumulator double-buffered in tensor memory
+  if (bn < step || bn > 256 || bn % step) return QV_ERR_UNSUPPORTED;
+  args.bn = bn;
   if (!make_map(&mw, A, M, K, lda, BM)) return QV_ERR_UNSUPPORTED;
   if (packed) mn = mw;
-  else if (!make_map(&mn, W, N, K, ldw, 128)) return QV_ERR_UNSUPPORTED;
-  dim3 grid((M + BM - 1) / BM, (N + 127) / 128, 1);
-  if (grid.y > 65535) return QV_ERR_TOO_LARGE;
-  if (epilogue == 1) return launch<128, 3, false, bf16, true>(mw, mn, args, grid, st);
-  if (c_dt == QV_DT_BF16) return launch<128, 3, false, bf16>(mw, mn, args, grid, st);
-  return launch<128, 3, false, float>(mw, mn, args, grid, st);
+  else if (!make_map(&mn, W, N, K, ldw, bn)) return QV_ERR_UNSUPPORTED;
+  const int total_tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+  if (epilogue == 1) return launch_persistent<256, 4, bf16, true>(mw, mn, args, total_tiles, st);
+  if (c_dt == QV_DT_BF16) return launch_persistent<256, 4, bf16, false>(mw, mn, args, total_tiles, st);
+  return launch_persistent<256, 4, float, false>(mw, mn, args, total_tiles, st);
 }
 
 // The QKV projection of more than 64 tokens with the rotation of query and key heads and the write
@@ -1085,7 +773,7 @@ extern "C" int qv_gemm_bf16_qkv_rope(void* C, const void* A, const void* packed,
                                      const float* cos_sin, int table_rows, const int* tok_pos, const int* tok_seg,
                                      const int* block_table, int max_blocks, void* cache, int H, int Hkv, int hd, int page_size,
                                      void* stream) {
-  if (M <= 64 || g_prefill_variant != 0 || !packed || !cache || !cos_sin) return QV_ERR_UNSUPPORTED;
+  if (M <= 64 || !packed || !cache || !cos_sin) return QV_ERR_UNSUPPORTED;
   if ((hd != 64 && hd != 128) || H <= 0 || Hkv <= 0 || page_size <= 0 || table_rows <= 0) return QV_ERR_UNSUPPORTED;
   const long long n_ll = (long long)(H + 2 * Hkv) * hd;
   if (n_ll > 0x7fffffffLL) return QV_ERR_TOO_LARGE;
@@ -1143,13 +831,13 @@ extern "C" int qv_gemm_bf16_norm(void* C, const void* A, const void* packed, int
   dim3 grid(tiles, 1, splits);
   cudaStream_t st = (cudaStream_t)stream;
 #define NORM_LAUNCH(BN_, ST_)                                                                     \
-  (c_dt == QV_DT_BF16 ? launch<BN_, ST_, true, bf16>(mn, mn, args, grid, st, na) : launch<BN_, ST_, true, float>(mn, mn, args, grid, st, na))
+  (c_dt == QV_DT_BF16 ? launch<BN_, ST_, bf16>(mn, mn, args, grid, st, na) : launch<BN_, ST_, float>(mn, mn, args, grid, st, na))
   if (epilogue == 1) {
-    if (bn == 16) return launch<16, 6, true, bf16, true>(mn, mn, args, grid, st, na);
-    if (bn == 32) return launch<32, 5, true, bf16, true>(mn, mn, args, grid, st, na);
-    return launch<64, 4, true, bf16, true>(mn, mn, args, grid, st, na);
+    if (bn == 16) return launch<16, 6, bf16, true>(mn, mn, args, grid, st, na);
+    if (bn == 32) return launch<32, 5, bf16, true>(mn, mn, args, grid, st, na);
+    return launch<64, 4, bf16, true>(mn, mn, args, grid, st, na);
   }
-  const bool one_wave = tiles * splits <= 148;
+  const bool one_wave = tiles * splits <= device_sms();
   if (bn == 16) return one_wave ? NORM_LAUNCH(16, 12) : NORM_LAUNCH(16, 6);
   if (bn == 32) return one_wave ? NORM_LAUNCH(32, 10) : NORM_LAUNCH(32, 5);
   return one_wave ? NORM_LAUNCH(64, 8) : NORM_LAUNCH(64, 4);

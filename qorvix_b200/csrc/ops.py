@@ -43,7 +43,6 @@ _ARGTYPES = {
     "qv_gemm_bf16_packed": [_V, _V, _V, _I, _I, _I, _I, _I, _I, _V, _I, _I, _V],
     "qv_gemm_bf16_qkv_rope": [_V, _V, _V, _I, _I, _I, _I, _V, _V, _I, _V, _V, _V, _I, _V, _I, _I, _I, _I, _V],
     "qv_gemm_bf16_norm": [_V, _V, _V, _I, _I, _I, _I, _I, _I, _V, _I, _V, _I, _V, _V, _V, _I, _F, _F, _V],
-    "qv_gemm_bf16_set_prefill_variant": [_I],
     "qv_gemm_bf16_set_prefill_bn": [_I],
     "qv_attention_generic": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V],
     "qv_attn_prefill_bf16": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V],
@@ -304,6 +303,13 @@ def gemm_bf16_norm(c, a, packed, N: int, swiglu: bool = False, residual=None, no
     return True
 
 
+def new_norm_stats(features: int, device) -> torch.Tensor:
+    """The buffer gemm_bf16_norm leaves a stream's sums of squares in (per tile of 128 features of the
+    few-token kernel, for its 64 token columns); what it holds is between the producing and the
+    consuming launch of that kernel."""
+    return torch.empty((-(-features // 128), 64), device=device, dtype=torch.float32)
+
+
 def folded_norm_enabled(tokens: int) -> bool:
     """Whether the RMS norms of a step of `tokens` tokens ride in the epilogues of the products around
     them: up to 16 tokens (one chunk of the epilogue, whose stream values are fetched while the main loop
@@ -346,13 +352,6 @@ def gemm_qkv_rope(qkv, x, packed, cache_layer, cos_sin, tok_pos, tok_seg, block_
         return False
     _check(rc, "gemm_qkv_rope")
     return True
-
-
-def gemm_bf16_set_prefill_variant(variant: int) -> None:
-    """0 (default): more than 64 tokens run on the persistent kernel (128 x 256 or 128 x 128 tiles,
-    double-buffered accumulator); 1: on the one-tile-per-CTA kernel (128 x 128 tiles); 3: on CTA pairs
-    (tcgen05.mma.cta_group::2, 256 x 256 tiles) where there are more than 128 tokens."""
-    _lib("gemm_bf16").qv_gemm_bf16_set_prefill_variant(variant)
 
 
 def gemm_bf16_set_prefill_tile_width(bn: int) -> None:
@@ -463,6 +462,18 @@ def attention_prefill_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table
 
 
 _decode_variant_forced = None
+_sm_count = None
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (asked once); without a device, as on a
+    machine that only plans steps, the B200's 148."""
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = 148
+        if torch.cuda.is_available():
+            _sm_count = int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+    return _sm_count
 
 
 def decode_variant(T: int, Hkv: int) -> int:
@@ -484,17 +495,18 @@ def decode_splits(T: int, Hkv: int, max_ctx: int, known: bool = True) -> int:
     if decode_variant(T, Hkv) == 0 and not known:
         # a captured step is replayed at contexts from a few keys up to max_ctx: one wave of CTAs, no
         # more (more slices than that pay only at long contexts and cost up to a third at short ones)
-        return max(1, min(16, (2 * 148) // pairs, max_ctx // 256))
+        return max(1, min(16, (2 * sm_count()) // pairs, max_ctx // 256))
     if decode_variant(T, Hkv) == 0:
-        # 296 CTAs run at once; a CTA's time is its slice of the keys plus a fixed part worth about
+        # two CTAs per SM run at once; a CTA's time is its slice of the keys plus a fixed part worth about
         # 256 keys.  The count that needs the least time over all waves, the smaller one on a tie.
         best, best_cost = 1, None
+        resident = 2 * sm_count()
         for s in range(1, max(1, min(16, max_ctx // 256)) + 1):
-            cost = -(-pairs * s // 296) * (-(-max_ctx // s) + 256)
+            cost = -(-pairs * s // resident) * (-(-max_ctx // s) + 256)
             if best_cost is None or cost < best_cost:
                 best, best_cost = s, cost
         return best
-    return max(1, min(16, -(-3 * 148 // pairs), -(-max_ctx // 64)))
+    return max(1, min(16, -(-3 * sm_count() // pairs), -(-max_ctx // 64)))
 
 
 def attention_decode_bf16(out, q, cache_layer, tok_pos, tok_seg, block_table, H, Hkv, hd, page, window, scale,

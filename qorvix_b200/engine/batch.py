@@ -45,7 +45,6 @@ class StepContext:
     max_q_len: int = 0
     max_ctx_len: int = 0
     captured: bool = False             # the step is being captured or replayed as a CUDA graph
-    fused: object = None               # engine.fused_decode.FusedDecode of a captured decode step, if the model allows
     next_norm: object = None           # set by the model before each block: the norm the block after it starts with
 
     @property

@@ -23,7 +23,6 @@ import torch
 
 from ..csrc import ops
 from .batch import StepContext
-from .fused_decode import FusedDecode
 
 
 def _bucket(n: int) -> int:
@@ -73,7 +72,6 @@ class DecodeGraph:
             seg_len=[1] * S, seg_start_pos=[0] * S, seg_slots=[cache.scratch_slot] * S, seg_first=[False] * S,
             max_q_len=1, max_ctx_len=runner.max_model_len)
         self.ctx.captured = True
-        self.ctx.fused = FusedDecode.try_build(runner.model, cache, self.ctx, S)
         self.next_ids = torch.zeros(S, dtype=torch.int32, device=dev)
         self.logits = None
         self.graph = None

@@ -40,6 +40,8 @@ def llama_spec(cfg: LlamaConfig) -> ModelSpec:
         final_norm=RMSNormSpec(cfg.hidden_size, cfg.rms_norm_eps, "model.norm.weight"),
         lm_head=None if tied else "lm_head.weight",
         optional_tensors=("lm_head.weight",) if tied else (),
+        # older checkpoints of this architecture store each layer's rotary frequencies as a buffer
+        ignored_tensors=("model.layers.*.self_attn.rotary_emb.inv_freq",),
         max_position=cfg.max_position_embeddings)
 
 

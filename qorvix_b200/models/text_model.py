@@ -19,7 +19,7 @@ class TextModel:
     def __init__(self, spec, source, rt: Runtime):
         self.spec = spec
         self.rt = rt
-        source.check(spec.expected_shapes(), optional=spec.optional_tensors)
+        source.check(spec.expected_shapes(), optional=spec.optional_tensors, ignored=getattr(spec, "ignored_tensors", ()))
         self.embedding = source.get(spec.embedding)
         self.blocks = [build_part("block", _BlockView(layer), source, rt) for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, source, rt)
@@ -51,11 +51,6 @@ class TextModel:
         T = ctx.num_tokens
         residual = torch.empty((T, self.spec.hidden_size), device=self.rt.device, dtype=torch.float32)
         ops.embed(residual, self.embedding, ctx.token_ids)
-        fused = getattr(ctx, "fused", None)
-        if fused is not None:
-            # a captured decode step of a model the fused kernel takes: all layers and the final norm
-            # in one launch; every row is wanted
-            return self.lm_head(fused.run(residual), out_dtype=torch.float32)
         pending = None
         for run, li in enumerate(self.order):
             # which norm reads the stream after this block (a block that can prepares that norm's input);

@@ -13,6 +13,10 @@ Norm          add_norm(residual, delta, rows=None): residual (float32) += delta 
               the normed rows in the compute dtype; with rows (int32 row indices) only those rows of
               residual + delta are normed and the residual is left as it is.  The sum and the norm
               are computed in float32.
+              A norm that is  x * rsqrt(mean(x^2) + eps) * w  for some per-feature w may declare
+              folds_into_products = True and give size, eps and scale_weight() (w as float32): parts
+              that fold norms then take its two passes over the stream into the epilogues of the
+              products around it.  Nothing else about the norm is assumed.
 Position      table() -> float32 [positions, rotary_dim/2, 2] of (cos, sin) if it is a rotation
               the attention kernels can fuse, else None; apply(qkv, ctx, H, Hkv, hd) rotates q and k
               in place for mixers that do not fuse it.
@@ -42,13 +46,15 @@ class Runtime:
 
 @dataclass
 class PreNormed:
-    """The input of an RMS norm as the product ahead of it left it: `scaled` is the float32 residual
-    stream times the norm's weight (compute dtype, not yet divided by the root mean square) and `ssq`
-    the stream's sums of squares per tile of 128 features, [tiles, 64 tokens].  The residual stream
-    already holds the product, so nothing is pending.  A consumer either scales the sums of its own
-    product by rsqrt(mean of squares + eps) or calls materialise() for the normed rows."""
+    """The input of a folding norm as the product ahead of it left it: `scaled` is the float32 residual
+    stream times the norm's weight (compute dtype, not yet divided by the root mean square) and
+    `stats` what the producing kernel left of the stream's squares; only the kernels that produce and
+    consume it (Linear.forward_to_stream / forward_prenormed) know its layout.  The residual stream
+    already holds the product, so nothing is pending.  A consumer either hands it to a Linear, which
+    scales the sums of its own product by rsqrt(mean of squares + eps), or calls materialise() for the
+    normed rows."""
     scaled: torch.Tensor
-    ssq: torch.Tensor
+    stats: object
     norm: object
     residual: torch.Tensor
 
@@ -73,7 +79,12 @@ class FeedForward:
 
 
 class Norm:
+    folds_into_products = False        # True: see the module's header; needs size, eps, scale_weight()
+
     def add_norm(self, residual, delta, rows=None):
+        raise NotImplementedError
+
+    def scale_weight(self):
         raise NotImplementedError
 
 

@@ -6,7 +6,6 @@ from __future__ import annotations
 
 from ..csrc import ops
 from .base import Block, PreNormed
-from .rmsnorm import RMSNorm
 from .registry import build_part, register_part
 
 
@@ -18,7 +17,7 @@ class PreNormBlock(Block):
         self.feed_forward = build_part("feed_forward", spec.feed_forward, source, rt)
 
     def forward(self, residual, pending, ctx, cache):
-        # Few tokens: a part that folds norms (folds_norms) is told which RMS norm reads the stream
+        # Few tokens: a part that folds norms (folds_norms) is told which norm (one that folds into products) reads the stream
         # after it; it may then add its output to the stream in its last product's epilogue and hand
         # on that norm's half-done input (a PreNormed) instead of a delta, and the part after the norm
         # finishes the norm in its first product.  Anything else takes the norm kernel.
@@ -28,13 +27,13 @@ class PreNormBlock(Block):
             x = self._normed(self.mixer_norm, self.mixer, residual, pending)
             if fold and getattr(self.mixer, "folds_norms", False):
                 nxt = self.ffn_norm if self.feed_forward is not None else after
-                pending = self.mixer.forward(x, ctx, cache, residual=residual, next_norm=nxt if type(nxt) is RMSNorm else None)
+                pending = self.mixer.forward(x, ctx, cache, residual=residual, next_norm=nxt if _folds(nxt) else None)
             else:
                 pending = self.mixer.forward(x, ctx, cache)
         if self.feed_forward is not None:
             x = self._normed(self.ffn_norm, self.feed_forward, residual, pending)
             if fold and getattr(self.feed_forward, "folds_norms", False):
-                pending = self.feed_forward.forward(x, ctx, residual=residual, next_norm=after if type(after) is RMSNorm else None)
+                pending = self.feed_forward.forward(x, ctx, residual=residual, next_norm=after if _folds(after) else None)
             else:
                 pending = self.feed_forward.forward(x, ctx)
         return residual, pending
@@ -52,6 +51,11 @@ class PreNormBlock(Block):
         if self.mixer is not None:
             return self.mixer_norm
         return self.ffn_norm if self.feed_forward is not None else None
+
+
+def _folds(norm) -> bool:
+    """Whether a norm lets the products around it take over its passes (see parts/base.py)."""
+    return norm is not None and getattr(norm, "folds_into_products", False)
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -18,8 +18,8 @@ class Linear:
         self.out_features, self.in_features = weight.shape
         # A bfloat16 matrix is stored as the 16 KB tiles the MMA consumes (128 rows x 64 k in its
         # swizzled shared-memory layout), which HBM and an SM's copy engine deliver faster than
-        # rows; the rows are then dropped (keep_rows, or QORVIX_KEEP_ROWS=1, keeps them: the
-        # opt-in fused decode kernel and tests that compare the two layouts read rows).
+        # rows; the rows are then dropped (keep_rows, or QORVIX_KEEP_ROWS=1, keeps them, for tests
+        # that compare the two layouts).
         self.packed = None
         if (self.weight.is_cuda and self.weight.dtype == torch.bfloat16 and self.in_features % 8 == 0
                 and ops.packed_weights_enabled()):
@@ -46,23 +46,23 @@ class Linear:
         sums); False, nothing written, when the kernel does not take the product."""
         if self.packed is None:
             return False
-        return ops.gemm_bf16_norm(out, pre.scaled, self.packed, self.out_features, swiglu=swiglu, ssq_in=pre.ssq,
+        return ops.gemm_bf16_norm(out, pre.scaled, self.packed, self.out_features, swiglu=swiglu, ssq_in=pre.stats,
                                   stream_width=pre.norm.size, eps=pre.norm.eps)
 
     def forward_to_stream(self, x: torch.Tensor, residual: torch.Tensor, norm):
-        """residual += x W^T in the product's epilogue; returns the PreNormed input of `norm` (an RMS
-        norm over the stream), or None, nothing written, when the kernel does not take the product."""
+        """residual += x W^T in the product's epilogue; returns the PreNormed input of `norm` (one that
+        declares folds_into_products), or None, nothing written, when the kernel does not take the product."""
         M, N = x.shape[0], self.out_features
         if (self.packed is None or M > 64 or x.dtype != torch.bfloat16 or residual.dtype != torch.float32
                 or tuple(residual.shape) != (M, N) or residual.stride(1) != 1 or norm.size != N):
             return None
         scaled = torch.empty((M, N), device=x.device, dtype=x.dtype)
-        ssq = torch.empty((-(-N // 128), 64), device=x.device, dtype=torch.float32)
-        if not ops.gemm_bf16_norm(scaled, x, self.packed, N, residual=residual, norm_weight=norm.weight, ssq_out=ssq):
+        stats = ops.new_norm_stats(N, x.device)
+        if not ops.gemm_bf16_norm(scaled, x, self.packed, N, residual=residual, norm_weight=norm.scale_weight(), ssq_out=stats):
             return None
-        return PreNormed(scaled=scaled, ssq=ssq, norm=norm, residual=residual)
+        return PreNormed(scaled=scaled, stats=stats, norm=norm, residual=residual)
 
 
 def _keep_rows() -> bool:
     import os
-    return os.environ.get("QORVIX_KEEP_ROWS", "0") == "1" or os.environ.get("QORVIX_FUSED_DECODE", "0") == "1"
+    return os.environ.get("QORVIX_KEEP_ROWS", "0") == "1"

@@ -17,6 +17,11 @@ class RMSNorm(Norm):
         self.weight = source.get(spec.weight, dtype=torch.float32)   # tiny; always read as float32
         self.rt = rt
 
+    folds_into_products = True         # x * rsqrt(mean(x^2) + eps) * weight
+
+    def scale_weight(self):
+        return self.weight
+
     def add_norm(self, residual, delta, rows=None):
         """residual[T,d] float32 (+= delta in place when rows is None).  rows: int32 row
         indices; then only those rows are normed and the residual is left as it is."""

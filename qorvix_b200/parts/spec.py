@@ -112,6 +112,7 @@ class ModelSpec:
     lm_head: Optional[str]                    # None: the head is the embedding table (tied)
     order: List[int] = None                   # layer indices in execution order; may repeat
     optional_tensors: Tuple[str, ...] = ()    # may be stored but are not used (e.g. a tied head's copy)
+    ignored_tensors: Tuple[str, ...] = ()     # name patterns (fnmatch) of stored buffers that are no weights
     max_position: int = 0
 
     def __post_init__(self):

@@ -106,13 +106,19 @@ class TensorSource:
     def shape(self, name):
         return tuple(self._tensors[name].shape) if self._tensors is not None else self._ckpt.shape(name)
 
-    def check(self, expected: Mapping[str, Tuple[int, ...]], optional: Iterable[str] = ()) -> None:
+    def check(self, expected: Mapping[str, Tuple[int, ...]], optional: Iterable[str] = (), ignored: Iterable[str] = ()) -> None:
         """Raises WeightError unless the stored names and shapes are exactly the expected ones
-        (names in `optional` may be present or absent)."""
+        (names in `optional` may be present or absent; names that match a pattern of `ignored` are
+        buffers some checkpoints of the architecture store beside the weights, such as a rotary
+        table, and are passed over).  The reference reads optional tensors the same way
+        (runtime/include/qorvix/runtime/tensor_load.hpp:82-92) and never looks at names it does not ask for."""
+        import fnmatch
         have = set(self.names())
         optional = set(optional)
+        ignored = tuple(ignored)
         missing = [n for n in expected if n not in have and n not in optional]
-        unexpected = [n for n in have if n not in expected and n not in optional]
+        unexpected = [n for n in have if n not in expected and n not in optional
+                      and not any(fnmatch.fnmatchcase(n, pat) for pat in ignored)]
         wrong = [(n, self.shape(n), tuple(expected[n])) for n in expected
                  if n in have and tuple(self.shape(n)) != tuple(expected[n])]
         if missing or unexpected or wrong:

@@ -15,7 +15,7 @@ from qorvix_b200.weights import random_tensors, write_safetensors
 
 ARCH = "LlamaForCausalLM"
 
-# Three tiny configurations that differ in every size and option.
+# Tiny configurations that differ in every size and option.
 TINY_A = LlamaConfig(architecture=ARCH, vocab_size=256, hidden_size=64, intermediate_size=172,
                      num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, head_dim=16,
                      max_position_embeddings=128, rms_norm_eps=1e-5, rope_theta=10000.0,
@@ -29,7 +29,17 @@ TINY_C = LlamaConfig(architecture=ARCH, vocab_size=331, hidden_size=144, interme
                      num_hidden_layers=4, num_attention_heads=5, num_key_value_heads=1, head_dim=48,
                      max_position_embeddings=512, rms_norm_eps=3e-6, rope_theta=25000.0,
                      rope_scaling=RopeScaling("llama3", 4.0, 1.0, 2.0, 128), tie_word_embeddings=False)
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# head sizes 64 and 128: the sizes the tcgen05 attention kernel, the tiled mma.sync kernel and the
+# projection with rotation and cache write in its epilogue are written for
+TINY_D = LlamaConfig(architecture=ARCH, vocab_size=410, hidden_size=256, intermediate_size=512,
+                     num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                     max_position_embeddings=640, rms_norm_eps=2e-6, rope_theta=300000.0,
+                     rope_scaling=RopeScaling("llama3", 16.0, 1.0, 4.0, 96), tie_word_embeddings=True)
+TINY_E = LlamaConfig(architecture=ARCH, vocab_size=275, hidden_size=512, intermediate_size=1024,
+                     num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1, head_dim=128,
+                     max_position_embeddings=768, rms_norm_eps=1e-5, rope_theta=40000.0,
+                     tie_word_embeddings=False)
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 FP32_TOL = 1e-4       # of max |logit|, float32 engine against the float64 plain implementation
 BF16_TOL = 2e-2       # of max |logit|, bfloat16 engine against the same
@@ -97,3 +107,45 @@ def assert_close_logits(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: 
         first = int(bad[0])
         raise AssertionError(f"{what}: {bad.numel()} of {err.numel()} rows off; first wrong row {first} "
                              f"(err {float(err[first]):.3e}, allowed {tol_of(dtype, sharp) * scale:.3e}, max err {float(err.max()):.3e})")
+
+
+class CallCounter:
+    """Counts the successful calls of functions of qorvix_b200.csrc.ops, so that a test can prove
+    which kernels served it:  with CallCounter(monkeypatch, "attention_prefill_tc") as n: ...; n["attention_prefill_tc"]."""
+
+    def __init__(self, monkeypatch, *names):
+        from qorvix_b200.csrc import ops
+        self.counts = {n: 0 for n in names}
+        for n in names:
+            monkeypatch.setattr(ops, n, self._wrap(n, getattr(ops, n)))
+
+    def _wrap(self, name, fn):
+        def counted(*a, **kw):
+            res = fn(*a, **kw)
+            if res is None or res:
+                self.counts[name] += 1
+            return res
+        return counted
+
+    def __getitem__(self, name):
+        return self.counts[name]
+
+
+def assert_greedy_follows_plain(pm, prompt, got, what: str = "", gap: float = 0.05, at_least: int = 1) -> int:
+    """`got` must be the plain implementation's greedy tokens, token for token, up to the first place
+    where the plain top-2 gap is under `gap` of max |logit| (a near tie that rounding may decide
+    either way; nothing after it is compared).  Returns how many tokens were compared and raises when
+    fewer than `at_least` were."""
+    seq = list(prompt)
+    compared = 0
+    for i, tok in enumerate(got):
+        full = pm.logits(seq)[-1]
+        top = torch.topk(full, 2)
+        if float(top.values[0] - top.values[1]) < gap * float(full.abs().max()):
+            break
+        want = int(top.indices[0])
+        assert int(tok) == want, f"{what}: generated token {i} is {tok}, the plain implementation's is {want} (so far {list(got[:i])})"
+        seq.append(int(tok))
+        compared += 1
+    assert compared >= at_least, f"{what}: only {compared} tokens could be compared before a near tie; pick another prompt"
+    return compared

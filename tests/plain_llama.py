@@ -153,13 +153,15 @@ def softmax(scores: torch.Tensor) -> torch.Tensor:
     return e / e.sum(dim=-1, keepdim=True)
 
 
-def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int = 0) -> torch.Tensor:
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int = 0, rows=None) -> torch.Tensor:
     """Causal grouped-query attention over one whole sequence.
 
     q[T,H,hd], k,v[T,Hkv,hd] -> [T,H,hd].  kvHead = h / (H/Hkv); score =
     (q.k)/sqrt(hd) for t <= pos; softmax; weighted sum of V
     (runtime/src/text_model.cpp:83-114).  `window` > 0 keeps only the last `window`
     keys (pos - window < t <= pos); the reference has no window, 0 means all keys.
+    `rows`: only these positions are computed (the others stay zero), for long sequences of
+    which a test looks at a few places.
     """
     T, H, hd = q.shape
     Hkv = k.shape[1]
@@ -168,7 +170,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int = 0
     inv_sqrt = 1.0 / math.sqrt(hd)
     for h in range(H):
         kvh = h // group
-        for pos in range(T):
+        for pos in (range(T) if rows is None else rows):
             lo = 0 if window <= 0 else max(0, pos - window + 1)
             s = (k[lo:pos + 1, kvh, :] @ q[pos, h, :]) * inv_sqrt
             p = softmax(s)
@@ -193,8 +195,9 @@ def head_dim_of(cfg: dict) -> int:
     return int(hd) if hd else int(cfg["hidden_size"]) // int(cfg["num_attention_heads"])
 
 
-def attention_block(x, w, prefix, cfg, positions, inv_freq):
-    """norm -> q,k,v -> rope(q), rope(k) -> attention -> o-proj (runtime/src/text_model.cpp:146-158)."""
+def attention_block(x, w, prefix, cfg, positions, inv_freq, rows=None):
+    """norm -> q,k,v -> rope(q), rope(k) -> attention -> o-proj (runtime/src/text_model.cpp:146-158).
+    With `rows` the output holds those positions only (keys and values are still the whole sequence's)."""
     H = int(cfg["num_attention_heads"])
     Hkv = int(cfg.get("num_key_value_heads") or H)
     hd = head_dim_of(cfg)
@@ -205,7 +208,9 @@ def attention_block(x, w, prefix, cfg, positions, inv_freq):
     v = linear(xn, w[prefix + "self_attn.v_proj.weight"]).reshape(T, Hkv, hd)
     q = rope(q, positions, inv_freq)
     k = rope(k, positions, inv_freq)
-    a = attention(q, k, v).reshape(T, H * hd)
+    a = attention(q, k, v, rows=rows).reshape(T, H * hd)
+    if rows is not None:
+        a = a[torch.as_tensor(list(rows), dtype=torch.long, device=a.device)]
     return linear(a, w[prefix + "self_attn.o_proj.weight"])
 
 
@@ -224,16 +229,23 @@ def lm_head_weight(w: dict, cfg: dict) -> torch.Tensor:
     return w["model.embed_tokens.weight"]
 
 
-def forward(cfg: dict, weights: dict, token_ids, dtype=torch.float64) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence (runtime/src/text_model.cpp:133-176)."""
+def forward(cfg: dict, weights: dict, token_ids, dtype=torch.float64, rows=None) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence (runtime/src/text_model.cpp:133-176).  With `rows`
+    only the logits at those positions, [len(rows), vocab]: the last layer's attention, feed-forward
+    and the head then run on those positions alone (the layers before it need every position)."""
     w = {k: v.to(dtype) for k, v in weights.items()}
     T = len(token_ids)
     positions = torch.arange(T)
     inv_freq = inv_freq_from_config(cfg)
     x = embedding(w["model.embed_tokens.weight"], token_ids)
-    for layer in range(int(cfg["num_hidden_layers"])):
+    n_layers = int(cfg["num_hidden_layers"])
+    for layer in range(n_layers):
         prefix = f"model.layers.{layer}."
-        x = x + attention_block(x, w, prefix, cfg, positions, inv_freq)
+        if rows is not None and layer == n_layers - 1:
+            idx = torch.as_tensor(list(rows), dtype=torch.long, device=x.device)
+            x = x[idx] + attention_block(x, w, prefix, cfg, positions, inv_freq, rows=list(rows))
+        else:
+            x = x + attention_block(x, w, prefix, cfg, positions, inv_freq)
         x = x + feed_forward_block(x, w, prefix, cfg)
     xn = rmsnorm(x, w["model.norm.weight"], float(cfg.get("rms_norm_eps", 1e-5)))
     return linear(xn, lm_head_weight(w, cfg))

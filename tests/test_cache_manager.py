@@ -3,7 +3,7 @@ import random
 
 import pytest
 
-from qorvix_b200.cache import CacheManager, FixedStateSpec, OutOfSlots, PageError, PagedKVSpec, PagePool
+from qorvix_b200.cache import CacheManager, FixedStateSpec, OutOfSlots, PageError, PagedKVSpec, native
 
 KV = PagedKVSpec(num_kv_heads=2, head_dim=16)
 WIN = PagedKVSpec(num_kv_heads=2, head_dim=16, window=40)
@@ -16,16 +16,28 @@ def manager(needs, tokens=256, max_requests=4, allocate=False):
 
 
 def test_pool_hands_out_low_ids_first_and_refuses_double_free():
-    p = PagePool(4)
-    assert p.alloc(2) == [0, 1]
-    assert p.alloc(3) is None and p.num_free == 2          # all or nothing
-    p.free([0])
-    assert p.alloc(1) == [0]                               # freed pages are used again at once
-    with pytest.raises(PageError):
-        p.free([3])                                        # never handed out
-    p.free([1])
-    with pytest.raises(PageError):
-        p.free([1])
+    """The free list of the C++ runtime (csrc/host_runtime.cpp), through its C entry points."""
+    L = native.lib()
+    pool = L.qvh_pool_create(4)
+
+    def alloc(n):
+        out = (native.c_int * max(n, 1))()
+        return list(out[:n]) if L.qvh_pool_alloc(pool, n, out) else None
+
+    def free(pages):
+        return L.qvh_pool_free(pool, native.ints(pages), len(pages))
+
+    try:
+        assert alloc(2) == [0, 1]
+        assert alloc(3) is None and L.qvh_pool_num_free(pool) == 2     # all or nothing
+        assert free([0]) == 0
+        assert alloc(1) == [0]                                          # freed pages are used again at once
+        assert free([3]) == -2 or free([3]) < 0                         # never handed out
+        assert free([1]) == 0
+        assert free([1]) < 0                                            # freed twice
+        assert L.qvh_pool_is_held(pool, 0) and not L.qvh_pool_is_held(pool, 1)
+    finally:
+        L.qvh_pool_destroy(pool)
 
 
 def test_pages_are_taken_on_page_edges():

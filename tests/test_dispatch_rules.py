@@ -78,14 +78,14 @@ def test_pre_norm_block_hands_a_prepared_norm_input_only_to_parts_that_take_it(m
 
         def forward(self, x, ctx, cache, residual=None, next_norm=None):
             calls.append(("mixer", type(x).__name__, next_norm))
-            return PreNormed(scaled=torch.zeros(2, 8), ssq=torch.zeros(1, 64), norm=next_norm, residual=residual)
+            return PreNormed(scaled=torch.zeros(2, 8), stats=torch.zeros(1, 64), norm=next_norm, residual=residual)
 
     class FoldingFfn:
         folds_norms = True
 
         def forward(self, x, ctx, residual=None, next_norm=None):
             calls.append(("ffn", type(x).__name__, next_norm))
-            return PreNormed(scaled=torch.zeros(2, 8), ssq=torch.zeros(1, 64), norm=next_norm, residual=residual)
+            return PreNormed(scaled=torch.zeros(2, 8), stats=torch.zeros(1, 64), norm=next_norm, residual=residual)
 
     class PlainFfn:
         def forward(self, x, ctx):
@@ -130,8 +130,20 @@ def test_pre_norm_block_hands_a_prepared_norm_input_only_to_parts_that_take_it(m
 
     block(CountingMixer(), PlainFfn()).forward(big, None, ctx, None)
     assert ("mixer_kw", []) in calls
-    # no RMS norm after the block (another kind of norm, or the final norm): the last part is told so
+    # no folding norm after the block (another kind of norm, or the final norm): the last part is told so
     calls.clear()
     ctx.next_norm = object()
     block(FoldingMixer(), FoldingFfn()).forward(residual, None, ctx, None)
     assert calls[-1] == ("ffn", "PreNormed", None)
+    # a norm class the package has never seen opts in by declaring the capability, nothing else
+    class ForeignNorm:
+        folds_into_products = True
+        size, eps = 8, 1e-6
+
+        def scale_weight(self):
+            return torch.ones(8)
+
+    calls.clear()
+    ctx.next_norm = ForeignNorm()
+    block(FoldingMixer(), FoldingFfn()).forward(residual, None, ctx, None)
+    assert calls[-1] == ("ffn", "PreNormed", ctx.next_norm)

@@ -27,17 +27,11 @@ def check(M, N, K, out_dtype, force_splits=0, lda=None):
     assert err <= tol * max(1.0, ref.abs().max().item()), f"M={M} N={N} K={K}: max err {err}"
 
 
-# 0: persistent kernel; 1: one 128x128 tile per CTA; 3: CTA pairs (tcgen05.mma.cta_group::2) on 256x256 tiles
-@pytest.mark.parametrize("variant", [0, 1, 3])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 256), (256, 384, 4096), (200, 1000, 328),
                                    (2048, 6144, 4096), (65, 136, 72), (300, 331, 1000), (4000, 2000, 136)])
-def test_many_tokens(M, N, K, out_dtype, variant):
-    ops.gemm_bf16_set_prefill_variant(variant)
-    try:
-        check(M, N, K, out_dtype)
-    finally:
-        ops.gemm_bf16_set_prefill_variant(0)
+def test_many_tokens(M, N, K, out_dtype):
+    check(M, N, K, out_dtype)
 
 
 @pytest.mark.parametrize("bn", [16, 48, 112, 128, 144, 240, 256])
@@ -95,16 +89,7 @@ def test_strided_activations_and_refused_shapes():
 
 @pytest.mark.parametrize("M,f,K", [(8, 256, 128), (3, 14336, 256), (40, 512, 4096), (64, 1008, 72), (128, 64, 64),
                                    (300, 1008, 328), (2048, 1024, 512)])
-@pytest.mark.parametrize("variant", [0, 3])
-def test_fused_swiglu_epilogue(M, f, K, variant):
-    ops.gemm_bf16_set_prefill_variant(variant)
-    try:
-        _fused_swiglu_epilogue(M, f, K)
-    finally:
-        ops.gemm_bf16_set_prefill_variant(0)
-
-
-def _fused_swiglu_epilogue(M, f, K):
+def test_fused_swiglu_epilogue(M, f, K):
     g, u = rnd(f, K, seed=5, scale=0.1), rnd(f, K, seed=6, scale=0.1)
     w = torch.stack([g.view(f // 16, 16, K), u.view(f // 16, 16, K)], dim=1).reshape(2 * f, K).contiguous()
     a = rnd(M, K, seed=7)

@@ -266,7 +266,7 @@ def _segments(lens_ctx, H, Hkv, hd, page, seed, window=0):
         for t in range(c):
             cache[pages[t // page], 0, :, t % page] = k[t]
             cache[pages[t // page], 1, :, t % page] = v[t]
-        ref = plain.attention(qfull.double(), k.double(), v.double(), window=window)[c - qlen:]
+        ref = plain.attention(qfull.double(), k.double(), v.double(), window=window, rows=range(c - qlen, c))[c - qlen:]
         qs.append(qfull[c - qlen:].reshape(qlen, H * hd))
         refs.append(ref.reshape(qlen, H * hd))
         pos += list(range(c - qlen, c))
@@ -364,3 +364,52 @@ def test_attention_prefill_tcgen05_finds_a_far_key():
         torch.cuda.synchronize()
         ops.check_kernel_errors()
         assert float(out.view(140, H, hd)[139, 1].float().min()) > 49.0, f"key {far} was not found"
+
+
+# ------------------------------------------------------------------ the lengths the benchmark runs
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("H,Hkv,hd", [(32, 8, 128), (32, 8, 64)])
+def test_attention_decode_bf16_at_8192_keys(H, Hkv, hd, variant):
+    """Single tokens over 8,192 and 5,000 cached keys (512 block-table entries a row), with the slice
+    count the dispatcher picks for such a step and with the most slices; one far key per request is
+    made to dominate one head, so that a slice that is skipped or read twice shows."""
+    page = 16
+    d = _segments([(1, 8192), (1, 5000), (1, 31)], H, Hkv, hd, page, seed=300 + hd)
+    q = d["q"].view(3, H, hd)
+    for s_i, far in ((0, 4097), (1, 0), (0, 8191)):
+        pages = d["bt"][s_i].tolist()
+        head = 1 if far != 8191 else 5                          # kv head 0 serves heads 0..3, kv head 1 heads 4..7
+        kvh = head // (H // Hkv)
+        d["cache"][pages[far // page], 0, kvh, far % page] = (q[s_i, head].float() * 6.0).to(torch.bfloat16)
+        d["cache"][pages[far // page], 1, kvh, far % page] = 50.0
+    ops.attention_set_decode_variant(variant)
+    try:
+        for splits in (ops.decode_splits(3, Hkv, 8192), ops.decode_splits(3, Hkv, 8192, known=False), 16):
+            out = torch.full_like(d["q"], float("nan"))
+            assert ops.attention_decode_bf16(out, d["q"], d["cache"], d["pos"], d["seg"], d["bt"], H, Hkv, hd, page, 0,
+                                             1.0 / math.sqrt(hd), splits)
+            ops.check_kernel_errors()
+            o = out.view(3, H, hd).float()
+            assert float(o[0, 1].min()) > 49.0 and float(o[1, 1].min()) > 49.0 and float(o[0, 5].min()) > 49.0, f"splits {splits}: a far key was missed"
+            untouched = torch.ones(3, H, dtype=torch.bool)
+            untouched[0, 0:8] = False; untouched[1, 0:4] = False       # heads that share a kv head with a planted key
+            ref = d["ref"].view(3, H, hd)
+            assert torch.allclose(out.view(3, H, hd).double().cpu()[untouched], ref[untouched], rtol=2e-2, atol=2e-2), f"splits {splits}"
+    finally:
+        ops.attention_set_decode_variant(None)
+
+
+@pytest.mark.parametrize("H,Hkv,hd,lens", [(32, 8, 128, [(2048, 2048)]), (8, 2, 128, [(2048, 4096), (100, 100)]),
+                                           (8, 2, 64, [(2048, 2048), (1, 700)])])
+def test_attention_prefill_tcgen05_at_2048_tokens(H, Hkv, hd, lens):
+    """A whole 2,048-token prompt (the benchmark's prefill), and a 2,048-token portion that follows
+    2,048 cached tokens, against float64."""
+    page = 16
+    d = _segments(lens, H, Hkv, hd, page, seed=400 + hd + H)
+    out = torch.full_like(d["q"], float("nan"))
+    assert ops.attention_prefill_tc(out, d["q"], d["cache"], d["qstart"], d["pos0"], d["bt"], d["S"], d["max_q"], H, Hkv, hd,
+                                    page, 0, 1.0 / math.sqrt(hd))
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    assert torch.allclose(out.double().cpu(), d["ref"], rtol=2e-2, atol=2e-2)

@@ -88,3 +88,30 @@ def test_sampler_filters():
     assert plain.sample_with_uniform(logits, 0.999, 1.0, top_k=1) == 1
     pen = plain.apply_penalties(logits, [1, 1], repetition_penalty=2.0, frequency_penalty=0.5)
     assert abs(pen[1] - (3.0 / 2.0 - 1.0)) < 1e-6
+
+
+def test_llama3_scaling_is_one_continuous_rule_and_both_implementations_state_it_alike():
+    """The llama3 rule has no counterpart in the reference, so nothing of the reference can pin it.
+    Two things do: its defining properties (the blend meets the kept range at wavelength orig/high
+    and the divided range at orig/low, so the scaled frequencies are continuous and decreasing in
+    i; factor 1 changes nothing), and two statements of it written apart (the loop of the plain
+    implementation and the vectorised one of the engine's rotary part) agreeing at the parameter
+    sets of the configurations the benchmark names."""
+    from qorvix_b200.config import RopeScaling
+    from qorvix_b200.parts.rotary import inverse_frequencies
+    sets = [(128, 500000.0, 8.0, 1.0, 4.0, 8192), (64, 500000.0, 32.0, 1.0, 4.0, 8192), (32, 500000.0, 8.0, 1.0, 4.0, 64),
+            (48, 25000.0, 4.0, 1.0, 2.0, 128), (64, 300000.0, 16.0, 1.0, 4.0, 96), (96, 10000.0, 3.0, 0.5, 8.0, 1000)]
+    for hd, base, factor, low, high, orig in sets:
+        a = plain.llama3_inv_freq(hd, base, factor, low, high, orig)
+        b = inverse_frequencies(hd, base, RopeScaling("llama3", factor, low, high, orig))
+        assert torch.allclose(a, b.double(), rtol=1e-14, atol=0), (hd, base, factor)
+        assert bool((a[1:] < a[:-1]).all()), "scaled frequencies decrease with i"
+        f = plain.plain_inv_freq(hd, base)
+        assert bool((a <= f * (1 + 1e-15)).all()) and bool((a >= f / factor * (1 - 1e-15)).all())
+    # continuity at the two edges: a frequency a hair inside the blend equals the neighbouring regime's value
+    orig, low, high, factor = 8192.0, 1.0, 4.0, 8.0
+    for wavelen, want in ((orig / high, 1.0), (orig / low, 1.0 / factor)):
+        fi = 2 * np.pi / wavelen
+        s = (orig / wavelen - low) / (high - low)
+        blended = (1.0 - s) * fi / factor + s * fi
+        assert abs(blended / fi - want) < 1e-12

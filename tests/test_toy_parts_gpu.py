@@ -277,3 +277,96 @@ def test_toy_parts_of_every_category_are_registered_built_and_stepped(toy, dtype
         got_a.append(r.step([StepEntry("a", [a[i]], [0])]))
     assert_close_logits(torch.cat(got_a), ref_a, dtype, "toy parts, request a in portions")
     assert_close_logits(torch.cat(got_b), ref_b, dtype, "toy parts, request b in portions")
+
+
+# ------------------------------------------------------------------ a norm of its own that folds into the products
+
+@dataclass(frozen=True)
+class OnePlusRMSSpec:
+    """x * rsqrt(mean(x^2) + eps) * (1 + w): not the framework's norm, but of the family whose two
+    passes over the stream the few-token products can take over."""
+    size: int
+    eps: float
+    weight: str
+    kind: str = "toy_one_plus_rms"
+
+    def tensors(self):
+        return {self.weight: ((self.size,), "matrix")}
+
+
+class OnePlusRMS(Norm):
+    folds_into_products = True
+
+    def __init__(self, spec, source, rt):
+        self.size, self.eps, self.rt = spec.size, spec.eps, rt
+        self.w1 = (1.0 + source.get(spec.weight, dtype=torch.float32)).contiguous()
+
+    def scale_weight(self):
+        return self.w1
+
+    def add_norm(self, residual, delta, rows=None):
+        if delta is not None and not hasattr(delta, "materialise"):
+            residual += delta.float()
+        x = residual if rows is None else residual[rows.long()]
+        return (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + self.eps) * self.w1).to(self.rt.dtype)
+
+
+def test_a_toy_norm_opts_into_folding_without_a_change_to_the_package(monkeypatch):
+    """Llama-shaped layers whose norms are the toy (1 + w) RMS norm above: in decode steps of the
+    bfloat16 engine the products around the norms take over its passes (the folding kernel is seen
+    to run) and the logits are those of float64 arithmetic with the same norm."""
+    from helpers import CallCounter
+    from qorvix_b200.parts import SwiGLUSpec
+    d, heads, kvh, hd, f, vocab, eps = 512, 4, 2, 128, 1024, 211, 1e-5
+
+    def spec(cfg):
+        layers = []
+        for i in range(2):
+            p = f"l{i}."
+            layers.append(LayerSpec(
+                mixer=AttentionSpec(hidden_size=d, num_heads=heads, num_kv_heads=kvh, head_dim=hd, scale=hd ** -0.5, q_proj=p + "q",
+                                    k_proj=p + "k", v_proj=p + "v", o_proj=p + "o", position=RotarySpec(hd, hd, 10000.0)),
+                feed_forward=SwiGLUSpec(d, f, p + "gate", p + "up", p + "down"),
+                mixer_norm=OnePlusRMSSpec(d, eps, p + "n1"), ffn_norm=OnePlusRMSSpec(d, eps, p + "n2")))
+        return ModelSpec(architecture="ToyNormLM", vocab_size=vocab, hidden_size=d, embedding="emb", layers=layers,
+                         final_norm=OnePlusRMSSpec(d, eps, "fn"), lm_head="head", max_position=128)
+
+    g = torch.Generator().manual_seed(5)
+    tensors = {}
+    for name, (shape, _) in spec(None).tensor_table().items():
+        t = torch.randn(shape, generator=g)
+        t = 0.2 * t if len(shape) == 1 else (0.08 * t if name.endswith((".q", ".k")) else 0.02 * t)
+        tensors[name] = t.to(torch.bfloat16)
+    w = {k: v.double() for k, v in tensors.items()}
+
+    def plain_model(tokens):
+        T = len(tokens)
+        pos = torch.arange(T)
+        inv = plain.plain_inv_freq(hd, 10000.0)
+        x = w["emb"][torch.tensor(tokens)]
+        for i in range(2):
+            p = f"l{i}."
+            h = plain.rmsnorm(x, 1.0 + w[p + "n1"], eps)
+            q = plain.rope(plain.linear(h, w[p + "q"]).reshape(T, heads, hd), pos, inv)
+            k = plain.rope(plain.linear(h, w[p + "k"]).reshape(T, kvh, hd), pos, inv)
+            v = plain.linear(h, w[p + "v"]).reshape(T, kvh, hd)
+            x = x + plain.linear(plain.attention(q, k, v).reshape(T, heads * hd), w[p + "o"])
+            h = plain.rmsnorm(x, 1.0 + w[p + "n2"], eps)
+            x = x + plain.linear(plain.swiglu(plain.linear(h, w[p + "gate"]), plain.linear(h, w[p + "up"])), w[p + "down"])
+        return plain.linear(plain.rmsnorm(x, 1.0 + w["fn"], eps), w["head"])
+
+    register_part("norm", "toy_one_plus_rms", OnePlusRMS)
+    register_architecture("ToyNormLM", lambda raw: ToyCfg("ToyNormLM"), spec)
+    try:
+        toks = random_tokens(vocab, 40, 9)
+        ref = plain_model(toks)
+        counts = CallCounter(monkeypatch, "gemm_bf16_norm")
+        r = ModelRunner(config=ToyCfg("ToyNormLM"), tensors=tensors, dtype="bfloat16", max_tokens=128, max_requests=2, use_graphs=False)
+        outs = [r.step([StepEntry("a", toks[:30], list(range(30)))])]
+        for i in range(30, 40):
+            outs.append(r.step([StepEntry("a", [toks[i]], [0])]))
+        assert counts["gemm_bf16_norm"] > 0, "the folding products were meant to serve the toy norm"
+        assert_close_logits(torch.cat(outs), ref, "bfloat16", "toy folding norm", sharp=True)
+    finally:
+        unregister_architecture("ToyNormLM")
+        unregister_part("norm", "toy_one_plus_rms")
