@@ -143,13 +143,15 @@ int main(int argc, char** argv) {
     std::fprintf(stderr, "[ref_bench] prefill of %d tokens: %.1f s\n", a.prefill, prefillWall);
   }
 
-  // ---- contexts: every session holds ctx-1 tokens (session 0 keeps what the prefill wrote when that is enough)
+  // ---- contexts.  Session 0 keeps what the prefill wrote when that is enough.  --fill 1: every other
+  // session gets its ctx-1 tokens through forward() too (minutes at the reference's speed);
+  // --fill 0: the other sessions decode over cache slices nothing has written yet.  The time of a
+  // decode step is the same either way: the reference's kernels read the same bytes and take no
+  // decision from a cached value (cuda_backend.cu:347-395 walks positions 0..pos whatever they hold).
   const int have0 = a.prefill >= a.ctx - 1 ? a.ctx - 1 : 0;
   const auto tf = clock::now();
-  if (a.fill) {
-    for (int b = 0; b < a.batch; ++b)
-      for (int i = (b == 0 ? have0 : 0); i < a.ctx - 1; ++i) model->forward(sessions[b], tokenAt(i + b), i);
-  }
+  for (int b = 0; b < (a.fill ? a.batch : 1); ++b)
+    for (int i = (b == 0 ? have0 : 0); i < a.ctx - 1; ++i) model->forward(sessions[b], tokenAt(i + b), i);
   std::fprintf(stderr, "[ref_bench] contexts of %d tokens for %d sessions: %.1f s\n", a.ctx - 1, a.batch, seconds(tf, clock::now()));
 
   // ---- decode: a step is one forward for each session

@@ -5,7 +5,7 @@ word; flags are `--flag value`, core/src/main.cpp:269-303):
                   [--top-p P] [--seed S] [--dtype bfloat16|float32]
   qorvix bench <model_dir> [--prompt N] [--gen N] [--warmup N] [--runs N] [--batch B] [--json]
   qorvix model-info <model_dir>
-  qorvix gpu-check <model_dir> [--tokens ...]      engine float32 and bfloat16 against each other
+  qorvix gpu-check <model_dir> [--tokens ...]      engine float32 and bfloat16 against the plain C++ CPU model
   qorvix random-model <out_dir> --config <config.json> [--seed S] [--dtype bfloat16|float32]
 
 `generate` keeps the reference's option names and defaults (--max 128, --temp 0.8, --top-k 40,
@@ -100,29 +100,42 @@ def cmd_model_info(args) -> int:
 
 
 def cmd_gpu_check(args) -> int:
-    """Like the reference's gpu-check (core/src/main.cpp:3629-3680): the same prompt through two
-    paths (here float32 and bfloat16 kernels), max abs / rel error and argmax agreement."""
-    import torch
+    """The reference's gpu-check (core/src/main.cpp:3629-3680): the same prompt through the GPU engine and
+    through a CPU model, logits compared position by position; PASS when the argmax agrees everywhere
+    and the relative error is under 5e-2 (core/src/main.cpp:3660-3678).  The CPU side here is the plain
+    C++ decoder of csrc/ref/, which shares nothing with the engine; both engine paths are checked,
+    float32 by the reference's rule, bfloat16 with the argmax demanded only where the CPU model's two
+    best logits lie further apart than twice the largest error."""
+    import numpy as np
     from ..config import load_config
+    from ..csrc import ops
+    from ..csrc.ref import RefModel
     from ..engine import ModelRunner, StepEntry
     if len(args) < 2:
         print("usage: qorvix gpu-check <model_dir> [--tokens 1,2,3 | --random-prompt N]", file=sys.stderr)
         return 1
     cfg = load_config(args[1])
     prompt = _prompt_from(args, cfg.vocab_size) or _prompt_from(args + ["--random-prompt", "32"], cfg.vocab_size)
-    outs = {}
+    want = RefModel(args[1]).logits(prompt).astype(np.float64)
+    scale = max(float(np.abs(want).max()), 1e-30)
+    top2 = np.sort(want, axis=-1)[:, -2:]
+    gap = top2[:, 1] - top2[:, 0]
+    all_ok = True
     for dt in ("float32", "bfloat16"):
         r = ModelRunner(args[1], dtype=dt, max_tokens=len(prompt) + 64, max_requests=1)
-        outs[dt] = r.step([StepEntry(0, prompt, list(range(len(prompt))))], end=[0]).double().cpu()
+        got = r.step([StepEntry(0, prompt, list(range(len(prompt))))], end=[0]).double().cpu().numpy()
+        ops.check_kernel_errors()
         del r
-    a, b = outs["float32"], outs["bfloat16"]
-    max_abs = float((a - b).abs().max())
-    rel = max_abs / max(float(a.abs().max()), 1e-30)
-    agree = int((a.argmax(-1) == b.argmax(-1)).sum())
-    print(f"gpu-check: {len(prompt)} positions | max abs err {max_abs:.3e} | rel err {rel:.3e} | argmax equal {agree}/{len(prompt)}")
-    ok = rel < 5e-2
-    print("PASS" if ok else "FAIL")
-    return 0 if ok else 1
+        max_abs = float(np.abs(got - want).max())
+        rel = max_abs / scale
+        same = got.argmax(-1) == want.argmax(-1)
+        must = np.ones(len(prompt), dtype=bool) if dt == "float32" else gap > 2 * max_abs
+        ok = rel < 5e-2 and bool(same[must].all())
+        all_ok = all_ok and ok
+        print(f"gpu-check {dt}: {len(prompt)} positions | max abs err {max_abs:.3e} | rel err {rel:.3e} | "
+              f"argmax equal {int(same.sum())}/{len(prompt)} ({int(must.sum())} decisive) | {'ok' if ok else 'MISMATCH'}")
+    print("PASS" if all_ok else "FAIL")
+    return 0 if all_ok else 1
 
 
 def cmd_random_model(args) -> int:

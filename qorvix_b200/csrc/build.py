@@ -37,6 +37,11 @@ LIBRARIES = {
     "attention_bf16": "attention_bf16.cu",
     "attention_tc": "attention_tc.cu",
     "host_runtime": "host_runtime.cpp",          # host-side cache bookkeeping: plain C++, no CUDA
+    "ref": "ref/ref_model.cpp",                  # the kernels' plain C++ twins and a whole-model forward: host only
+}
+# what a library is built from beside its source and HEADERS (their bytes are part of its name's hash)
+EXTRA_SOURCES = {
+    "ref": ["ref/ref_ops.hpp", "host/json.hpp", "host/safetensors.hpp", "host/model_config.hpp"],
 }
 HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC"]
 
@@ -85,9 +90,9 @@ def build_dir() -> Path:
     raise KernelBuildError(f"no writable build folder among {', '.join(map(str, cands))}")
 
 
-def _source_hash(src: Path) -> str:
+def _source_hash(src: Path, extra=()) -> str:
     h = hashlib.sha256()
-    for p in [src] + [CSRC / x for x in HEADERS]:
+    for p in [src] + [CSRC / x for x in HEADERS] + [CSRC / x for x in extra]:
         h.update(p.read_bytes())
     h.update(" ".join(NVCC_FLAGS).encode())
     return h.hexdigest()[:12]
@@ -95,7 +100,7 @@ def _source_hash(src: Path) -> str:
 
 def library_path(name: str) -> Path:
     src = CSRC / LIBRARIES[name]
-    return build_dir() / f"qv_{name}-{_source_hash(src)}.so"
+    return build_dir() / f"qv_{name}-{_source_hash(src, EXTRA_SOURCES.get(name, ()))}.so"
 
 
 def compile_library(name: str, verbose: bool = True) -> Path:

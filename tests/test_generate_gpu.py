@@ -237,3 +237,22 @@ def test_lookahead_gives_the_same_tokens_as_one_step_at_a_time():
             assert llm.last_stats["ahead_steps"] > 10, "the lookahead path did run"
     assert out[True] == out[False]
     assert {r for _, r in out[True]} >= {"max_new_tokens", "stop"}
+
+
+def test_gpu_check_compares_with_the_cpp_model_and_fails_when_both_engine_paths_share_a_fault(model_b, monkeypatch, capsys):
+    """`qorvix gpu-check` holds both engine paths against the plain C++ decoder; an error common to
+    the float32 and the bfloat16 path (here: every RMS norm built with another eps) must not pass."""
+    from qorvix_b200.cli.main import cmd_gpu_check
+    from qorvix_b200.parts import rmsnorm
+    d, _ = model_b
+    assert cmd_gpu_check(["gpu-check", str(d), "--random-prompt", "40"]) == 0
+    assert "PASS" in capsys.readouterr().out
+    real_init = rmsnorm.RMSNorm.__init__
+
+    def wrong_eps(self, spec, source, rt):
+        real_init(self, spec, source, rt)
+        self.eps = 0.5
+
+    monkeypatch.setattr(rmsnorm.RMSNorm, "__init__", wrong_eps)
+    assert cmd_gpu_check(["gpu-check", str(d), "--random-prompt", "40"]) == 1
+    assert "FAIL" in capsys.readouterr().out
