@@ -32,6 +32,8 @@ def lib():
             "qvh_table_copy": (c_int, [c_void_p, c_longlong, c_int, POINTER(c_int), c_int]),
             "qvh_youngest": (c_int, [c_void_p, c_int, POINTER(c_longlong)]),
             "qvh_check": (c_int, [c_void_p, c_char_p, c_int]),
+            "qvh_decode_variant": (c_int, [c_int, c_int]), "qvh_decode_splits": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int]),
+            "qvh_folded_norm_enabled": (c_int, [c_int]), "qvh_fused_rope_enabled": (c_int, [c_int]),
             "qvh_fill_decode": (c_int, [c_void_p, c_int, POINTER(c_longlong), POINTER(c_int), c_int, c_int, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p]),
         }

@@ -38,9 +38,19 @@ LIBRARIES = {
     "attention_tc": "attention_tc.cu",
     "host_runtime": "host_runtime.cpp",          # host-side cache bookkeeping: plain C++, no CUDA
     "ref": "ref/ref_model.cpp",                  # the kernels' plain C++ twins and a whole-model forward: host only
+    "executor": "host/executor_api.cpp",         # the native step executor behind a C interface (host code, CUDA runtime calls)
 }
+# host code that calls the CUDA runtime: compiled and linked by nvcc (no device code in it)
+CUDA_HOST_LIBRARIES = {"executor"}
+# the native command line: an executable, built from these sources by nvcc
+CLI_SOURCES = ["cli/qorvix_main.cpp", "host_runtime.cpp", "ref/ref_model.cpp"]
+CLI_HEADERS = ["host/json.hpp", "host/safetensors.hpp", "host/model_config.hpp", "host/kernels.hpp", "host/dispatch.hpp",
+               "host/executor.hpp", "host/engine.hpp", "host/scheduler.hpp", "ref/ref_ops.hpp"]
+KERNEL_LIBRARIES = ["elementwise", "gemm_simt", "gemm_bf16", "attention_generic", "attention_bf16", "attention_tc", "sampling"]
 # what a library is built from beside its source and HEADERS (their bytes are part of its name's hash)
 EXTRA_SOURCES = {
+    "host_runtime": ["host/dispatch.hpp"],
+    "executor": ["host/executor.hpp", "host/kernels.hpp", "host/dispatch.hpp"],
     "ref": ["ref/ref_ops.hpp", "host/json.hpp", "host/safetensors.hpp", "host/model_config.hpp"],
 }
 HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC"]
@@ -114,7 +124,12 @@ def compile_library(name: str, verbose: bool = True) -> Path:
     if out.is_file():
         return out
     tmp = out.with_name(out.name + f".tmp{os.getpid()}")
-    if src.suffix == ".cpp":
+    if name in CUDA_HOST_LIBRARIES:
+        cmd = [find_nvcc(), "-O2", "-std=c++17", "--shared", "-Xcompiler", "-fPIC", "-Wno-deprecated-gpu-targets", "-I", str(CSRC),
+               "-o", str(tmp), str(src), "-ldl"]
+        if verbose:
+            _say(f"compiling {src.name} ...")
+    elif src.suffix == ".cpp":
         cxx = find_host_compiler()
         flags = ["--shared", "-Xcompiler", "-fPIC", "-O2", "-std=c++17"] if os.path.basename(cxx).startswith("nvcc") else HOST_FLAGS
         cmd = [cxx, *flags, "-I", str(CSRC), "-o", str(tmp), str(src)]
@@ -168,5 +183,51 @@ def load_library(name: str) -> ctypes.CDLL:
         return lib
 
 
+def write_manifest() -> Path:
+    """Builds the kernel libraries if need be and writes `kernels.manifest` beside them: the lines
+    name=path that the native executor and the native command line load their kernels from."""
+    lines = [f"{n}={compile_library(n)}" for n in KERNEL_LIBRARIES]
+    out = build_dir() / "kernels.manifest"
+    text = "\n".join(lines) + "\n"
+    if not out.is_file() or out.read_text() != text:
+        tmp = out.with_name(out.name + f".tmp{os.getpid()}")
+        tmp.write_text(text)
+        os.replace(tmp, out)
+    return out
+
+
+def build_cli(verbose: bool = True) -> Path:
+    """The native command line (csrc/cli/qorvix_main.cpp with the engine, scheduler, cache bookkeeping
+    and plain C++ decoder it is made of) as an executable beside the libraries; returns its path."""
+    h = hashlib.sha256()
+    for rel in CLI_SOURCES + CLI_HEADERS:
+        h.update((CSRC / rel).read_bytes())
+    out = build_dir() / f"qorvix_native-{h.hexdigest()[:12]}"
+    write_manifest()
+    if out.is_file():
+        return out
+    tmp = out.with_name(out.name + f".tmp{os.getpid()}")
+    cmd = [find_nvcc(), "-O2", "-std=c++17", "-Wno-deprecated-gpu-targets", "-I", str(CSRC), "-o", str(tmp),
+           *[str(CSRC / x) for x in CLI_SOURCES], "-ldl"]
+    if verbose:
+        _say("compiling the native command line ...")
+    t0 = time.time()
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        raise KernelBuildError(f"the compiler failed on the native command line:\n{proc.stdout}")
+    os.replace(tmp, out)
+    for old in out.parent.glob("qorvix_native-*"):
+        if old != out and ".tmp" not in old.name:
+            try:
+                old.unlink()
+            except OSError:
+                pass
+    if verbose:
+        _say(f"  built {out.name} in {time.time() - t0:.1f} s")
+    return out
+
+
 def build_all(verbose: bool = True) -> list:
-    return [compile_library(n, verbose) for n in LIBRARIES if (CSRC / LIBRARIES[n]).is_file()]
+    built = [compile_library(n, verbose) for n in LIBRARIES if (CSRC / LIBRARIES[n]).is_file()]
+    built.append(build_cli(verbose))
+    return built

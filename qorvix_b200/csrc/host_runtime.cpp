@@ -15,6 +15,8 @@
 #include <unordered_map>
 #include <vector>
 
+#include "host/dispatch.hpp"
+
 namespace {
 
 struct Pool {
@@ -356,5 +358,13 @@ int qvh_fill_decode(void* h, int n, const long long* rids, const int* tokens, in
   }
   return 0;
 }
+
+// ------------------------------------------------------------------ kernel choice (host/dispatch.hpp)
+int qvh_decode_variant(int T, int Hkv) { return qv::decode_variant(T, Hkv); }
+int qvh_decode_splits(int T, int Hkv, int max_ctx, int known, int variant, int sms) {
+  return qv::decode_splits(T, Hkv, max_ctx, known != 0, variant, sms);
+}
+int qvh_folded_norm_enabled(int tokens) { return qv::folded_norm_enabled(tokens) ? 1 : 0; }
+int qvh_fused_rope_enabled(int tokens) { return qv::fused_rope_enabled(tokens) ? 1 : 0; }
 
 }  // extern "C"

@@ -310,22 +310,23 @@ def new_norm_stats(features: int, device) -> torch.Tensor:
     return torch.empty((-(-features // 128), 64), device=device, dtype=torch.float32)
 
 
+def _rules():
+    """The kernel-choice rules live in C++ (csrc/host/dispatch.hpp), one statement for this module and
+    for the native executor; they are reached through the host runtime library."""
+    from ..cache import native
+    return native.lib()
+
+
 def folded_norm_enabled(tokens: int) -> bool:
     """Whether the RMS norms of a step of `tokens` tokens ride in the epilogues of the products around
-    them: up to 16 tokens (one chunk of the epilogue, whose stream values are fetched while the main loop
-    runs; at 64 tokens the longer epilogues cost more than the two launches they save: 11.0k against
-    11.9k tokens/s at batch 64), unless QORVIX_FOLDED_NORM=0 (never) or =64 (up to 64 tokens; for
-    comparison)."""
-    import os
-    mode = os.environ.get("QORVIX_FOLDED_NORM", "1")
-    return mode != "0" and tokens <= (64 if mode == "64" else 16)
+    them: up to 16 tokens, unless QORVIX_FOLDED_NORM=0 (never) or =64 (up to 64 tokens; for comparison)."""
+    return bool(_rules().qvh_folded_norm_enabled(int(tokens)))
 
 
 def fused_rope_enabled(tokens: int) -> bool:
     """Whether the QKV projection of a step of `tokens` tokens takes the rotation and the cache write
     into its epilogue: above 64 tokens, unless QORVIX_FUSED_ROPE=0 (for comparison)."""
-    import os
-    return tokens > 64 and os.environ.get("QORVIX_FUSED_ROPE", "1") != "0"
+    return bool(_rules().qvh_fused_rope_enabled(int(tokens)))
 
 
 def gemm_qkv_rope(qkv, x, packed, cache_layer, cos_sin, tok_pos, tok_seg, block_table, H, Hkv, hd, page) -> bool:
@@ -482,31 +483,14 @@ def decode_variant(T: int, Hkv: int) -> int:
     ranges), 1 through per-thread loads (less set-up; better when there are few pairs)."""
     if _decode_variant_forced is not None:
         return _decode_variant_forced
-    return 0 if T * Hkv >= 32 else 1
+    return _rules().qvh_decode_variant(int(T), int(Hkv))
 
 
 def decode_splits(T: int, Hkv: int, max_ctx: int, known: bool = True) -> int:
-    """How many slices of the keys each (token, kv head) is cut into: about three CTAs per SM for the
-    per-thread-load kernel; for the bulk-copy kernel (two CTAs per SM, each with 64 KB of keys and
-    values in flight, at least 256 keys a slice) the count whose waves of CTAs take the least time
-    when max_ctx is the step's real longest context (`known`), else the count that fills one wave.
-    A function of the step's shape only (a captured step keeps it)."""
-    pairs = max(1, T * Hkv)
-    if decode_variant(T, Hkv) == 0 and not known:
-        # a captured step is replayed at contexts from a few keys up to max_ctx: one wave of CTAs, no
-        # more (more slices than that pay only at long contexts and cost up to a third at short ones)
-        return max(1, min(16, (2 * sm_count()) // pairs, max_ctx // 256))
-    if decode_variant(T, Hkv) == 0:
-        # two CTAs per SM run at once; a CTA's time is its slice of the keys plus a fixed part worth about
-        # 256 keys.  The count that needs the least time over all waves, the smaller one on a tie.
-        best, best_cost = 1, None
-        resident = 2 * sm_count()
-        for s in range(1, max(1, min(16, max_ctx // 256)) + 1):
-            cost = -(-pairs * s // resident) * (-(-max_ctx // s) + 256)
-            if best_cost is None or cost < best_cost:
-                best, best_cost = s, cost
-        return best
-    return max(1, min(16, -(-3 * sm_count() // pairs), -(-max_ctx // 64)))
+    """How many slices of the keys each (token, kv head) is cut into: the count whose waves of CTAs
+    take the least time when max_ctx is the step's real longest context (`known`), else the count that
+    fills one wave.  A function of the step's shape only (a captured step keeps it)."""
+    return _rules().qvh_decode_splits(int(T), int(Hkv), int(max_ctx), 1 if known else 0, decode_variant(T, Hkv), sm_count())
 
 
 def attention_decode_bf16(out, q, cache_layer, tok_pos, tok_seg, block_table, H, Hkv, hd, page, window, scale,

@@ -25,6 +25,7 @@ class TextModel:
         self.final_norm = build_part("norm", spec.final_norm, source, rt)
         self.lm_head = Linear(source.get(spec.lm_head)) if spec.lm_head is not None else Linear(self.embedding)
         self.order: List[int] = list(spec.order)
+        self._native = None            # the native executor of this model over a cache, made on first use (False: not applicable)
 
     def cache_needs(self):
         """What each RUN of the execution order wants of the cache manager: (cache spec or None, index
@@ -49,6 +50,12 @@ class TextModel:
     def forward(self, ctx, cache) -> Optional[torch.Tensor]:
         """Runs the tokens of `ctx`; returns float32 logits [wanted rows, vocab] (None if none wanted)."""
         T = ctx.num_tokens
+        if self._native is None:
+            from ..engine.native_executor import NativeExecutor
+            self._native = NativeExecutor.try_build(self, cache) or False
+        if self._native:
+            # every block is one the native executor knows: the whole step in one call
+            return self._native.forward(ctx)
         residual = torch.empty((T, self.spec.hidden_size), device=self.rt.device, dtype=torch.float32)
         ops.embed(residual, self.embedding, ctx.token_ids)
         pending = None

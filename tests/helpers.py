@@ -110,12 +110,17 @@ def assert_close_logits(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: 
 
 
 class CallCounter:
-    """Counts the successful calls of functions of qorvix_b200.csrc.ops, so that a test can prove
-    which kernels served it:  with CallCounter(monkeypatch, "attention_prefill_tc") as n: ...; n["attention_prefill_tc"]."""
+    """Counts how often kernels of qorvix_b200.csrc.ops served, so that a test can prove its route:
+    the successful calls of the Python functions of those names, plus what the native step executor
+    (which launches the same kernels itself) counted since this object was made.
+        counts = CallCounter(monkeypatch, "attention_prefill_tc"); ...; counts["attention_prefill_tc"]"""
 
     def __init__(self, monkeypatch, *names):
         from qorvix_b200.csrc import ops
-        self.counts = {n: 0 for n in names}
+        from qorvix_b200.engine import native_executor
+        self._native = native_executor
+        self._calls = {n: 0 for n in names}
+        self._base = native_executor.route_counts()
         for n in names:
             monkeypatch.setattr(ops, n, self._wrap(n, getattr(ops, n)))
 
@@ -123,29 +128,14 @@ class CallCounter:
         def counted(*a, **kw):
             res = fn(*a, **kw)
             if res is None or res:
-                self.counts[name] += 1
+                self._calls[name] += 1
             return res
         return counted
 
+    @property
+    def counts(self):
+        now = self._native.route_counts()
+        return {n: c + now.get(n, 0) - self._base.get(n, 0) for n, c in self._calls.items()}
+
     def __getitem__(self, name):
         return self.counts[name]
-
-
-def assert_greedy_follows_plain(pm, prompt, got, what: str = "", gap: float = 0.05, at_least: int = 1) -> int:
-    """`got` must be the plain implementation's greedy tokens, token for token, up to the first place
-    where the plain top-2 gap is under `gap` of max |logit| (a near tie that rounding may decide
-    either way; nothing after it is compared).  Returns how many tokens were compared and raises when
-    fewer than `at_least` were."""
-    seq = list(prompt)
-    compared = 0
-    for i, tok in enumerate(got):
-        full = pm.logits(seq)[-1]
-        top = torch.topk(full, 2)
-        if float(top.values[0] - top.values[1]) < gap * float(full.abs().max()):
-            break
-        want = int(top.indices[0])
-        assert int(tok) == want, f"{what}: generated token {i} is {tok}, the plain implementation's is {want} (so far {list(got[:i])})"
-        seq.append(int(tok))
-        compared += 1
-    assert compared >= at_least, f"{what}: only {compared} tokens could be compared before a near tie; pick another prompt"
-    return compared
