@@ -139,3 +139,23 @@ class CallCounter:
 
     def __getitem__(self, name):
         return self.counts[name]
+
+
+def assert_greedy_follows_plain(pm, prompt, got, what: str = "", gap: float = 0.05, at_least: int = 1) -> int:
+    """`got` must be the plain implementation's greedy tokens, token for token, up to the first place
+    where the plain top-2 gap is under `gap` of max |logit| (a near tie that rounding may decide
+    either way; nothing after it is compared).  Returns how many tokens were compared and raises when
+    fewer than `at_least` were."""
+    seq = list(prompt)
+    compared = 0
+    for i, tok in enumerate(got):
+        full = pm.logits(seq)[-1]
+        top = torch.topk(full, 2)
+        if float(top.values[0] - top.values[1]) < gap * float(full.abs().max()):
+            break
+        want = int(top.indices[0])
+        assert int(tok) == want, f"{what}: generated token {i} is {tok}, the plain implementation's is {want} (so far {list(got[:i])})"
+        seq.append(int(tok))
+        compared += 1
+    assert compared >= at_least, f"{what}: only {compared} tokens could be compared before a near tie; pick another prompt"
+    return compared
