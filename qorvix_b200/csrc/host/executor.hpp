@@ -131,8 +131,10 @@ class Executor {
     enum { NONE, DELTA, PRENORMED } pending = NONE;
     int pre = 0;                                   // which of scaled[]/stats[] holds the prepared input
     const int L = (int)m.layers.size();
+    const size_t layer_scratch = ws.used;          // what a layer takes beyond this (slices' partial results, an unfused gate/up) is the next layer's again
     for (int li = 0; li < L; ++li) {
       const LayerW& w = m.layers[(size_t)li];
+      ws.used = layer_scratch;
       // ---- attention
       bool have_qkv = false;
       if (pending == PRENORMED) {
@@ -191,6 +193,7 @@ class Executor {
       if (to_stream) pending = PRENORMED;
       else { gemm(part_out, d, m.dt, act, m.f, w.down, T, st); pending = DELTA; }
     }
+    ws.used = layer_scratch;
     if (io.R <= 0) return;
     // final norm on the wanted rows only, then the output head in float32
     void* h = ws.take((size_t)io.R * d * e);
