@@ -26,15 +26,24 @@ def _run(*args, stdin=None, timeout=900):
 
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("E", "float32"), ("D", "float32")])
 def test_native_generate_prints_the_plain_implementations_greedy_tokens(name, dtype):
+    """--temp 0 is greedy after the penalties, as in the reference (runtime/src/sampler.cpp:43-50 applies
+    the penalties, whose repetition penalty defaults to 1.1, before it looks at the temperature): the
+    expected tokens are the plain implementation's logits through the plain penalties and argmax."""
+    import plain_llama as plain
     cfg = TINY[name]
     d = make_model_dir(cfg, seed=4, sharpen=6.0)
     pm = PlainModel(d)
     prompt = random_tokens(cfg.vocab_size, 70, 8)
+    want, seq = [], list(prompt)
+    for _ in range(12):
+        row = plain.apply_penalties(pm.logits(seq)[-1].numpy(), seq, repetition_penalty=1.1, penalty_last_n=64)
+        want.append(int(np.argmax(row)))
+        seq.append(want[-1])
     p = _run("generate", str(d), "--tokens", ",".join(map(str, prompt)), "--max", "12", "--temp", "0", "--dtype", dtype)
     assert p.returncode == 0, p.stderr[-2000:]
     lines = p.stdout.strip().split("\n")
     assert [int(t) for t in lines[0].split()] == prompt
-    assert [int(t) for t in lines[1].split()] == pm.greedy(prompt, 12)
+    assert [int(t) for t in lines[1].split()] == want
     assert "70 prompt tokens, 12 generated" in p.stdout
     # the Python command line prints the same tokens
     q = subprocess.run([sys.executable, str(ROOT / "bin" / "qorvix"), "generate", str(d), "--tokens", ",".join(map(str, prompt)), "--max", "12",
