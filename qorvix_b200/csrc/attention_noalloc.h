@@ -27,6 +27,11 @@
 // different streams, or from different threads) would overwrite each other's partial results:
 // keep calls on one stream, or order them with events.
 //
+// One device per process: the workspace's address is kept per device, but the kernels' launch
+// configuration, the word their bounded waits report into and the choice between the two decode
+// kernels (qv_attn_set_error_word, qv_attn_set_decode_variant, shared with qv_attn_decode_bf16) are
+// kept once per process.  A process that drives several GPUs through this library is not served.
+//
 // The function allocates nothing: no cudaMalloc, cudaFree or allocating library routine.
 #pragma once
 

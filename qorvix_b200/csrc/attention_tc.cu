@@ -9,13 +9,14 @@
 //   warp 0        TMA: Q once, then K and V tiles into a ring of three stages, every lane issuing
 //                 one of a stage's loads (a page may hold no more than 16 keys)
 //   warp 1        MMA: S[j] = Q K_j^T into one of two S buffers in tensor memory (so that S[j+1] is
-//                 computed while the softmax of tile j runs), then O += P_j V_j with P read from
-//                 tensor memory and V as an MN-major operand from shared memory
+//                 computed while the softmax of tile j runs), then O += P_j V_j with P read from one
+//                 of two P buffers in tensor memory and V as an MN-major operand from shared memory
 //   warps 2..     softmax, WGS warpgroups of four warps.  A query row is shared by WGS threads (one
 //                 per warpgroup, same lane of tensor memory), each owning 128 / WGS of the tile's keys:
 //                 it reads its part of the row of S once, agrees with its partners on the row's
-//                 reference maximum through shared memory, writes its exponentials as bfloat16 into
-//                 P's columns in tensor memory and keeps its part of the row sum.  With two
+//                 reference maximum through shared memory, computes its exponentials (before it waits
+//                 for anything the tensor pipe still owes), writes them as bfloat16 into P's columns
+//                 in tensor memory and keeps its part of the row sum.  With two
 //                 warpgroups every scheduler of the SM has two softmax warps to issue from and each
 //                 thread half the exponentials, which is what bounds the one-warpgroup form.
 // The output row lives in tensor memory and the P.V products accumulate into it; a row's reference
@@ -68,12 +69,12 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
   uint64_t* q_full = bars;                           // 1
   uint64_t* s_full = bars + 1;                       // 2
   uint64_t* s_empty = bars + 3;                      // 2
-  uint64_t* p_full = bars + 5;
-  uint64_t* p_empty = bars + 6;
-  uint64_t* pv_full = bars + 7;
-  uint64_t* kv_full = bars + 8;                      // KV_ST
-  uint64_t* kv_empty = bars + 8 + KV_ST;             // KV_ST
-  uint32_t* tmem_slot = (uint32_t*)(bars + 8 + 2 * KV_ST);
+  uint64_t* p_full = bars + 5;                       // 2
+  uint64_t* p_empty = bars + 7;                      // 2
+  uint64_t* pv_full = bars + 9;
+  uint64_t* kv_full = bars + 10;                     // KV_ST
+  uint64_t* kv_empty = bars + 10 + KV_ST;            // KV_ST
+  uint32_t* tmem_slot = (uint32_t*)(bars + 10 + 2 * KV_ST);
   // What the threads of a row tell each other, 256 bytes for each quarter of the rows (the warps of
   // a quarter meet at a barrier of their own and run ahead of or behind the other quarters): the
   // tile's maxima (bfloat16, rounded up, two tiles in flight: [2][WGS][32 rows]) and at the end the
@@ -103,8 +104,11 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < KV_ST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128 * WGS); }
-    mbar_init(p_full, 128 * WGS); mbar_init(p_empty, 1); mbar_init(pv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128 * WGS);
+      mbar_init(&p_full[i], 128 * WGS); mbar_init(&p_empty[i], 1);
+    }
+    mbar_init(pv_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -117,7 +121,7 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;                  // columns 0..255: S, double-buffered
   const uint32_t tmem_pv = tmem + 256;               // HD columns: the output rows
-  const uint32_t tmem_p = tmem + 384;                // 64 columns: a row of P, two keys per column
+  const uint32_t tmem_p = tmem + 384;                // 2 x 64 columns: a row of P, two keys per column, for tiles j and j + 1
 
   if (warp == 0) {
     // The whole warp requests: a tile of keys and values is 8 blocks of 16 keys (a page may hold no
@@ -172,17 +176,18 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);
         if (!ok) break;
         const int s = j % KV_ST;                     // the stage of this tile's keys and values
-        if (!mbar_wait(p_full, j & 1, a.err, 15)) break;
+        const int pb = j & 1;                        // which P buffer this tile's probabilities are in
+        if (!mbar_wait(&p_full[pb], (j >> 1) & 1, a.err, 15)) break;
         tc_fence_after();
         // P [128 rows][128 keys] in tensor memory (64 columns of two keys); V [128 keys][HD] MN-major
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk) {
           const uint32_t v_addr = smem_u32(sV + s * K_BYTES + (kk * 16) * 128);
-          umma_f16_ts(tmem_pv, tmem_p + (uint32_t)(kk * 8), umma_desc_mn(v_addr, HALF_BYTES), idesc_pv, (kk > 0 || j > 0) ? 1u : 0u);
+          umma_f16_ts(tmem_pv, tmem_p + (uint32_t)(pb * 64 + kk * 8), umma_desc_mn(v_addr, HALF_BYTES), idesc_pv, (kk > 0 || j > 0) ? 1u : 0u);
         }
         umma_commit(pv_full);
         umma_commit(&kv_empty[s]);
-        umma_commit(p_empty);
+        umma_commit(&p_empty[pb]);
       }
     }
   } else {
@@ -245,36 +250,21 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
         corr = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - mx);
         m_ref = mx;
       }
-      // P's columns are free, and the output row is at rest, once the previous tile's P.V is done
-      ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (j & 1) ^ 1, a.err, 18));
-      if (!ok) continue;
-      tc_fence_after();
-      if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-        // some row of this warp moves its reference: scale this thread's columns of the warp's rows
-        // of O (by 1 where nothing moved); the partner warps decide alike, from the same values
-#pragma unroll
-        for (int c = 0; c < OPT; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(tmem_pv + lane_base + (uint32_t)(wg * OPT + c), v);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-          tmem_st32(tmem_pv + lane_base + (uint32_t)(wg * OPT + c), v);
-        }
-      }
+      // the exponentials first, into registers: nothing here waits for the tensor pipe, so this runs
+      // while the product of the tile before is still under way
       l *= corr;
       float sum = 0.f;
       const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+      uint32_t w[KPT / 2];
 #pragma unroll
       for (int c = 0; c < KPT; c += 64) {
-        uint32_t w[32];
         if (all_visible) {                             // most tiles: no mask, two instructions per score
 #pragma unroll
           for (int i = 0; i < 64; i += 2) {
             const float e0 = fast_exp2(fmaf(__uint_as_float(sv[c + i]), a.scale_log2, neg_m));
             const float e1 = fast_exp2(fmaf(__uint_as_float(sv[c + i + 1]), a.scale_log2, neg_m));
             sum += e0 + e1;
-            w[i >> 1] = pack2_bf16(e0, e1);
+            w[(c + i) >> 1] = pack2_bf16(e0, e1);
           }
         } else {
 #pragma unroll
@@ -286,15 +276,40 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
               e[x] = (key >= lo && key <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c + i + x]), a.scale_log2, neg_m)) : 0.f;
             }
             sum += e[0] + e[1];
-            w[i >> 1] = pack2_bf16(e[0], e[1]);
+            w[(c + i) >> 1] = pack2_bf16(e[0], e[1]);
           }
         }
-        tmem_st32(tmem_p + lane_base + (uint32_t)((wg * KPT + c) >> 1), w);
       }
+      l += sum;
+      // this tile's P buffer is free once the product of two tiles ago has read it
+      const int pb = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&p_empty[pb], ((j >> 1) & 1) ^ 1, a.err, 18));
+      if (!ok) continue;
+      if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+        // Some row of this warp moves its reference: scale this thread's columns of the warp's rows of
+        // O (by 1 where nothing moved); the partner warps decide alike, from the same values.  O is at
+        // rest once the product of the tile before is done, and stays so until every thread has handed
+        // in this tile's P.  (That product's barrier is waited on only here: it cannot run ahead of
+        // the tile this thread is in, because the next product needs this thread's P.)
+        ok = __all_sync(0xffffffffu, mbar_wait(pv_full, (j - 1) & 1, a.err, 19));
+        if (!ok) continue;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < OPT; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_pv + lane_base + (uint32_t)(wg * OPT + c), v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+          tmem_st32(tmem_pv + lane_base + (uint32_t)(wg * OPT + c), v);
+        }
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < KPT; c += 64) tmem_st32(tmem_p + lane_base + (uint32_t)(pb * 64 + ((wg * KPT + c) >> 1)), w + (c >> 1));
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(p_full);
-      l += sum;
+      mbar_arrive(&p_full[pb]);
     }
     if (WGS > 1) {
       // the row's sum: every thread's part, added in the same order by all of them.  The barrier

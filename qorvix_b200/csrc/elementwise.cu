@@ -284,6 +284,33 @@ extern "C" int qv_cast(void* out, const void* in, long long n, int in_dt, int ou
   return qv_launch_status();
 }
 
+// out[r, c] = in[r, c] for matrices whose rows are contiguous but may lie any stride apart, with a
+// change of type on the way if asked: what makes an aligned, dense copy of a column slice of a wider
+// buffer, or of float32 rows for a kernel that takes bfloat16.
+template <typename FROM, typename TO>
+__global__ void cast_rows_kernel(TO* __restrict__ out, long long ld_out, const FROM* __restrict__ in, long long ld_in, int rows, int cols) {
+  const size_t n = (size_t)rows * cols;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / cols, c = i - r * cols;
+    out[r * ld_out + c] = from_f<TO>(to_f(in[r * ld_in + c]));
+  }
+}
+
+extern "C" int qv_cast_rows(void* out, long long ld_out, const void* in, long long ld_in, int rows, int cols, int in_dt, int out_dt, void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const size_t n = (size_t)rows * cols;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  cudaStream_t st = (cudaStream_t)stream;
+#define QV_CAST_ROWS(FROM, TO) cast_rows_kernel<FROM, TO><<<blocks, 256, 0, st>>>((TO*)out, ld_out, (const FROM*)in, ld_in, rows, cols)
+  if (in_dt == QV_DT_F32 && out_dt == QV_DT_BF16) QV_CAST_ROWS(float, bf16);
+  else if (in_dt == QV_DT_BF16 && out_dt == QV_DT_F32) QV_CAST_ROWS(bf16, float);
+  else if (in_dt == QV_DT_F32 && out_dt == QV_DT_F32) QV_CAST_ROWS(float, float);
+  else if (in_dt == QV_DT_BF16 && out_dt == QV_DT_BF16) QV_CAST_ROWS(bf16, bf16);
+  else return QV_ERR_UNSUPPORTED;
+#undef QV_CAST_ROWS
+  return qv_launch_status();
+}
+
 extern "C" const char* qv_error_string(int code) {
   if (code == QV_ERR_UNSUPPORTED) return "size or dtype not supported by this kernel";
   if (code == QV_ERR_TOO_LARGE) return "size exceeds what this kernel can hold on chip";

@@ -91,7 +91,7 @@ class Engine {
     desc_ = model_desc_from_config(parse_json(read_text_file(model_dir + "/config.json")));
     cuda_check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
     cuda_check(cudaMalloc(&err_word_, sizeof(int)), "cudaMalloc");
-    cuda_check(cudaMemset(err_word_, 0, sizeof(int)), "cudaMemset");
+    cuda_check(cudaMemsetAsync(err_word_, 0, sizeof(int), stream_), "cudaMemsetAsync");
     k_.attn_set_error_word(err_word_);
     page_ = opt.page_size;
     const long long pool_tokens = (opt.max_tokens + page_ - 1) / page_ * page_;
@@ -105,6 +105,7 @@ class Engine {
     cache_ = qvh_create(1, &window, num_pages_, page_, opt.max_requests);
     if (!cache_) throw EngineError("the cache manager could not be made");
     exec_.reset(new Executor(&k_, &w_, err_word_));
+    cuda_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
   }
 
   ~Engine() {
@@ -158,9 +159,10 @@ class Engine {
   void check_kernel_errors() {
     int code = 0;
     cuda_check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
-    cuda_check(cudaMemcpy(&code, err_word_, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy");
+    cuda_check(cudaMemcpyAsync(&code, err_word_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "cudaMemcpyAsync");
+    cuda_check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
     if (code) {
-      cudaMemset(err_word_, 0, sizeof(int));
+      cudaMemsetAsync(err_word_, 0, sizeof(int), stream_);
       throw EngineError("a tensor-core kernel gave up waiting on a barrier (code " + std::to_string(code) + ")");
     }
   }
@@ -272,19 +274,26 @@ class Engine {
     if ((u & 0x7F800000u) == 0x7F800000u) return (uint16_t)((u >> 16) | ((u & 0xFFFF) ? 0x40 : 0));
     return (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1)) >> 16);
   }
-  // uploads `t` (rows x cols) in type `want` into dst + row_offset rows
+  // Host to device on the engine's own stream, and done when it returns.  (The stream does not wait
+  // for the default stream, so every copy, fill and kernel of the engine goes through this stream;
+  // a plain cudaMemcpy from pageable memory may return before its last bytes have landed.)
+  void copy_in(void* dst, const void* src, size_t bytes) {
+    cuda_check(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync");
+    cuda_check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+  }
+  // uploads `t` in type `want`
   void upload(void* dst, int want, const StTensor& t) {
     const size_t n = (size_t)t.numel();
     if (want == DT_F32) {
-      if (t.dtype == "F32") { cuda_check(cudaMemcpy(dst, t.data, n * 4, cudaMemcpyHostToDevice), "cudaMemcpy"); return; }
+      if (t.dtype == "F32") { copy_in(dst, t.data, n * 4); return; }
       const std::vector<float> f = to_float(t);
-      cuda_check(cudaMemcpy(dst, f.data(), n * 4, cudaMemcpyHostToDevice), "cudaMemcpy");
+      copy_in(dst, f.data(), n * 4);
     } else {
-      if (t.dtype == "BF16") { cuda_check(cudaMemcpy(dst, t.data, n * 2, cudaMemcpyHostToDevice), "cudaMemcpy"); return; }
+      if (t.dtype == "BF16") { copy_in(dst, t.data, n * 2); return; }
       const std::vector<float> f = to_float(t);
       std::vector<uint16_t> h(n);
       for (size_t i = 0; i < n; ++i) h[i] = to_bf16(f[i]);
-      cuda_check(cudaMemcpy(dst, h.data(), n * 2, cudaMemcpyHostToDevice), "cudaMemcpy");
+      copy_in(dst, h.data(), n * 2);
     }
   }
   int storage_dt(const StTensor& t) const { return dt_ == DT_F32 ? DT_F32 : stored_dt(t); }
@@ -378,8 +387,10 @@ class Engine {
         const size_t es = dt_size(gu.dt), row = (size_t)gu.K * es, grp = 16 * row;
         uint8_t* mixed = (uint8_t*)dev_alloc((size_t)gu.N * row);
         const uint8_t* src = (const uint8_t*)gu.rows;
-        cuda_check(cudaMemcpy2D(mixed, 2 * grp, src, grp, grp, (size_t)c.ffn / 16, cudaMemcpyDeviceToDevice), "cudaMemcpy2D");
-        cuda_check(cudaMemcpy2D(mixed + grp, 2 * grp, src + (size_t)c.ffn * row, grp, grp, (size_t)c.ffn / 16, cudaMemcpyDeviceToDevice), "cudaMemcpy2D");
+        cuda_check(cudaMemcpy2DAsync(mixed, 2 * grp, src, grp, grp, (size_t)c.ffn / 16, cudaMemcpyDeviceToDevice, stream_), "cudaMemcpy2DAsync");
+        cuda_check(cudaMemcpy2DAsync(mixed + grp, 2 * grp, src + (size_t)c.ffn * row, grp, grp, (size_t)c.ffn / 16, cudaMemcpyDeviceToDevice, stream_),
+                   "cudaMemcpy2DAsync");
+        cuda_check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
         dev_free((void*)gu.rows);
         gu.rows = mixed;
       }
@@ -401,7 +412,7 @@ class Engine {
         table[((size_t)p * half + i) * 2 + 1] = (float)std::sin(a);
       }
     void* d = dev_alloc(table.size() * 4);
-    cuda_check(cudaMemcpy(d, table.data(), table.size() * 4, cudaMemcpyHostToDevice), "cudaMemcpy");
+    copy_in(d, table.data(), table.size() * 4);
     w_.cos_sin = (const float*)d;
     w_.table_rows = (int)max_model_len_;
   }
@@ -410,7 +421,8 @@ class Engine {
   void allocate_cache() {
     const size_t per_layer = (size_t)(num_pages_ + 1) * 2 * w_.Hkv * page_ * w_.hd * dt_size(dt_);
     uint8_t* base = (uint8_t*)dev_alloc(per_layer * w_.layers.size());
-    cuda_check(cudaMemset(base, 0, per_layer * w_.layers.size()), "cudaMemset");
+    cuda_check(cudaMemsetAsync(base, 0, per_layer * w_.layers.size(), stream_), "cudaMemsetAsync");
+    cuda_check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
     for (size_t l = 0; l < w_.layers.size(); ++l) {
       w_.layers[l].cache = base + l * per_layer;
       w_.layers[l].cache_pages = num_pages_ + 1;
@@ -561,7 +573,7 @@ class Engine {
     for (int i = 0; i < S; ++i) { init[(size_t)o + i] = i; init[(size_t)o + 2 * S + 1 + i] = i; }     // tok_seg, want_rows
     for (int i = 0; i <= S; ++i) init[(size_t)o + S + i] = i;                             // seg_q_start
     std::memcpy(g.host, init.data(), (size_t)g.n_dyn * 4);
-    cuda_check(cudaMemcpy(g.dev, init.data(), total * 4, cudaMemcpyHostToDevice), "cudaMemcpy");
+    copy_in(g.dev, init.data(), total * 4);
     g.row_epoch.assign((size_t)S, 0);
     g.row_len.assign((size_t)S, 0);
     g.logits = (float*)dev_alloc((size_t)S * w_.V * 4);

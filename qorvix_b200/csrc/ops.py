@@ -36,6 +36,7 @@ _ARGTYPES = {
     "qv_rope_kv_write": [_V, _I, _V, _V, _I, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _V],
     "qv_swiglu": [_V, _V, _I, _I, _I, _I, _V],
     "qv_cast": [_V, _V, _L, _I, _I, _V],
+    "qv_cast_rows": [_V, _L, _V, _L, _I, _I, _I, _I, _V],
     "qv_gemm_simt": [_V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V],
     "qv_gemm_bf16_tc": [_V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _V, _I, _I, _V],
     "qv_packed_weight_bytes": [_I, _I],
@@ -193,6 +194,16 @@ def cast(out, src) -> None:
     rc = _lib("elementwise").qv_cast(
         _ptr(out), _ptr(src), src.numel(), dt_code(src.dtype), dt_code(out.dtype), _stream())
     _check(rc, "cast")
+
+
+def cast_rows(out, src) -> None:
+    """out[r, c] = src[r, c] for 2-D tensors whose rows are contiguous (any row stride), float32 or
+    bfloat16 each: a dense copy of a slice, with a change of type if the two differ."""
+    _need_cuda(out, src)
+    assert out.dim() == 2 and out.shape == src.shape and out.stride(1) == 1 and src.stride(1) == 1
+    rc = _lib("elementwise").qv_cast_rows(_ptr(out), out.stride(0), _ptr(src), src.stride(0), src.shape[0], src.shape[1],
+                                          dt_code(src.dtype), dt_code(out.dtype), _stream())
+    _check(rc, "cast_rows")
 
 
 # ------------------------------------------------------------------ matrix products
@@ -402,6 +413,13 @@ def gemm(out, x, w, packed=None, n: int = 0) -> None:
     if x.dtype == torch.bfloat16 and packed is not None and gemm_bf16_packed(out, x, packed, n or w.shape[0]):
         return
     if w is None:
+        # Only the packed tiles are kept and the kernel that reads them refused x as it is (float32
+        # values, rows that do not start on 16 bytes, a row stride that is no multiple of 8): an
+        # aligned bfloat16 copy of x, which that kernel takes.
+        xb = torch.empty(x.shape, device=x.device, dtype=torch.bfloat16)
+        cast_rows(xb, x)
+        if packed is not None and gemm_bf16_packed(out, xb, packed, n):
+            return
         raise KernelError("the product's shape is one the tensor-core kernel refuses and the weight rows were not kept")
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and gemm_bf16_tc(out, x, w):
         return
@@ -518,8 +536,6 @@ def attention_decode_bf16(out, q, cache_layer, tok_pos, tok_seg, block_table, H,
     if rc == -2:
         return False
     _check(rc, "attention_decode_bf16")
-    if splits > 1:
-        add_launches(1)                              # the merge of the slices
     return True
 
 

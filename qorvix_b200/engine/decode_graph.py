@@ -161,3 +161,4 @@ class DecodeLoop:
 
     def finish(self) -> None:
         torch.cuda.synchronize(self.runner.device)
+        ops.check_kernel_errors()                  # a kernel that gave up on a bounded wait makes the loop's tokens void

@@ -249,3 +249,23 @@ def test_few_tokens_product_scaled_by_the_norm_of_its_input(M, N, K, swiglu):
     torch.cuda.synchronize()
     ops.check_kernel_errors()
     assert (c.double() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+
+
+def test_a_linear_that_kept_only_its_packed_tiles_still_takes_float32_and_sliced_inputs():
+    """Linear drops a bfloat16 matrix's rows once the packed tiles exist; an input the packed kernel
+    refuses as it is (float32 values, a view whose rows do not start on 16 bytes) is then copied
+    into aligned bfloat16 rows instead of failing."""
+    from qorvix_b200.parts.linear import Linear
+    w = rnd(200, 136, seed=3, scale=0.05)
+    lin = Linear(w.clone())
+    assert lin.weight is None and lin.packed is not None
+    x32 = torch.randn(5, 136, device=DEV, generator=torch.Generator(device=DEV).manual_seed(1))
+    ref = x32.to(torch.bfloat16).double() @ w.double().t()
+    out = lin(x32, out_dtype=torch.float32)
+    assert (out.double() - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
+    wide = rnd(7, 141, seed=4)
+    xs = wide[:, 5:]                                   # rows start 10 bytes into a 16-byte line
+    assert xs.data_ptr() % 16 != 0
+    out = lin(xs, out_dtype=torch.bfloat16)
+    ref = xs.double() @ w.double().t()
+    assert (out.double() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()

@@ -6,6 +6,12 @@ workspace of the key slices in an array inside the library.  Here it is checked 
 regular entry point, on two calls in a row with different shapes (the second call finds the
 first call's leftovers in the shared array), and its size limit is checked to refuse cleanly.
 
+Why equality with the regular entry point is the claim: both run the same kernels on the same
+inputs with the same slice counts, the only difference being where the slices' partial results
+lie, so the outputs must agree bit for bit; that the regular entry point computes the right
+attention is held against float64 arithmetic in tests/test_kernels_gpu.py.  The call must also
+leave the device's memory as it found it: nothing allocated, nothing freed.
+
 This file sorts last on purpose: a run that stops at the first failure has then run every
 other test already.
 """
@@ -58,9 +64,13 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice_in_a_row():
         want = torch.zeros_like(q)
         assert ops.attention_decode_bf16(want, q, cache, pos, seg, bt, s["H"], s["Hkv"], s["hd"], s["page"], 0, scale, s["splits"])
         got = torch.full_like(q, float("nan"))
+        torch.cuda.synchronize()
+        held, (free_before, _) = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()
         rc = _static_call(lib, got, q, cache, pos, seg, bt, s["H"], s["Hkv"], s["hd"], s["page"], scale, s["splits"])
         assert rc == 0, rc
         torch.cuda.synchronize()
+        if s is not shapes[0]:           # (the library's first launch on a device may load its kernels)
+            assert torch.cuda.memory_allocated() == held and torch.cuda.mem_get_info()[0] == free_before
         assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2)
         assert torch.equal(got, want)        # same kernels, same order of sums: in fact identical
 
