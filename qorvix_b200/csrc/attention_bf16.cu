@@ -298,58 +298,13 @@ int launch_prefill_tile(bf16* out, int ld_out, const bf16* q, int ld_q, const bf
 }
 
 // ---------------------------------------------------------------- decode
-// When the keys of a (token, kv head) are cut into slices, each slice's CTA leaves its partial result
-// in the workspace and draws a ticket; the CTA that draws the last one merges all slices, in slice
-// order whichever CTA it is, and puts the ticket counter back to zero for the next launch.  (A
-// second launch for the merge cost about as much as the slices of a short context themselves.)
-// The counters are shared by every launch of this library on a device: launches of the decode
-// kernels that may run at the same time (other streams, other threads) must not share a
-// (token index, kv head); launches in one stream never overlap, also under programmatic dependent launch,
-// since each waits for the launch ahead of it before it touches anything.
-#define DEC_TICKETS 32768
-__device__ unsigned int g_decode_tickets[DEC_TICKETS];
-
-// Called by all threads of a slice's CTA after its partial result is written.  `flag` is one int of
-// shared memory.  G query heads share the kv head; out gets the merged rows.
-template <int HD>
-__device__ __forceinline__ void merge_slices_by_last_cta(bf16* __restrict__ out, int ld_out, const float* __restrict__ partial, int t, int kvh,
-                                                         int H, int Hkv, int G, int splits, int* flag) {
-  constexpr int ROW = HD + 2;
-  __threadfence();                                  // this CTA's partial result before its ticket
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    unsigned int* ticket = &g_decode_tickets[((size_t)t * Hkv + kvh) % DEC_TICKETS];
-    const unsigned int mine = atomicAdd(ticket, 1u);
-    *flag = mine == (unsigned int)(splits - 1);
-    if (*flag) *ticket = 0u;
-  }
-  __syncthreads();
-  if (!*flag) return;
-  __threadfence();                                  // the other CTAs' partial results after the last ticket
-  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
-    const int row = idx / HD, d = idx - row * HD;
-    const int h = kvh * G + row;
-    const float* src = partial + ((size_t)t * H + h) * splits * ROW;
-    float m = -INFINITY;
-    for (int sp = 0; sp < splits; ++sp) m = fmaxf(m, __ldcg(src + (size_t)sp * ROW + HD));
-    float acc = 0.f, l = 0.f;
-    for (int sp = 0; sp < splits; ++sp) {
-      const float ms = __ldcg(src + (size_t)sp * ROW + HD);
-      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
-      acc += __ldcg(src + (size_t)sp * ROW + d) * f;
-      l += __ldcg(src + (size_t)sp * ROW + HD + 1) * f;
-    }
-    out[(size_t)t * ld_out + (size_t)h * HD + d] = __float2bfloat16_rn(acc / l);
-  }
-}
-
 // partial results of a slice: [token][head][slice][HD + 2] floats (out unnormalised, then m, l)
 template <int HD, int ROWS>
 __global__ void __launch_bounds__(128) attn_decode_kernel(bf16* __restrict__ out, int ld_out, const bf16* __restrict__ q, int ld_q,
                                                           const bf16* __restrict__ cache, const int* __restrict__ tok_pos,
                                                           const int* __restrict__ tok_seg, const int* __restrict__ block_table,
                                                           int max_blocks, int H, int Hkv, int page, int window, float scale_log2,
-                                                          int splits, float* __restrict__ partial, int fused_merge) {
+                                                          int splits, float* __restrict__ partial) {
   extern __shared__ float sm[];                 // [4 warps][16 rows][HD + 2]
   pdl_wait();
   pdl_launch_dependents();
@@ -422,10 +377,6 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(bf16* __restrict__ out
       if (d == 0) { dst[HD] = m; dst[HD + 1] = l; }
     }
   }
-  if (splits > 1 && fused_merge) {
-    __syncthreads();                               // the staging rows in shared memory are read; one word of them serves as the flag
-    merge_slices_by_last_cta<HD>(out, ld_out, partial, t, kvh, H, Hkv, G, splits, (int*)sm);
-  }
 }
 
 // The same slice of work with the keys and values brought into shared memory by the copy engine:
@@ -441,7 +392,7 @@ __global__ void __launch_bounds__(32 * (NW + 1)) attn_decode_bulk_kernel(bf16* _
                                                                const bf16* __restrict__ cache, const int* __restrict__ tok_pos,
                                                                const int* __restrict__ tok_seg, const int* __restrict__ block_table,
                                                                int max_blocks, int H, int Hkv, int page, int window, float scale_log2,
-                                                               int splits, float* __restrict__ partial, int* err, int fused_merge) {
+                                                               int splits, float* __restrict__ partial, int* err) {
   extern __shared__ uint8_t dec_smem[];
   constexpr int KB = 16 * HD * 2;                       // bytes of 16 key rows (and of 16 value rows)
   constexpr int STAGE = 2 * KB;
@@ -553,10 +504,6 @@ __global__ void __launch_bounds__(32 * (NW + 1)) attn_decode_bulk_kernel(bf16* _
       if (d == 0) { dst[HD] = m; dst[HD + 1] = l; }
     }
   }
-  if (splits > 1 && fused_merge) {
-    __syncthreads();                               // the staging rows in shared memory are read; one word of them serves as the flag
-    merge_slices_by_last_cta<HD>(out, ld_out, partial, t, kvh, H, Hkv, G, splits, (int*)sm);
-  }
 }
 
 // merges the slices of one (token, head) in slice order
@@ -599,8 +546,6 @@ int launch_decode(bf16* out, int ld_out, const bf16* q, int ld_q, const bf16* ca
                   float* partial, cudaStream_t st) {
   dim3 grid(splits, Hkv, T);
   int rc;
-  // the slices' results are merged by the CTA that finishes last, when every (token, kv head) has a ticket counter of its own
-  const int fused_merge = (splits > 1 && (long long)T * Hkv <= DEC_TICKETS) ? 1 : 0;
   if (g_decode_variant == 0 && g_decode_err != nullptr) {
     // at most 8 query heads per kv head: half-tile state (fewer registers, fewer instructions)
     const int G = H / Hkv;
@@ -615,7 +560,7 @@ int launch_decode(bf16* out, int ld_out, const bf16* q, int ld_q, const bf16* ca
       configured = true;                                                                                                 \
     }                                                                                                                    \
     rc = qv_launch(attn_decode_bulk_kernel<HD, ROWS_, NW_>, grid, dim3(32 * (NW_ + 1)), smem, st, out, ld_out, q, ld_q, cache, tok_pos, \
-                   tok_seg, bt, max_blocks, H, Hkv, page, window, scale_log2, splits, partial, g_decode_err, fused_merge); \
+                   tok_seg, bt, max_blocks, H, Hkv, page, window, scale_log2, splits, partial, g_decode_err);           \
   } while (0)
     if (G > 8) BULK_LAUNCH(2, 4);
     else BULK_LAUNCH(1, 4);
@@ -630,9 +575,9 @@ int launch_decode(bf16* out, int ld_out, const bf16* q, int ld_q, const bf16* ca
     }
     // (the half-tile state that helps the bulk kernel measured slower here: 14.8 against 13.6 us)
     rc = qv_launch(attn_decode_kernel<HD, 2>, grid, dim3(128), smem, st, out, ld_out, q, ld_q, cache, tok_pos, tok_seg, bt,
-                   max_blocks, H, Hkv, page, window, scale_log2, splits, partial, fused_merge);
+                   max_blocks, H, Hkv, page, window, scale_log2, splits, partial);
   }
-  if (rc || splits == 1 || fused_merge) return rc;
+  if (rc || splits == 1) return rc;
   return qv_launch(attn_combine_kernel, dim3(H, T), dim3(HD < 128 ? 64 : 128), 0, st, out, ld_out, (const float*)partial, H,
                    (int)HD, splits);
 }

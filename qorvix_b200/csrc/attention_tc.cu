@@ -6,17 +6,19 @@
 // the CUDA cores (cuda/src/cuda_backend.cu:347-395).
 //
 // One CTA = 128 query rows of one head, walking 128-key tiles:
-//   warp 0        TMA: Q once, then K and V tiles into a ring of three stages, every lane issuing
-//                 one of a stage's loads (a page may hold no more than 16 keys)
+//   warp 0        TMA: Q once, then K and V tiles into rings of three stages each, every lane issuing
+//                 one of a stage's loads (a page may hold no more than 16 keys).  Keys and values
+//                 have barriers of their own: a key stage is free again as soon as its Q.K^T is done,
+//                 two products earlier than its values, so that the next keys are under way long
+//                 before the tensor pipe asks for them.
 //   warp 1        MMA: S[j] = Q K_j^T into one of two S buffers in tensor memory (so that S[j+1] is
-//                 computed while the softmax of tile j runs), then O += P_j V_j with P read from one
-//                 of two P buffers in tensor memory and V as an MN-major operand from shared memory
+//                 computed while the softmax of tile j runs), then O += P_j V_j with P read from
+//                 tensor memory and V as an MN-major operand from shared memory
 //   warps 2..     softmax, WGS warpgroups of four warps.  A query row is shared by WGS threads (one
 //                 per warpgroup, same lane of tensor memory), each owning 128 / WGS of the tile's keys:
 //                 it reads its part of the row of S once, agrees with its partners on the row's
-//                 reference maximum through shared memory, computes its exponentials (before it waits
-//                 for anything the tensor pipe still owes), writes them as bfloat16 into P's columns
-//                 in tensor memory and keeps its part of the row sum.  With two
+//                 reference maximum through shared memory, writes its exponentials as bfloat16 into
+//                 P's columns in tensor memory and keeps its part of the row sum.  With two
 //                 warpgroups every scheduler of the SM has two softmax warps to issue from and each
 //                 thread half the exponentials, which is what bounds the one-warpgroup form.
 // The output row lives in tensor memory and the P.V products accumulate into it; a row's reference
@@ -69,12 +71,14 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
   uint64_t* q_full = bars;                           // 1
   uint64_t* s_full = bars + 1;                       // 2
   uint64_t* s_empty = bars + 3;                      // 2
-  uint64_t* p_full = bars + 5;                       // 2
-  uint64_t* p_empty = bars + 7;                      // 2
-  uint64_t* pv_full = bars + 9;
-  uint64_t* kv_full = bars + 10;                     // KV_ST
-  uint64_t* kv_empty = bars + 10 + KV_ST;            // KV_ST
-  uint32_t* tmem_slot = (uint32_t*)(bars + 10 + 2 * KV_ST);
+  uint64_t* p_full = bars + 5;
+  uint64_t* p_empty = bars + 6;
+  uint64_t* pv_full = bars + 7;
+  uint64_t* k_full = bars + 8;                       // KV_ST each
+  uint64_t* k_empty = k_full + KV_ST;
+  uint64_t* v_full = k_empty + KV_ST;
+  uint64_t* v_empty = v_full + KV_ST;
+  uint32_t* tmem_slot = (uint32_t*)(v_empty + KV_ST);
   // What the threads of a row tell each other, 256 bytes for each quarter of the rows (the warps of
   // a quarter meet at a barrier of their own and run ahead of or behind the other quarters): the
   // tile's maxima (bfloat16, rounded up, two tiles in flight: [2][WGS][32 rows]) and at the end the
@@ -103,12 +107,12 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < KV_ST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128 * WGS);
-      mbar_init(&p_full[i], 128 * WGS); mbar_init(&p_empty[i], 1);
+    for (int i = 0; i < KV_ST; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
     }
-    mbar_init(pv_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128 * WGS); }
+    mbar_init(p_full, 128 * WGS); mbar_init(p_empty, 1); mbar_init(pv_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -121,7 +125,7 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;                  // columns 0..255: S, double-buffered
   const uint32_t tmem_pv = tmem + 256;               // HD columns: the output rows
-  const uint32_t tmem_p = tmem + 384;                // 2 x 64 columns: a row of P, two keys per column, for tiles j and j + 1
+  const uint32_t tmem_p = tmem + 384;                // 64 columns: a row of P, two keys per column
 
   if (warp == 0) {
     // The whole warp requests: a tile of keys and values is 8 blocks of 16 keys (a page may hold no
@@ -132,22 +136,29 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
       for (int hf = 0; hf < NH; ++hf) tma_load_2d(sQ + hf * HALF_BYTES, &map_q, q_full, h * HD + hf * 64, q0 + tile0);
     }
     const int last_block = k_last & ~15;
-    const int which = lane / (8 * NH);               // 0: keys, 1: values
+    const int which = lane / (8 * NH);               // 0: keys, 1: values (lanes beyond have nothing to do)
     const int blk = (lane % (8 * NH)) / NH, hf = lane % NH;
-    bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int s = j % KV_ST;
-      if (lane == 0) {
-        ok = mbar_wait(&kv_empty[s], ((j / KV_ST) & 1) ^ 1, a.err, 11);
-        if (ok) mbar_expect_tx(&kv_full[s], 2 * K_BYTES);
-      }
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      if (which < 2) {
+    if (which < 2) {
+      // the lanes that load keys and the lanes that load values each follow their own barriers
+      const int leader = which * 8 * NH;
+      const unsigned group = ((1u << (8 * NH)) - 1u) << leader;
+      uint64_t* full = which ? v_full : k_full;
+      uint64_t* empty = which ? v_empty : k_empty;
+      uint8_t* dst = (which ? sV : sK) + hf * HALF_BYTES + blk * 16 * 128;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % KV_ST;
         int key0 = (tile_begin + j) * KT + blk * 16;
         if (key0 > last_block) key0 = last_block;            // keys nobody sees: any valid page will do
-        const int row = ((bt[key0 / a.page] * 2 + which) * a.Hkv + kvh) * a.page + (key0 % a.page);
-        tma_load_2d((which ? sV : sK) + s * K_BYTES + hf * HALF_BYTES + blk * 16 * 128, &map_kv, &kv_full[s], hf * 64, row);
+        const int pg = bt[key0 / a.page];                    // fetched before the wait: its latency is the wait's
+        int ok = 1;
+        if (lane == leader) {
+          ok = mbar_wait(&empty[s], ((j / KV_ST) & 1) ^ 1, a.err, 11) ? 1 : 0;
+          if (ok) mbar_expect_tx(&full[s], K_BYTES);
+        }
+        ok = __shfl_sync(group, ok, leader);
+        if (!ok) break;
+        const int row = ((pg * 2 + which) * a.Hkv + kvh) * a.page + (key0 % a.page);
+        tma_load_2d(dst + s * K_BYTES, &map_kv, &full[s], hf * 64, row);
       }
     }
   } else if (warp == 1) {
@@ -157,7 +168,7 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
       bool ok = mbar_wait(q_full, 0, a.err, 12);
       auto issue_qk = [&](int j) -> bool {
         const int s = j & 1, ks = j % KV_ST;
-        if (!mbar_wait(&kv_full[ks], (j / KV_ST) & 1, a.err, 13)) return false;
+        if (!mbar_wait(&k_full[ks], (j / KV_ST) & 1, a.err, 13)) return false;
         if (!mbar_wait(&s_empty[s], ((j >> 1) & 1) ^ 1, a.err, 14)) return false;
         tc_fence_after();
         const uint32_t d = tmem + (uint32_t)(s * KT);
@@ -169,6 +180,7 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
           for (int kk = 0; kk < 4; ++kk) umma_f16(d, dq + 2 * kk, dk + 2 * kk, idesc_qk, (hf > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&s_full[s]);
+        umma_commit(&k_empty[ks]);                   // the keys' stage is free once this product has read it
         return true;
       };
       if (ok) ok = issue_qk(0);
@@ -176,18 +188,18 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);
         if (!ok) break;
         const int s = j % KV_ST;                     // the stage of this tile's keys and values
-        const int pb = j & 1;                        // which P buffer this tile's probabilities are in
-        if (!mbar_wait(&p_full[pb], (j >> 1) & 1, a.err, 15)) break;
+        if (!mbar_wait(&v_full[s], (j / KV_ST) & 1, a.err, 16)) break;
+        if (!mbar_wait(p_full, j & 1, a.err, 15)) break;
         tc_fence_after();
         // P [128 rows][128 keys] in tensor memory (64 columns of two keys); V [128 keys][HD] MN-major
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk) {
           const uint32_t v_addr = smem_u32(sV + s * K_BYTES + (kk * 16) * 128);
-          umma_f16_ts(tmem_pv, tmem_p + (uint32_t)(pb * 64 + kk * 8), umma_desc_mn(v_addr, HALF_BYTES), idesc_pv, (kk > 0 || j > 0) ? 1u : 0u);
+          umma_f16_ts(tmem_pv, tmem_p + (uint32_t)(kk * 8), umma_desc_mn(v_addr, HALF_BYTES), idesc_pv, (kk > 0 || j > 0) ? 1u : 0u);
         }
         umma_commit(pv_full);
-        umma_commit(&kv_empty[s]);
-        umma_commit(&p_empty[pb]);
+        umma_commit(&v_empty[s]);
+        umma_commit(p_empty);
       }
     }
   } else {
@@ -281,19 +293,13 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
         }
       }
       l += sum;
-      // this tile's P buffer is free once the product of two tiles ago has read it
-      const int pb = j & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(&p_empty[pb], ((j >> 1) & 1) ^ 1, a.err, 18));
+      // P's columns are free, and the output row is at rest, once the previous tile's P.V is done
+      ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (j & 1) ^ 1, a.err, 18));
       if (!ok) continue;
+      tc_fence_after();
       if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-        // Some row of this warp moves its reference: scale this thread's columns of the warp's rows of
-        // O (by 1 where nothing moved); the partner warps decide alike, from the same values.  O is at
-        // rest once the product of the tile before is done, and stays so until every thread has handed
-        // in this tile's P.  (That product's barrier is waited on only here: it cannot run ahead of
-        // the tile this thread is in, because the next product needs this thread's P.)
-        ok = __all_sync(0xffffffffu, mbar_wait(pv_full, (j - 1) & 1, a.err, 19));
-        if (!ok) continue;
-        tc_fence_after();
+        // some row of this warp moves its reference: scale this thread's columns of the warp's rows
+        // of O (by 1 where nothing moved); the partner warps decide alike, from the same values
 #pragma unroll
         for (int c = 0; c < OPT; c += 32) {
           uint32_t v[32];
@@ -304,12 +310,11 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
           tmem_st32(tmem_pv + lane_base + (uint32_t)(wg * OPT + c), v);
         }
       }
-      tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < KPT; c += 64) tmem_st32(tmem_p + lane_base + (uint32_t)(pb * 64 + ((wg * KPT + c) >> 1)), w + (c >> 1));
+      for (int c = 0; c < KPT; c += 64) tmem_st32(tmem_p + lane_base + (uint32_t)((wg * KPT + c) >> 1), w + (c >> 1));
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&p_full[pb]);
+      mbar_arrive(p_full);
     }
     if (WGS > 1) {
       // the row's sum: every thread's part, added in the same order by all of them.  The barrier

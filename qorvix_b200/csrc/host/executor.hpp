@@ -267,6 +267,7 @@ class Executor {
     if (rc == ERR_UNSUPPORTED) return false;
     check(rc, "attention_decode_bf16");
     ++route_counts()[ROUTE_DECODE];
+    if (splits > 1) ++launches;                    // the merge of the slices
     return true;
   }
 

@@ -536,6 +536,8 @@ def attention_decode_bf16(out, q, cache_layer, tok_pos, tok_seg, block_table, H,
     if rc == -2:
         return False
     _check(rc, "attention_decode_bf16")
+    if splits > 1:
+        add_launches(1)                              # the merge of the slices
     return True
 
 
