@@ -37,28 +37,14 @@ if ROOT not in sys.path:
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
-LLAMA31_8B = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden_size=4096, intermediate_size=14336,
-                  num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
-                  max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=500000.0,
-                  rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
-                                    original_max_position_embeddings=8192),
-                  tie_word_embeddings=False, hidden_act="silu")
+def _shape(name):
+    """config.json of a shape the baseline names (baseline/configs/<name>.json)."""
+    with open(os.path.join(ROOT, "baseline", "configs", name + ".json")) as f:
+        return json.load(f)
 
 
-LLAMA32_1B = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden_size=2048, intermediate_size=8192,
-                  num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
-                  max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=500000.0,
-                  rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
-                                    original_max_position_embeddings=8192),
-                  tie_word_embeddings=True, hidden_act="silu")
-
-LLAMA2_13B = dict(architectures=["LlamaForCausalLM"], vocab_size=32000, hidden_size=5120, intermediate_size=13824,
-                  num_hidden_layers=40, num_attention_heads=40, num_key_value_heads=40, head_dim=128,
-                  max_position_embeddings=4096, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False,
-                  hidden_act="silu")
-
-SHAPES = {"llama31_8b": ("Llama-3.1-8B shape", LLAMA31_8B), "llama32_1b": ("Llama-3.2-1B shape", LLAMA32_1B),
-          "llama2_13b": ("Llama-2-13B shape", LLAMA2_13B)}
+SHAPES = {"llama31_8b": ("Llama-3.1-8B shape", _shape("llama31_8b")), "llama32_1b": ("Llama-3.2-1B shape", _shape("llama32_1b")),
+          "llama2_13b": ("Llama-2-13B shape", _shape("llama2_13b"))}
 
 
 def peaks():

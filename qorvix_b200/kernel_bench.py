@@ -3,7 +3,7 @@
 bench.py puts these figures beside the step's own (`kernels` in its JSON line); run as a program
 it prints them for any of the named shapes:
 
-    python -m qorvix_b200.kernel_bench --config path/to/config.json --batch 8 --ctx 1024 --prefill 2048
+    python -m qorvix_b200.kernel_bench --config baseline/configs/llama31_8b.json --batch 8 --ctx 1024 --prefill 2048 [--only prefill_attention]
 
 Each launch is timed inside a captured chain of launches over rotating weight (or cache) buffers
 larger than L2, with CUDA events around three replays, so the figure is a warm launch's device
@@ -113,18 +113,20 @@ def prefill_attention_case(T: int, H: int, Hkv: int, hd: int, page: int, peaks: 
     return _figures(us, 2 * q.numel() * 2 + T * 2 * Hkv * hd * 2, flops, peaks)
 
 
-def headline_kernels(cfg, batch: int, ctx: int, prefill_tokens: int, peaks: dict, page: int = 16) -> Dict[str, dict]:
+def headline_kernels(cfg, batch: int, ctx: int, prefill_tokens: int, peaks: dict, page: int = 16, only: str = "") -> Dict[str, dict]:
     """The kernels a decode step of `batch` requests at `ctx` tokens and a prefill of `prefill_tokens`
-    spend their time in, each alone: the few-token products, decode attention, the many-token gate/up
-    product and prefill attention."""
+    spend their time in, each alone: the few-token products, decode attention, the many-token products
+    and prefill attention.  `only`: just the cases whose name contains it."""
     H, Hkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
-    out = {}
+    cases = []
     for name, N, K, fused in layer_products(cfg):
-        out[f"decode_{name}_m{batch}"] = gemm_case(batch, N, K, fused, peaks, torch.float32 if name == "lm_head" else torch.bfloat16)
-    out[f"decode_attention_b{batch}_ctx{ctx}"] = decode_attention_case(batch, ctx, H, Hkv, hd, page, peaks)
+        cases.append((f"decode_{name}_m{batch}", lambda N=N, K=K, fused=fused, name=name: gemm_case(
+            batch, N, K, fused, peaks, torch.float32 if name == "lm_head" else torch.bfloat16)))
+    cases.append((f"decode_attention_b{batch}_ctx{ctx}", lambda: decode_attention_case(batch, ctx, H, Hkv, hd, page, peaks)))
     for name, N, K, fused in layer_products(cfg)[:4]:
-        out[f"prefill_{name}_m{prefill_tokens}"] = gemm_case(prefill_tokens, N, K, fused, peaks)
-    out[f"prefill_attention_t{prefill_tokens}"] = prefill_attention_case(prefill_tokens, H, Hkv, hd, page, peaks)
+        cases.append((f"prefill_{name}_m{prefill_tokens}", lambda N=N, K=K, fused=fused: gemm_case(prefill_tokens, N, K, fused, peaks)))
+    cases.append((f"prefill_attention_t{prefill_tokens}", lambda: prefill_attention_case(prefill_tokens, H, Hkv, hd, page, peaks)))
+    out = {name: run() for name, run in cases if only in name}
     ops.check_kernel_errors()
     return out
 
@@ -136,6 +138,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=1024)
     ap.add_argument("--prefill", type=int, default=2048)
+    ap.add_argument("--only", default="", help="just the cases whose name contains this (e.g. prefill_attention, decode_attention, decode_o)")
     ap.add_argument("--hbm-gbs", type=float, default=6650.0)
     ap.add_argument("--bf16-tflops", type=float, default=1590.0)
     args = ap.parse_args()
@@ -144,7 +147,7 @@ def main() -> int:
     raw = json.load(open(args.config))
     cfg = lookup_architecture(architecture_of(raw)).config_from_dict(raw)
     peaks = {"hbm_gbs": args.hbm_gbs, "bf16_tflops": args.bf16_tflops}
-    for name, fig in headline_kernels(cfg, args.batch, args.ctx, args.prefill, peaks).items():
+    for name, fig in headline_kernels(cfg, args.batch, args.ctx, args.prefill, peaks, only=args.only).items():
         print(f"{name:34s} {json.dumps(fig)}", flush=True)
     return 0
 
