@@ -233,8 +233,14 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
         tc_fence_before();
         mbar_arrive(&s_empty[s]);                     // S[s] may be overwritten by tile j + 2
         if (all_visible) {
+          // four independent chains: one chain of KPT dependent maxima would cost more than the loads did
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-          for (int i = 0; i < KPT; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+          for (int i = 0; i < KPT; i += 4) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) m4[u] = fmaxf(m4[u], __uint_as_float(sv[i + u]));
+          }
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         } else {
 #pragma unroll
           for (int i = 0; i < KPT; ++i) {
@@ -271,13 +277,15 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
 #pragma unroll
       for (int c = 0; c < KPT; c += 64) {
         if (all_visible) {                             // most tiles: no mask, two instructions per score
+          float s4[4] = {0.f, 0.f, 0.f, 0.f};          // the row sum in four chains, added in a fixed order
 #pragma unroll
           for (int i = 0; i < 64; i += 2) {
             const float e0 = fast_exp2(fmaf(__uint_as_float(sv[c + i]), a.scale_log2, neg_m));
             const float e1 = fast_exp2(fmaf(__uint_as_float(sv[c + i + 1]), a.scale_log2, neg_m));
-            sum += e0 + e1;
+            s4[(i >> 1) & 3] += e0 + e1;
             w[(c + i) >> 1] = pack2_bf16(e0, e1);
           }
+          sum += (s4[0] + s4[1]) + (s4[2] + s4[3]);
         } else {
 #pragma unroll
           for (int i = 0; i < 64; i += 2) {
