@@ -45,7 +45,7 @@ CUDA_HOST_LIBRARIES = {"executor"}
 # the native command line: an executable, built from these sources by nvcc
 CLI_SOURCES = ["cli/qorvix_main.cpp", "host_runtime.cpp", "ref/ref_model.cpp"]
 CLI_HEADERS = ["host/json.hpp", "host/safetensors.hpp", "host/model_config.hpp", "host/kernels.hpp", "host/dispatch.hpp",
-               "host/executor.hpp", "host/engine.hpp", "host/scheduler.hpp", "ref/ref_ops.hpp"]
+               "host/executor.hpp", "host/engine.hpp", "host/scheduler.hpp", "host/step_types.hpp", "ref/ref_ops.hpp"]
 KERNEL_LIBRARIES = ["elementwise", "gemm_simt", "gemm_bf16", "attention_generic", "attention_bf16", "attention_tc", "sampling"]
 # what a library is built from beside its source and HEADERS (their bytes are part of its name's hash)
 EXTRA_SOURCES = {

@@ -22,6 +22,7 @@
 #include <numeric>
 #include <sstream>
 
+#include "../host/engine.hpp"
 #include "../host/scheduler.hpp"
 
 extern "C" {
@@ -108,7 +109,7 @@ int cmd_generate(const Args& a) {
   std::fflush(stdout);
   qv::SchedulerConfig sc;
   sc.max_concurrent = 1;
-  qv::Scheduler sched(&engine, sc, desc.eos_token_ids);
+  qv::SchedulerT<qv::Engine> sched(&engine, sc, desc.eos_token_ids);
   const double t1 = now_s();
   sched.submit(prompt, sp, 0, [](long long, int tok) { std::printf("%d ", tok); std::fflush(stdout); });
   const auto results = sched.run_to_completion();

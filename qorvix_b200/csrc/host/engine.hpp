@@ -23,6 +23,7 @@
 #include "executor.hpp"
 #include "model_config.hpp"
 #include "safetensors.hpp"
+#include "step_types.hpp"
 
 extern "C" {
 // csrc/host_runtime.cpp
@@ -71,12 +72,6 @@ struct EngineOptions {
   bool use_graphs = true;
   int max_graph_batch = 64;
   bool packed_weights = true;
-};
-
-struct StepEntry {
-  long long id = 0;
-  std::vector<int> tokens;
-  std::vector<int> want;                // places among these tokens whose logits are asked for
 };
 
 class Engine {
@@ -188,6 +183,50 @@ class Engine {
   }
   const int* greedy_ids() const { return greedy_ids_; }
   long long steps_run = 0, tokens_run = 0;
+
+  // One token per row of `logits` (float32 [rows, vocab] on the device, as step() returned them;
+  // rewritten in place by the penalties), in the order of runtime/src/sampler.cpp:43-101: penalties,
+  // greedy if temperature <= 0, temperature, softmax, top-k, top-p, min-p, draw.  Rows that are plainly
+  // greedy take the argmax (the captured decode step's own when it has one).
+  std::vector<int> sample(const float* logits, const std::vector<SampleRow>& rows_spec) {
+    const int rows = (int)rows_spec.size(), V = vocab();
+    std::vector<int> host((size_t)rows);
+    if (rows == 0) return host;
+    int* out = (int*)buffer("sampled", (size_t)rows * 4);
+    bool all_greedy = true;
+    int width = 0;
+    for (const auto& r : rows_spec) { all_greedy = all_greedy && r.plain_greedy(); width = std::max(width, (int)r.recent.size()); }
+    if (all_greedy) {
+      const int* ids = greedy_ids_;
+      if (!ids) {
+        if (k_.argmax(out, logits, rows, V, V, stream_) != 0) throw EngineError("argmax failed to launch");
+        ids = out;
+      }
+      cuda_check(cudaMemcpyAsync(host.data(), ids, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream_), "cudaMemcpyAsync");
+      cuda_check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+      return host;
+    }
+    // per-row parameters: 7 float rows, then top_k and the recent tokens (-1: none) as integers
+    std::vector<float> f((size_t)7 * rows);
+    std::vector<int> iv((size_t)rows * (1 + width), -1);
+    for (int i = 0; i < rows; ++i) {
+      const SampleRow& r = rows_spec[(size_t)i];
+      const float vals[7] = {r.temperature, r.top_p, r.min_p, r.uniform, r.repetition_penalty, r.frequency_penalty, r.presence_penalty};
+      for (int k = 0; k < 7; ++k) f[(size_t)k * rows + i] = vals[k];
+      iv[(size_t)i] = r.top_k;
+      for (size_t k = 0; k < r.recent.size(); ++k) iv[(size_t)rows + (size_t)i * width + k] = r.recent[k];
+    }
+    float* df = (float*)buffer("sample_f", f.size() * 4);
+    int* di = (int*)buffer("sample_i", iv.size() * 4);
+    cuda_check(cudaMemcpyAsync(df, f.data(), f.size() * 4, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync");
+    cuda_check(cudaMemcpyAsync(di, iv.data(), iv.size() * 4, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync");
+    const int rc = k_.sample(out, (float*)logits, rows, V, V, df, di, df + rows, df + 2 * rows, df + 3 * rows, width ? di + rows : nullptr, width,
+                             width ? df + 4 * rows : nullptr, width ? df + 5 * rows : nullptr, width ? df + 6 * rows : nullptr, stream_);
+    if (rc != 0) throw EngineError("the sampling kernel failed to launch (code " + std::to_string(rc) + ")");
+    cuda_check(cudaMemcpyAsync(host.data(), out, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream_), "cudaMemcpyAsync");
+    cuda_check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+    return host;
+  }
 
   // Copies `rows` logits rows to the host.
   std::vector<float> logits_to_host(const float* dev, int rows) {

@@ -24,7 +24,13 @@
 #include <random>
 #include <set>
 
-#include "engine.hpp"
+#include <algorithm>
+#include <string>
+#include <tuple>
+#include <unordered_map>
+#include <vector>
+
+#include "step_types.hpp"
 
 namespace qv {
 
@@ -62,10 +68,14 @@ struct SchedulerConfig {
   int max_chunk = 0;                    // longest prompt portion; 0: the budget alone limits it
 };
 
-class Scheduler {
+// EngineT: max_model_len(), page_size(), length(id), can_run(entries), one_more_token_fits(ids),
+// release(id), step(entries, end, &rows) -> logits handle, sample(logits, rows) -> one id per row.
+// (The native Engine of engine.hpp; a fake with the real page bookkeeping in the scheduler's CPU test.)
+template <class EngineT>
+class SchedulerT {
  public:
   using TokenCallback = std::function<void(long long, int)>;
-  Scheduler(Engine* engine, const SchedulerConfig& cfg, const std::vector<long long>& eos) : e_(engine), cfg_(cfg) {
+  SchedulerT(EngineT* engine, const SchedulerConfig& cfg, const std::vector<long long>& eos) : e_(engine), cfg_(cfg) {
     for (long long t : eos) eos_.insert((int)t);
   }
 
@@ -122,13 +132,13 @@ class Scheduler {
     }
     if (entries.empty()) return finished;
     int rows = 0;
-    const float* logits = e_->step(entries, {}, &rows);
+    const auto logits = e_->step(entries, {}, &rows);
     ++stats.steps;
     stats.tokens += (long long)plan.decode.size();
     for (long long id : plan.decode) { Request& r = requests_.at(id); r.computed += 1; r.has_pending = false; }
     for (const auto& pf : plan.prefill) { requests_.at(pf.first).computed += pf.second; stats.tokens += pf.second; }
     if (!samplers.empty()) {
-      const std::vector<int> ids = sample(logits, rows, samplers);
+      const std::vector<int> ids = e_->sample(logits, sample_rows(samplers));
       for (size_t i = 0; i < samplers.size(); ++i) accept(requests_.at(samplers[i]), ids[i]);
     }
     for (size_t i = 0; i < running_.size();) {
@@ -180,7 +190,7 @@ class Scheduler {
     bool operator<(const Waiting& o) const { return std::tie(neg_priority, seq, id) < std::tie(o.neg_priority, o.seq, o.id); }
   };
 
-  Engine* e_;
+  EngineT* e_;
   SchedulerConfig cfg_;
   std::set<int> eos_;
   long long next_id_ = 1, next_seq_ = 0, front_ = -1;
@@ -312,58 +322,27 @@ class Scheduler {
     return o;
   }
 
-  // one token per row of logits (float32 [rows, vocab] on the device; rewritten in place by the penalties)
-  std::vector<int> sample(const float* logits, int rows, const std::vector<long long>& ids) {
-    const int V = e_->vocab();
-    int* out = (int*)e_->buffer("sampled", (size_t)rows * 4);
-    cudaStream_t st = e_->stream();
-    bool all_greedy = true;
-    for (long long id : ids) { const SamplingParams& p = requests_.at(id).params; all_greedy = all_greedy && p.greedy() && !p.has_penalties(); }
-    const int* greedy = e_->greedy_ids();
-    std::vector<int> host((size_t)rows);
-    if (all_greedy) {
-      if (!greedy) {
-        if (e_->kernels().argmax(out, logits, rows, V, V, st) != 0) throw EngineError("argmax failed to launch");
-        greedy = out;
-      }
-      cuda_check(cudaMemcpyAsync(host.data(), greedy, (size_t)rows * 4, cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync");
-      cuda_check(cudaStreamSynchronize(st), "cudaStreamSynchronize");
-      return host;
-    }
-    int width = 0;
+  // what sampling needs of each row: the request's parameters, the next number of its own random
+  // stream, and the tokens its penalties look at
+  std::vector<SampleRow> sample_rows(const std::vector<long long>& ids) {
+    std::vector<SampleRow> rows;
     for (long long id : ids) {
-      const Request& r = requests_.at(id);
-      if (r.params.has_penalties()) width = std::max(width, std::min(r.n_prompt + (int)r.generated.size(), r.params.penalty_last_n));
-    }
-    // per-row parameters: 7 float rows, then top_k and the recent tokens as integers
-    std::vector<float> f((size_t)7 * rows);
-    std::vector<int> iv((size_t)rows * (1 + width), -1);
-    for (int i = 0; i < rows; ++i) {
-      Request& r = requests_.at(ids[(size_t)i]);
+      Request& r = requests_.at(id);
       const SamplingParams& p = r.params;
-      const bool pen = p.has_penalties();
-      const double u = p.greedy() ? 0.0 : (double)(r.rng() >> 11) * (1.0 / 9007199254740992.0);
-      const float vals[7] = {(float)p.temperature, (float)p.top_p, (float)p.min_p, (float)u, pen ? (float)p.repetition_penalty : 1.f,
-                             pen ? (float)p.frequency_penalty : 0.f, pen ? (float)p.presence_penalty : 0.f};
-      for (int k = 0; k < 7; ++k) f[(size_t)k * rows + i] = vals[k];
-      iv[(size_t)i] = p.top_k;
-      if (pen && width) {
+      SampleRow row;
+      row.temperature = (float)p.temperature; row.top_k = p.top_k; row.top_p = (float)p.top_p; row.min_p = (float)p.min_p;
+      row.uniform = p.greedy() ? 0.f : (float)((double)(r.rng() >> 11) * (1.0 / 9007199254740992.0));
+      if (p.has_penalties()) {
+        row.repetition_penalty = (float)p.repetition_penalty; row.frequency_penalty = (float)p.frequency_penalty;
+        row.presence_penalty = (float)p.presence_penalty;
         std::vector<int> hist(r.prompt.begin(), r.prompt.begin() + r.n_prompt);
         hist.insert(hist.end(), r.generated.begin(), r.generated.end());
-        const int n = std::min((int)hist.size(), p.penalty_last_n);
-        for (int k = 0; k < n; ++k) iv[(size_t)rows + (size_t)i * width + k] = hist[hist.size() - (size_t)n + (size_t)k];
+        const size_t n = std::min(hist.size(), (size_t)p.penalty_last_n);
+        row.recent.assign(hist.end() - (long)n, hist.end());
       }
+      rows.push_back(std::move(row));
     }
-    float* df = (float*)e_->buffer("sample_f", f.size() * 4);
-    int* di = (int*)e_->buffer("sample_i", iv.size() * 4);
-    cuda_check(cudaMemcpyAsync(df, f.data(), f.size() * 4, cudaMemcpyHostToDevice, st), "cudaMemcpyAsync");
-    cuda_check(cudaMemcpyAsync(di, iv.data(), iv.size() * 4, cudaMemcpyHostToDevice, st), "cudaMemcpyAsync");
-    const int rc = e_->kernels().sample(out, (float*)logits, rows, V, V, df, di, df + rows, df + 2 * rows, df + 3 * rows, width ? di + rows : nullptr,
-                                        width, width ? df + 4 * rows : nullptr, width ? df + 5 * rows : nullptr, width ? df + 6 * rows : nullptr, st);
-    if (rc != 0) throw EngineError("the sampling kernel failed to launch (code " + std::to_string(rc) + ")");
-    cuda_check(cudaMemcpyAsync(host.data(), out, (size_t)rows * 4, cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync");
-    cuda_check(cudaStreamSynchronize(st), "cudaStreamSynchronize");
-    return host;
+    return rows;
   }
 };
 

@@ -49,3 +49,17 @@ def test_kernel_bench_takes_its_shapes_from_the_configuration():
                                      num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128))
     assert layer_products(cfg) == [("qkv", 6144, 4096, False), ("o", 4096, 4096, False), ("gate_up", 28672, 4096, True),
                                    ("down", 4096, 14336, False), ("lm_head", 128256, 4096, False)]
+
+
+def test_native_scheduler_decisions_with_a_fake_engine(tmp_path):
+    """tests/native/scheduler_test.cpp: the C++ scheduler (token budget, portions, priority, admission on
+    whole-prompt pages, preemption by recompute, finishes, sampling rows) over the real page bookkeeping
+    with a fake engine; compiled with the host compiler and run here."""
+    from qorvix_b200.csrc.build import CSRC, find_host_compiler
+    exe = tmp_path / "scheduler_test"
+    cmd = [find_host_compiler(), "-O1", "-std=c++17", "-I", str(CSRC), "-o", str(exe), str(ROOT / "tests" / "native" / "scheduler_test.cpp"),
+           str(CSRC / "host_runtime.cpp")]
+    build = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert build.returncode == 0, build.stderr[-3000:]
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0 and run.stdout.strip() == "ok", run.stderr[-2000:]
