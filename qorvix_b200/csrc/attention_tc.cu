@@ -24,8 +24,11 @@
 //                 the first half of its own columns of S (P lives where S was, which leaves room
 //                 for the second O) and keeps its part of the row sum.
 // Order in tensor memory: Q.K^T of tile g+2 overwrites the P of tile g, so the MMA thread issues it only
-// after P.V of tile g has finished (products of different shapes are not kept in issue order), and that
-// product was issued only after every softmax thread had read its S and arrived for tile g.
+// after P.V of tile g has finished, and that product was issued only after every softmax thread had read
+// its S and arrived for tile g.  A softmax warp may run a tile ahead of the others.  The products'
+// completions therefore go to two barriers in turn: a warp that waits for the last product while the one
+// before is still running would be two phases ahead of a single barrier, and a parity wait cannot tell
+// that from "done".
 // The output row lives in tensor memory and the P.V products accumulate into it; a row's reference
 // maximum moves only when the true maximum has grown by more than 2^RESCALE_STEP (then the row in
 // tensor memory is scaled down once, after the product before has finished), so P may reach
@@ -125,7 +128,7 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
   uint64_t* q_empty = bars + 1;                      // 1
   uint64_t* s_full = bars + 2;                       // 2
   uint64_t* p_full = bars + 4;                       // 2
-  uint64_t* pv_full = bars + 6;                      // 1
+  uint64_t* pv_full = bars + 6;                      // 2
   uint64_t* k_full = bars + 8;                       // KV_ST each
   uint64_t* k_empty = k_full + KV_ST;
   uint64_t* v_full = k_empty + KV_ST;
@@ -149,7 +152,7 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 128 * WGS); }
-    mbar_init(pv_full, 1);
+    mbar_init(&pv_full[0], 1); mbar_init(&pv_full[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -221,7 +224,7 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
         // This S goes where the P of two tiles ago lies (and the one after the next where the last P
         // lies): the products that read them must have finished.  Waiting for the last one issued
         // covers both; it was issued a softmax ago, so this costs the softmax warps nothing.
-        if (pv_issued > 0 && !mbar_wait(pv_full, (pv_issued - 1) & 1, a.err, 14)) return false;
+        if (pv_issued > 0 && !mbar_wait(&pv_full[(pv_issued - 1) & 1], ((pv_issued - 1) >> 1) & 1, a.err, 14)) return false;
         tc_fence_after();
         const uint32_t d = tmem + (uint32_t)((gt & 1) * KT);
 #pragma unroll
@@ -258,7 +261,7 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
             const uint32_t p_col = (uint32_t)(((kk * 16) / KPT) * KPT + ((kk * 16) % KPT) / 2);
             umma_f16_ts(o, p + p_col, umma_desc_mn(v_addr, HALF_BYTES), idesc_pv, (kk > 0 || j > 0) ? 1u : 0u);
           }
-          umma_commit(pv_full);
+          umma_commit(&pv_full[g & 1]);
           umma_commit(&v_empty[s]);
           ++pv_issued;
         }
@@ -362,18 +365,13 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
           }
         }
         l += sum;
-        // P is stored only once the product of the tile before has finished.  Without this wait a warp
-        // that runs a tile ahead of the others gave wrong rows now and then (found by the tests with
-        // segments of unequal lengths; a store to unused columns at the same point did no harm, so it
-        // is not the store as such).  The exponentials above did not have to wait.
-        if (g > 0) {
-          ok = __all_sync(0xffffffffu, mbar_wait(pv_full, (g - 1) & 1, a.err, 18));
+        if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+          // Some row of this warp moves its reference: once the product of the tile before has come
+          // to rest, scale this thread's columns of the warp's rows of O (by 1 where nothing moved);
+          // the partner warps decide alike, from the same values.
+          ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[(g - 1) & 1], ((g - 1) >> 1) & 1, a.err, 18));
           if (!ok) continue;
           tc_fence_after();
-        }
-        if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-          // some row of this warp moves its reference: scale this thread's columns of the warp's rows
-          // of O (by 1 where nothing moved); the partner warps decide alike, from the same values
 #pragma unroll
           for (int c = 0; c < OPT; c += 32) {
             uint32_t v[32];
@@ -404,7 +402,7 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
         named_barrier(1 + qd, 32 * WGS);
       }
       if (ok) {
-        ok = __all_sync(0xffffffffu, mbar_wait(pv_full, (g - 1) & 1, a.err, 20));
+        ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[(g - 1) & 1], ((g - 1) >> 1) & 1, a.err, 20));
         tc_fence_after();
         // every lane takes part in the loads (they are warp-wide); only rows of the segment are stored
         const bool store = ok && row_in_seg < t.qlen;
