@@ -5,45 +5,51 @@
 // reference's (runtime/src/text_model.cpp:83-114); its CUDA kernel handles one query at a time on
 // the CUDA cores (cuda/src/cuda_backend.cu:347-395).
 //
-// A work item = 128 query rows of one head, walking 128-key tiles.  One CTA per SM takes items in turn
-// (longest first; see Walk) and runs them through one pipeline that never drains between items:
-//   warp 0        TMA: an item's Q as soon as the last Q.K^T of the item before has read the old one,
-//                 and K and V tiles into rings of three stages each that run on across items, every
-//                 lane issuing one of a stage's loads (a page may hold no more than 16 keys).  Keys
-//                 and values have barriers of their own: a key stage is free again as soon as its
-//                 Q.K^T is done, two products earlier than its values.
-//   warp 1        MMA: S[g] = Q K^T into one of two S buffers in tensor memory (so that S[g+1] is
-//                 computed while the softmax of tile g runs), then O += P V with P read from
-//                 tensor memory and V as an MN-major operand from shared memory.  O has two buffers
-//                 too, one per item in turn: the first products of the next item run while the
-//                 softmax warps still write the last item's output.
-//   warps 2..     softmax, WGS warpgroups of four warps.  A query row is shared by WGS threads (one
-//                 per warpgroup, same lane of tensor memory), each owning 128 / WGS of the tile's keys:
-//                 it reads its part of the row of S once, agrees with its partners on the row's
-//                 reference maximum through shared memory, writes its exponentials as bfloat16 over
-//                 the first half of its own columns of S (P lives where S was, which leaves room
-//                 for the second O) and keeps its part of the row sum.
-// Order in tensor memory: Q.K^T of tile g+2 overwrites the P of tile g, so the MMA thread issues it only
-// after P.V of tile g has finished, and that product was issued only after every softmax thread had read
-// its S and arrived for tile g.  A softmax warp may run a tile ahead of the others.  The products'
-// completions therefore go to two barriers in turn: a warp that waits for the last product while the one
-// before is still running would be two phases ahead of a single barrier, and a parity wait cannot tell
-// that from "done".
-// The output row lives in tensor memory and the P.V products accumulate into it; a row's reference
+// A work item = two neighbouring tiles of 128 query rows of one head, A and B (B is missing where a
+// segment ends after A), walking the 128-key tiles that they see.  One CTA per SM takes items in turn
+// (longest first; see Walk) and runs them through one pipeline that is set up once.  In launches
+// with so few tiles that pairs would leave SMs without work (PAIRED = false) an item is one tile:
+// tile B's warps then idle and the tile's S takes both S buffers in turn, so that the S of the next
+// keys is computed while the softmax of these runs.
+//   warp 0        TMA: K and V tiles into rings of two stages each that run on
+//                 across items, every lane issuing one of a stage's loads (a page may hold no more
+//                 than 16 keys).  A key stage is free again as soon as the last Q.K^T that uses it
+//                 is done, its values' stage after the last P.V.
+//   warp 1        MMA: for each query tile in turn, O += P V of the tile's current keys (P read from
+//                 tensor memory, V as an MN-major operand from shared memory) as soon as its softmax
+//                 warpgroup has written P, then S = Q K^T of the next keys into the tile's S.
+//   warp 2        TMA: an item's Q tiles, each as soon as the last Q.K^T of the item before has read
+//                 the old one.
+//   warps 4..11   softmax of tile A, warps 12..19 of tile B, two warpgroups each.  A query row is
+//                 shared by two threads (one per warpgroup, same lane of tensor memory), each owning 64
+//                 of the tile's 128 keys: it reads its part of the row of S (once for the maximum, on
+//                 which it agrees with its partner through shared memory, and once more, 32 columns
+//                 at a time, for the exponentials: few registers a thread), writes the exponentials as
+//                 bfloat16 over the first half of its own columns of S (P lives where S was) and keeps
+//                 its part of the row sum.  While the warps of one tile wait for their next S (the
+//                 tile's P.V and next Q.K^T run then), those of the other compute: every scheduler
+//                 of the SM has four softmax warps in two phases to issue from, which keeps the
+//                 special-function unit busy (one or two warps a scheduler leave it idle half the time).
+// Order in tensor memory: the next Q.K^T into an S buffer overwrites the P in it, so the MMA thread
+// issues it only after the P.V that reads that P has finished; with pairs a full S therefore also says
+// that the tile's output rows are at rest.  No thread is ever two phases behind a barrier (a parity
+// wait cannot tell that from "done"): the P.V completions have a barrier per S buffer for that reason.
+// The output rows live in tensor memory and the P.V products accumulate into them; a row's reference
 // maximum moves only when the true maximum has grown by more than 2^RESCALE_STEP (then the row in
-// tensor memory is scaled down once, after the product before has finished), so P may reach
-// 2^RESCALE_STEP and most tiles need no work on O.
+// tensor memory is scaled down once), so P may reach 2^RESCALE_STEP and most tiles need no work on O.
 // Softmax statistics, rescaling and the output sum are float32.  Every mbarrier wait is bounded
 // and reports through *err instead of hanging.
 #include "tc_common.cuh"
 
-#define KV_ST 3             // stages of keys and values in shared memory
+#define K_ST 2              // stages of keys in shared memory
+#define V_ST 2              // stages of values
 #define RESCALE_STEP 8.0f
-#define QT 128              // query rows per item
+#define QT 128              // query rows per tile
 #define KT 128              // keys per tile
-#define SOFTMAX_WGS 2       // warpgroups that share the softmax of a tile (1 or 2)
+#define ATTN_THREADS 640    // warps 0..3: TMA of keys and values, MMA, TMA of queries, idle; 4..11 and 12..19: softmax
 
 namespace {
+
 
 struct AttnArgs {
   bf16* out;
@@ -52,7 +58,8 @@ struct AttnArgs {
   const int* block_table;
   int* err;
   int ld_out, max_blocks, H, Hkv, page, window;
-  int segments, q_tiles, items;                      // items = H x segments x q_tiles (some of them empty)
+  int segments, q_pairs, items;                      // items = H x segments x q_pairs (some of them empty)
+  int paired;                                        // 1: an item is two query tiles; 0: one (q_pairs then counts tiles)
   float scale_log2;
 };
 
@@ -63,29 +70,38 @@ __device__ __forceinline__ void named_barrier(int id, int count) {
 
 struct Item {
   const int* bt;                                     // the segment's row of the block table
-  int h, kvh, q0, qlen, tile0, pos0, k_last, tile_begin, n_tiles;
+  int h, kvh, q0, qlen, tile0, pos0;                 // tile0: first row of tile A in its segment (B: tile0 + 128)
+  int k_last, tile_begin;                            // the last key any row of the item sees; its first key tile
+  int n_a, n_b;                                      // key tiles of A and of B (0: no B; else n_a or n_a + 1)
 };
 
 // Item `idx` of the launch: heads fastest (the heads of one kv head are neighbours and read the same
-// keys and values), then segments, then query tiles from the last one (which sees the most keys)
-// down.  False for a tile beyond its segment's end.
+// keys and values), then segments, then pairs of query tiles from the last pair (which sees the most
+// keys) down.  False for a pair beyond its segment's end.
+template <bool PAIRED>
 __device__ __forceinline__ bool item_at(const AttnArgs& a, int idx, Item& t) {
   t.h = idx % a.H;
   const int rest = idx / a.H;
   const int seg = rest % a.segments, y = rest / a.segments;
   t.q0 = a.seg_q_start[seg];
   t.qlen = a.seg_q_start[seg + 1] - t.q0;
-  t.tile0 = (a.q_tiles - 1 - y) * QT;
+  t.tile0 = (a.q_pairs - 1 - y) * (PAIRED ? 2 * QT : QT);
   if (t.tile0 >= t.qlen) return false;
   t.pos0 = a.seg_pos0[seg];
   t.kvh = t.h / (a.H / a.Hkv);
   t.bt = a.block_table + (size_t)seg * a.max_blocks;
-  const int rows_here = t.qlen - t.tile0 < QT ? t.qlen - t.tile0 : QT;
-  t.k_last = t.pos0 + t.tile0 + rows_here - 1;
+  const int rows = t.qlen - t.tile0;                 // of both tiles
+  const int last_a = t.pos0 + t.tile0 + (rows < QT ? rows : QT) - 1;
   int k_first = 0;
   if (a.window > 0) { const int f = t.pos0 + t.tile0 - a.window + 1; k_first = f > 0 ? f : 0; }
   t.tile_begin = k_first / KT;
-  t.n_tiles = t.k_last / KT - t.tile_begin + 1;
+  t.n_a = last_a / KT - t.tile_begin + 1;
+  t.n_b = 0;
+  t.k_last = last_a;
+  if (PAIRED && rows > QT) {
+    t.k_last = t.pos0 + t.tile0 + (rows < 2 * QT ? rows : 2 * QT) - 1;
+    t.n_b = t.k_last / KT - t.tile_begin + 1;
+  }
   return true;
 }
 
@@ -93,6 +109,7 @@ __device__ __forceinline__ bool item_at(const AttnArgs& a, int idx, Item& t) {
 // and fro (CTA c gets item c of an even round and item gridDim.x - 1 - c of an odd one), so that a
 // CTA that got a long item in one round gets a short one in the next.  Every role of the CTA walks
 // the same list on its own.
+template <bool PAIRED>
 struct Walk {
   int round, cta, ctas;
   __device__ bool next(const AttnArgs& a, Item& t) {
@@ -101,43 +118,39 @@ struct Walk {
       if (first >= a.items) return false;
       const long long idx = first + ((round & 1) ? ctas - 1 - cta : cta);
       ++round;
-      if (idx < a.items && item_at(a, (int)idx, t)) return true;
+      if (idx < a.items && item_at<PAIRED>(a, (int)idx, t)) return true;
     }
   }
 };
 
-template <int HD, int WGS>
-__global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
-                                                                         const __grid_constant__ CUtensorMap map_kv, const AttnArgs a) {
+template <int HD, bool PAIRED>
+__global__ void __launch_bounds__(ATTN_THREADS) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                       const __grid_constant__ CUtensorMap map_kv, const AttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int NH = HD / 64;                        // 64-element halves of the head
   constexpr int Q_BYTES = QT * HD * 2;               // [NH][128 rows][64]
   constexpr int K_BYTES = KT * HD * 2;               // [NH][128 keys][64]
   constexpr int HALF_BYTES = 128 * 128;              // one [128][64] bf16 tile
-  constexpr int KPT = KT / WGS;                      // keys of a tile per softmax thread
-  constexpr int OPT = HD / WGS;                      // output columns per softmax thread
-  static_assert(WGS == 1 || WGS == 2, "one or two softmax warpgroups");
-  static_assert(KPT % 64 == 0 && OPT % 32 == 0, "a thread's keys come in chunks of 64, its output columns in chunks of 32");
-  static_assert(2 * KT + 2 * HD <= 512, "S and O, two buffers each, must fit tensor memory");
+  static_assert(2 * KT + 2 * HD <= 512, "S and O of both query tiles must fit tensor memory");
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = base;
-  uint8_t* sK = sQ + Q_BYTES;                        // KV_ST stages
-  uint8_t* sV = sK + KV_ST * K_BYTES;                // KV_ST stages
-  uint64_t* bars = (uint64_t*)(sV + KV_ST * K_BYTES);
-  uint64_t* q_full = bars;                           // 1
-  uint64_t* q_empty = bars + 1;                      // 1
-  uint64_t* s_full = bars + 2;                       // 2
-  uint64_t* p_full = bars + 4;                       // 2
-  uint64_t* pv_full = bars + 6;                      // 2
-  uint64_t* k_full = bars + 8;                       // KV_ST each
-  uint64_t* k_empty = k_full + KV_ST;
-  uint64_t* v_full = k_empty + KV_ST;
-  uint64_t* v_empty = v_full + KV_ST;
-  uint32_t* tmem_slot = (uint32_t*)(v_empty + KV_ST);
-  // What the threads of a row tell each other, 256 bytes for each quarter of the rows (the warps of
-  // a quarter meet at a barrier of their own and run ahead of or behind the other quarters): the
-  // tile's maxima (bfloat16, rounded up, two tiles in flight: [2][WGS][32 rows]) and at the end of
-  // an item the row sums (float32 [WGS][32 rows], over the same bytes)
+  uint8_t* sQ = base;                                // tiles A and B
+  uint8_t* sK = sQ + 2 * Q_BYTES;                    // K_ST stages
+  uint8_t* sV = sK + K_ST * K_BYTES;                 // V_ST stages
+  uint64_t* bars = (uint64_t*)(sV + V_ST * K_BYTES);
+  uint64_t* q_full = bars;                           // [2]: one per query tile, like the next four
+  uint64_t* q_empty = bars + 2;
+  uint64_t* s_full = bars + 4;
+  uint64_t* p_full = bars + 6;
+  uint64_t* pv_done = bars + 8;
+  uint64_t* k_full = bars + 10;                      // K_ST each
+  uint64_t* k_empty = k_full + K_ST;
+  uint64_t* v_full = k_empty + K_ST;                 // V_ST each
+  uint64_t* v_empty = v_full + V_ST;
+  uint32_t* tmem_slot = (uint32_t*)(v_empty + V_ST);
+  // What the two threads of a row tell each other, 256 bytes for each (query tile, quarter of the rows)
+  // (the warps of a quarter meet at a barrier of their own): the tile's maxima (bfloat16, rounded up,
+  // two tiles in flight: [2][2][32 rows]) and at the end of an item the row sums (float32 [2][32 rows],
+  // over the same bytes)
   uint8_t* xchg = (uint8_t*)(bars + 32);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -145,14 +158,12 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
   pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
-    for (int i = 0; i < KV_ST; ++i) {
-      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(&q_full[x], 1); mbar_init(&q_empty[x], 1);
+      mbar_init(&s_full[x], 1); mbar_init(&p_full[x], 256); mbar_init(&pv_done[x], 1);
     }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 128 * WGS); }
-    mbar_init(&pv_full[0], 1); mbar_init(&pv_full[1], 1);
+    for (int i = 0; i < K_ST; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
+    for (int i = 0; i < V_ST; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -163,17 +174,15 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = *tmem_slot;                  // columns 0..255: S, two buffers (P over the first half of each thread's share)
-  const uint32_t tmem_o = tmem + 2 * KT;             // 2 x HD columns: the output rows, two buffers
+  const uint32_t tmem = *tmem_slot;                  // columns 0..255: S of A and of B (P over the first half of each)
+  const uint32_t tmem_o = tmem + 2 * KT;             // 2 x HD columns: the output rows of A and of B
 
-  Walk walk{0, (int)blockIdx.x, (int)gridDim.x};
+  Walk<PAIRED> walk{0, (int)blockIdx.x, (int)gridDim.x};
   Item t;
-  // `it` counts this CTA's items, `g` its key tiles over all items: rings and buffers are indexed by them
 
   if (warp == 0) {
     // The whole warp requests: a tile of keys and values is 8 blocks of 16 keys (a page may hold no
-    // more), each in NH halves of 64 dims, i.e. up to 32 small TMA loads.  One thread issuing them
-    // all took as long as the tile's softmax; the lanes issue one load each.
+    // more), each in NH halves of 64 dims, i.e. up to 32 small TMA loads; the lanes issue one each.
     const int which = lane / (8 * NH);               // 0: keys, 1: values (lanes beyond have nothing to do)
     const int blk = (lane % (8 * NH)) / NH, hf = lane % NH;
     if (which < 2) {
@@ -182,33 +191,45 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
       const unsigned group = ((1u << (8 * NH)) - 1u) << leader;
       uint64_t* full = which ? v_full : k_full;
       uint64_t* empty = which ? v_empty : k_empty;
+      const int stages = which ? V_ST : K_ST;
       uint8_t* dst = (which ? sV : sK) + hf * HALF_BYTES + blk * 16 * 128;
-      int g = 0;
+      int s = 0;                                     // the ring's stage, and how often it has been round
+      uint32_t lap = 0;
       bool alive = true;
-      for (int it = 0; alive && walk.next(a, t); ++it) {
-        if (lane == 0) {
-          // the last Q.K^T of the item before has read the old Q
-          alive = mbar_wait(q_empty, (it & 1) ^ 1, a.err, 10);
-          if (alive) {
-            mbar_expect_tx(q_full, Q_BYTES);
-            for (int f = 0; f < NH; ++f) tma_load_2d(sQ + f * HALF_BYTES, &map_q, q_full, t.h * HD + f * 64, t.q0 + t.tile0);
-          }
-        }
+      while (alive && walk.next(a, t)) {
         const int last_block = t.k_last & ~15;
-        for (int j = 0; j < t.n_tiles; ++j, ++g) {
-          const int s = g % KV_ST;
+        const int n = t.n_b > t.n_a ? t.n_b : t.n_a;
+        for (int j = 0; j < n; ++j) {
           int key0 = (t.tile_begin + j) * KT + blk * 16;
           if (key0 > last_block) key0 = last_block;            // keys nobody sees: any valid page will do
           const int pg = t.bt[key0 / a.page];                  // fetched before the wait: its latency is the wait's
           int ok = 1;
           if (lane == leader) {
-            ok = alive && mbar_wait(&empty[s], ((g / KV_ST) & 1) ^ 1, a.err, 11) ? 1 : 0;
+            ok = mbar_wait(&empty[s], (lap & 1) ^ 1, a.err, 11) ? 1 : 0;
             if (ok) mbar_expect_tx(&full[s], K_BYTES);
           }
           ok = __shfl_sync(group, ok, leader);
           if (!ok) { alive = false; break; }
           const int row = ((pg * 2 + which) * a.Hkv + t.kvh) * a.page + (key0 % a.page);
           tma_load_2d(dst + s * K_BYTES, &map_kv, &full[s], hf * 64, row);
+          if (++s == stages) { s = 0; ++lap; }
+        }
+      }
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {
+      int loads[2] = {0, 0};                         // of tile A and of tile B so far: their barriers' phases
+      bool alive = true;
+      while (alive && walk.next(a, t)) {
+        for (int x = 0; x < 2 && alive; ++x) {
+          if (x == 1 && t.n_b == 0) break;
+          // the last Q.K^T of the tile loaded before has read the old Q
+          alive = mbar_wait(&q_empty[x], (loads[x] & 1) ^ 1, a.err, 10);
+          if (!alive) break;
+          mbar_expect_tx(&q_full[x], Q_BYTES);
+          for (int f = 0; f < NH; ++f)
+            tma_load_2d(sQ + x * Q_BYTES + f * HALF_BYTES, &map_q, &q_full[x], t.h * HD + f * 64, t.q0 + t.tile0 + x * QT);
+          ++loads[x];
         }
       }
     }
@@ -216,90 +237,126 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(QT, KT, 0);
       constexpr uint32_t idesc_pv = umma_idesc(QT, HD, 1);
-      int pv_issued = 0;                             // P.V products issued so far (= committed to pv_full)
-      // S of key tile gt; `last`: no later product of the item reads Q
-      auto issue_qk = [&](int gt, bool last) -> bool {
-        const int ks = gt % KV_ST;
-        if (!mbar_wait(&k_full[ks], (gt / KV_ST) & 1, a.err, 13)) return false;
-        // This S goes where the P of two tiles ago lies (and the one after the next where the last P
-        // lies): the products that read them must have finished.  Waiting for the last one issued
-        // covers both; it was issued a softmax ago, so this costs the softmax warps nothing.
-        if (pv_issued > 0 && !mbar_wait(&pv_full[(pv_issued - 1) & 1], ((pv_issued - 1) >> 1) & 1, a.err, 14)) return false;
+      int loads[2] = {0, 0};                         // Q tiles of A and of B seen so far
+      int n_pv[2] = {0, 0};                          // P.V products of A and of B issued so far (Q.K^T run one ahead)
+      int kbase = 0;                                 // key tiles of all items before this one: the rings' positions
+      // S of query tile qx over the item's key tile j, into S buffer x (`last`: no later product reads this Q)
+      auto qk = [&](int x, int qx, int j, bool last) -> bool {
+        const int g = kbase + j, ks = g % K_ST;
+        if (!mbar_wait(&k_full[ks], (g / K_ST) & 1, a.err, 13)) return false;
+        // the buffer's last P lies where this S goes: the product that reads it must have finished
+        if (n_pv[x] > 0 && !mbar_wait(&pv_done[x], (n_pv[x] - 1) & 1, a.err, 14)) return false;
         tc_fence_after();
-        const uint32_t d = tmem + (uint32_t)((gt & 1) * KT);
+        const uint32_t d = tmem + (uint32_t)(x * KT);
 #pragma unroll
         for (int hf = 0; hf < NH; ++hf) {
-          const uint64_t dq = umma_desc(smem_u32(sQ + hf * HALF_BYTES));
+          const uint64_t dq = umma_desc(smem_u32(sQ + qx * Q_BYTES + hf * HALF_BYTES));
           const uint64_t dk = umma_desc(smem_u32(sK + ks * K_BYTES + hf * HALF_BYTES));
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) umma_f16(d, dq + 2 * kk, dk + 2 * kk, idesc_qk, (hf > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&s_full[gt & 1]);
-        umma_commit(&k_empty[ks]);                   // the keys' stage is free once this product has read it
-        if (last) umma_commit(q_empty);
+        umma_commit(&s_full[x]);
+        if (qx == 1 || t.n_b == 0) umma_commit(&k_empty[ks]);  // B (where there is one) is the last to read a key tile
+        if (last) umma_commit(&q_empty[qx]);
         return true;
       };
-      int g = 0;
-      bool ok = true;
-      for (int it = 0; ok && walk.next(a, t); ++it) {
-        ok = mbar_wait(q_full, it & 1, a.err, 12);
-        if (ok) ok = issue_qk(g, t.n_tiles == 1);
-        const uint32_t o = tmem_o + (uint32_t)((it & 1) * HD);
-        for (int j = 0; j < t.n_tiles && ok; ++j, ++g) {
-          if (j + 1 < t.n_tiles) ok = issue_qk(g + 1, j + 2 == t.n_tiles);
-          if (!ok) break;
-          const int s = g % KV_ST;                   // the stage of this tile's values
-          if (!mbar_wait(&v_full[s], (g / KV_ST) & 1, a.err, 16)) { ok = false; break; }
-          if (!mbar_wait(&p_full[g & 1], (g >> 1) & 1, a.err, 15)) { ok = false; break; }
-          tc_fence_after();
-          // P [128 rows][128 keys] in tensor memory, two keys per column, each softmax warpgroup's share
-          // at the start of its share of S; V [128 keys][HD] MN-major
-          const uint32_t p = tmem + (uint32_t)((g & 1) * KT);
+      // O of query tile qx += P V over the item's key tile j, P from S buffer x
+      auto pv = [&](int x, int qx, int j) -> bool {
+        const int g = kbase + j, vs = g % V_ST;
+        if (!mbar_wait(&v_full[vs], (g / V_ST) & 1, a.err, 16)) return false;
+        if (!mbar_wait(&p_full[x], n_pv[x] & 1, a.err, 15)) return false;
+        tc_fence_after();
+        // P [128 rows][128 keys] in tensor memory, two keys per column, each softmax warpgroup's 64 keys at the
+        // start of its share of S; V [128 keys][HD] MN-major
+        const uint32_t o = tmem_o + (uint32_t)(qx * HD), p = tmem + (uint32_t)(x * KT);
 #pragma unroll
-          for (int kk = 0; kk < KT / 16; ++kk) {
-            const uint32_t v_addr = smem_u32(sV + s * K_BYTES + (kk * 16) * 128);
-            const uint32_t p_col = (uint32_t)(((kk * 16) / KPT) * KPT + ((kk * 16) % KPT) / 2);
-            umma_f16_ts(o, p + p_col, umma_desc_mn(v_addr, HALF_BYTES), idesc_pv, (kk > 0 || j > 0) ? 1u : 0u);
-          }
-          umma_commit(&pv_full[g & 1]);
-          umma_commit(&v_empty[s]);
-          ++pv_issued;
+        for (int kk = 0; kk < KT / 16; ++kk) {
+          const uint32_t v_addr = smem_u32(sV + vs * K_BYTES + (kk * 16) * 128);
+          const uint32_t p_col = (uint32_t)(((kk * 16) / 64) * 64 + ((kk * 16) % 64) / 2);
+          umma_f16_ts(o, p + p_col, umma_desc_mn(v_addr, HALF_BYTES), idesc_pv, (kk > 0 || j > 0) ? 1u : 0u);
         }
+        umma_commit(&pv_done[x]);
+        ++n_pv[x];
+        if (qx == 1 || t.n_b == 0) umma_commit(&v_empty[vs]);
+        return true;
+      };
+      bool ok = true;
+      while (ok && walk.next(a, t)) {
+        ok = mbar_wait(&q_full[0], loads[0] & 1, a.err, 12);
+        ++loads[0];
+        if (!PAIRED) {
+          // One query tile an item: its S takes the two S buffers in turn (by the running count of key
+          // tiles), so that S of the next keys is computed while the softmax of these runs.
+          if (ok) ok = qk(kbase & 1, 0, 0, t.n_a == 1);
+          for (int j = 0; j < t.n_a && ok; ++j) {
+            if (j + 1 < t.n_a) ok = qk((kbase + j + 1) & 1, 0, j + 1, j + 2 == t.n_a);
+            if (ok) ok = pv((kbase + j) & 1, 0, j);
+          }
+          kbase += t.n_a;
+          continue;
+        }
+        if (ok) ok = qk(0, 0, 0, t.n_a == 1);
+        if (ok && t.n_b > 0) {
+          ok = mbar_wait(&q_full[1], loads[1] & 1, a.err, 12);
+          ++loads[1];
+          if (ok) ok = qk(1, 1, 0, t.n_b == 1);
+        }
+        const int n = t.n_b > t.n_a ? t.n_b : t.n_a;
+        for (int j = 0; j < n && ok; ++j) {
+          if (j < t.n_a) {
+            ok = pv(0, 0, j);
+            if (ok && j + 1 < t.n_a) ok = qk(0, 0, j + 1, j + 2 == t.n_a);
+          }
+          if (ok && j < t.n_b) {
+            ok = pv(1, 1, j);
+            if (ok && j + 1 < t.n_b) ok = qk(1, 1, j + 1, j + 2 == t.n_b);
+          }
+        }
+        kbase += n;
       }
     }
-  } else {
-    // softmax: thread = (query row, share of the tile's keys)
+  } else if (warp >= 4) {
+    // softmax: thread = (query row of tile x, half of the tile's keys)
+    constexpr int KPT = KT / 2;                        // keys of a tile per thread
+    constexpr int OPT = HD / 2;                        // output columns per thread
+    const int x = (warp - 4) >> 3;
+    const int wg = ((warp - 4) >> 2) & 1;              // which half of the keys and of the output columns
     const int qd = warp & 3;                           // the quarter of tensor memory's lanes this warp may touch
-    const int wg = (warp - 2) >> 2;                    // which share of the keys and of the output columns
     const int r = qd * 32 + lane;
     const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
-    bf16* mx_x = (bf16*)(xchg + qd * 256);
-    float* l_x = (float*)(xchg + qd * 256);
-    int g = 0;
+    const uint32_t o_addr = tmem_o + lane_base + (uint32_t)(x * HD + wg * OPT);
+    bf16* mx_x = (bf16*)(xchg + (x * 4 + qd) * 256);
+    float* l_x = (float*)(xchg + (x * 4 + qd) * 256);
+    const int bar_id = 1 + x * 4 + qd;
+    int n_t = 0;                                       // this tile's key tiles so far: its barriers' phases
     bool ok = true;
     // A wait that gives up makes the whole warp skip the rest of its work, but not the meetings with
-    // its partner warps: those are kept to the end, so that nobody waits at a barrier for ever.
-    for (int it = 0; walk.next(a, t); ++it) {
-      const int row_in_seg = t.tile0 + r;
+    // its partner warp: those are kept to the end, so that nobody waits at a barrier for ever.
+    while (walk.next(a, t)) {
+      const int n = x ? t.n_b : t.n_a;               // without pairs tile B's warps have nothing to do
+      if (n == 0) continue;
+      const int row_in_seg = t.tile0 + x * QT + r;
       const int hi = row_in_seg < t.qlen ? t.pos0 + row_in_seg : -1;
       const int lo = (a.window > 0 && hi - a.window + 1 > 0) ? hi - a.window + 1 : 0;
-      const uint32_t o_addr = tmem_o + lane_base + (uint32_t)((it & 1) * HD + wg * OPT);
       float m_ref = -INFINITY, l = 0.f;
-      for (int j = 0; j < t.n_tiles; ++j, ++g) {
-        const int s = g & 1;
+      for (int j = 0; j < n; ++j, ++n_t) {
         const int key_base = (t.tile_begin + j) * KT + wg * KPT;
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[s], (g >> 1) & 1, a.err, 17));
-        float mx = -INFINITY;
-        uint32_t sv[KPT];                                  // this thread's part of the row of S, read once
         const bool all_visible = key_base >= lo && key_base + KPT - 1 <= hi;   // no mask needed in this part
-        const uint32_t s_addr = tmem + lane_base + (uint32_t)(s * KT + wg * KPT);
+        // with pairs this tile has S buffer x to itself; a tile alone takes the two buffers in turn
+        const int buf = PAIRED ? x : (n_t & 1);
+        const uint32_t phase = PAIRED ? (uint32_t)(n_t & 1) : (uint32_t)((n_t >> 1) & 1);
+        const uint32_t s_addr = tmem + lane_base + (uint32_t)(buf * KT + wg * KPT);
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[buf], phase, a.err, 17));
+        // first pass over this thread's part of the row of S: its maximum
+        float mx = -INFINITY;
         if (ok) {
           tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < KPT; c += 32) tmem_ld32(s_addr + c, sv + c);
+          uint32_t sv[KPT];
+          tmem_ld32(s_addr, sv);
+          tmem_ld32(s_addr + 32, sv + 32);
           tmem_wait_ld();
           if (all_visible) {
-            // four independent chains: one chain of KPT dependent maxima would cost more than the loads did
+            // four independent chains: one chain of dependent maxima would cost more than the loads did
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int i = 0; i < KPT; i += 4) {
@@ -316,17 +373,15 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
           }
           mx *= a.scale_log2;                            // the scale is positive: max commutes with it
         }
-        if (WGS > 1) {
-          // The threads of a row agree on one value: each rounds its maximum up to bfloat16, leaves it
-          // for the others and takes the largest.  (The reference maximum need not be the exact one:
+        {
+          // The two threads of a row agree on one value: each rounds its maximum up to bfloat16, leaves
+          // it for the other and takes the larger.  (The reference maximum need not be the exact one:
           // any common value at or above the true maximum less 2^RESCALE_STEP serves.)
           const bf16 mine = __float2bfloat16_ru(mx);
-          bf16* slot = mx_x + (g & 1) * (WGS * 32);
+          bf16* slot = mx_x + (n_t & 1) * 64;
           slot[wg * 32 + lane] = mine;
-          named_barrier(1 + qd, 32 * WGS);
-          mx = __bfloat162float(mine);
-#pragma unroll
-          for (int w = 0; w < WGS; ++w) mx = fmaxf(mx, __bfloat162float(slot[w * 32 + lane]));
+          named_barrier(bar_id, 64);
+          mx = fmaxf(__bfloat162float(mine), __bfloat162float(slot[(wg ^ 1) * 32 + lane]));
         }
         if (!ok) continue;
         float corr = 1.f;
@@ -335,44 +390,17 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
           m_ref = mx;
         }
         l *= corr;
-        float sum = 0.f;
-        const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-        uint32_t w[KPT / 2];
-#pragma unroll
-        for (int c = 0; c < KPT; c += 64) {
-          if (all_visible) {                             // most tiles: no mask, two instructions per score
-            float s4[4] = {0.f, 0.f, 0.f, 0.f};          // the row sum in four chains, added in a fixed order
-#pragma unroll
-            for (int i = 0; i < 64; i += 2) {
-              const float e0 = fast_exp2(fmaf(__uint_as_float(sv[c + i]), a.scale_log2, neg_m));
-              const float e1 = fast_exp2(fmaf(__uint_as_float(sv[c + i + 1]), a.scale_log2, neg_m));
-              s4[(i >> 1) & 3] += e0 + e1;
-              w[(c + i) >> 1] = pack2_bf16(e0, e1);
-            }
-            sum += (s4[0] + s4[1]) + (s4[2] + s4[3]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 64; i += 2) {
-              float e[2];
-#pragma unroll
-              for (int x = 0; x < 2; ++x) {
-                const int key = key_base + c + i + x;
-                e[x] = (key >= lo && key <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c + i + x]), a.scale_log2, neg_m)) : 0.f;
-              }
-              sum += e[0] + e[1];
-              w[(c + i) >> 1] = pack2_bf16(e[0], e[1]);
-            }
-          }
-        }
-        l += sum;
         if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-          // Some row of this warp moves its reference: once the product of the tile before has come
-          // to rest, scale this thread's columns of the warp's rows of O (by 1 where nothing moved);
-          // the partner warps decide alike, from the same values.
-          ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[(g - 1) & 1], ((g - 1) >> 1) & 1, a.err, 18));
-          if (!ok) continue;
-          tc_fence_after();
-#pragma unroll
+          // Some row of this warp moves its reference: scale this thread's columns of the warp's rows
+          // of O (by 1 where nothing moved); the partner warp decides alike, from the same values.
+          // With pairs the product of the tile before has finished (this S was issued after it); a
+          // tile alone, whose S is computed ahead, waits for it.
+          if (!PAIRED) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(n_t - 1) & 1], (uint32_t)(((n_t - 1) >> 1) & 1), a.err, 18));
+            if (!ok) continue;
+            tc_fence_after();
+          }
+#pragma unroll 1
           for (int c = 0; c < OPT; c += 32) {
             uint32_t v[32];
             tmem_ld32(o_addr + c, v);
@@ -382,33 +410,65 @@ __global__ void __launch_bounds__(64 + 128 * WGS) attn_prefill_tc_kernel(const _
             tmem_st32(o_addr + c, v);
           }
         }
-        // P over the first half of this thread's own columns of S (all of which it has read)
+        // second pass, 32 columns at a time:
+        // the exponentials, as P over the first half of this thread's columns (a store overwrites
+        // only columns that have been read), and their sum
+        const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+        float sum = 0.f;
 #pragma unroll
-        for (int c = 0; c < KPT; c += 64) tmem_st32(s_addr + (uint32_t)(c >> 1), w + (c >> 1));
+        for (int c = 0; c < KPT; c += 32) {
+          uint32_t sv[32], w[16];
+          tmem_ld32(s_addr + c, sv);
+          tmem_wait_ld();
+          if (all_visible) {                             // most tiles: no mask, two instructions per score
+            float s4[4] = {0.f, 0.f, 0.f, 0.f};          // the row sum in four chains, added in a fixed order
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float e0 = fast_exp2(fmaf(__uint_as_float(sv[i]), a.scale_log2, neg_m));
+              const float e1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), a.scale_log2, neg_m));
+              s4[(i >> 1) & 3] += e0 + e1;
+              w[i >> 1] = pack2_bf16(e0, e1);
+            }
+            sum += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float e[2];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const int key = key_base + c + i + u;
+                e[u] = (key >= lo && key <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[i + u]), a.scale_log2, neg_m)) : 0.f;
+              }
+              sum += e[0] + e[1];
+              w[i >> 1] = pack2_bf16(e[0], e[1]);
+            }
+          }
+          tmem_st16(s_addr + (uint32_t)(c >> 1), w);
+        }
+        l += sum;
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&p_full[s]);
+        mbar_arrive(&p_full[buf]);
       }
-      if (WGS > 1) {
-        // the row's sum: every thread's part, added in the same order by all of them.  A barrier
-        // first (the maxima of the last two tiles lie in the bytes the sums go to) and one after
-        // (the next item's maxima go to the same bytes).
-        named_barrier(1 + qd, 32 * WGS);
+      {
+        // the row's sum: both threads' parts, added in the same order by both.  A barrier first (the
+        // maxima of the last two tiles lie in the bytes the sums go to) and one after (the next
+        // item's maxima go to the same bytes).
+        named_barrier(bar_id, 64);
         l_x[wg * 32 + lane] = l;
-        named_barrier(1 + qd, 32 * WGS);
-        l = 0.f;
-#pragma unroll
-        for (int w = 0; w < WGS; ++w) l += l_x[w * 32 + lane];
-        named_barrier(1 + qd, 32 * WGS);
+        named_barrier(bar_id, 64);
+        l = l_x[lane] + l_x[32 + lane];
+        named_barrier(bar_id, 64);
       }
       if (ok) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&pv_full[(g - 1) & 1], ((g - 1) >> 1) & 1, a.err, 20));
+        ok = PAIRED ? __all_sync(0xffffffffu, mbar_wait(&pv_done[x], (uint32_t)((n_t - 1) & 1), a.err, 20))
+                      : __all_sync(0xffffffffu, mbar_wait(&pv_done[(n_t - 1) & 1], (uint32_t)(((n_t - 1) >> 1) & 1), a.err, 20));
         tc_fence_after();
         // every lane takes part in the loads (they are warp-wide); only rows of the segment are stored
         const bool store = ok && row_in_seg < t.qlen;
         const float inv = store ? 1.f / l : 0.f;
         bf16* orow = a.out + (size_t)(t.q0 + (store ? row_in_seg : 0)) * a.ld_out + (size_t)t.h * HD + wg * OPT;
-#pragma unroll
+#pragma unroll 1
         for (int c = 0; c < OPT; c += 32) {
           uint32_t v[32];
           tmem_ld32(o_addr + c, v);
@@ -443,13 +503,13 @@ int device_sms() {
   return sms;
 }
 
-template <int HD>
+template <int HD, bool PAIRED>
 int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const AttnArgs& args, cudaStream_t st) {
-  // Q, the ring of keys and values, 256 bytes of barriers, 1 KB for what a row's threads exchange, 1 KB to align
-  constexpr int smem = QT * HD * 2 + 2 * KV_ST * KT * HD * 2 + 256 + 1024 + 1024;
+  // two Q tiles, the rings of keys and values, 256 bytes of barriers, 2 KB for what a row's threads exchange, 1 KB to align
+  constexpr int smem = 2 * QT * HD * 2 + (K_ST + V_ST) * KT * HD * 2 + 256 + 2048 + 1024;
   static_assert(smem <= 227 * 1024, "more shared memory than a CTA can have");
   static bool configured = false;
-  auto kernel = attn_prefill_tc_kernel<HD, SOFTMAX_WGS>;
+  auto kernel = attn_prefill_tc_kernel<HD, PAIRED>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
@@ -457,7 +517,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const AttnArgs& args, 
   }
   // one CTA per SM, or one per item when there are fewer
   const int ctas = args.items < device_sms() ? args.items : device_sms();
-  return qv_launch(kernel, dim3(ctas), dim3(64 + 128 * SOFTMAX_WGS), (size_t)smem, st, mq, mkv, args);
+  return qv_launch(kernel, dim3(ctas), dim3(ATTN_THREADS), (size_t)smem, st, mq, mkv, args);
 }
 
 }  // namespace
@@ -472,8 +532,11 @@ extern "C" int qv_attn_prefill_tc(void* out, int ld_out, const void* q, int ld_q
   if ((hd != 64 && hd != 128) || Hkv <= 0 || H % Hkv || page % 16 || (ld_q & 7) || (ld_out & 7) || ((uintptr_t)q & 15) ||
       ((uintptr_t)cache & 15) || ((uintptr_t)out & 15))
     return QV_ERR_UNSUPPORTED;
+  // Two query tiles an item (their softmax warps take turns), unless that leaves SMs without an item
   const long long q_tiles = (max_q_len + QT - 1) / QT;
-  if ((long long)H * S * q_tiles > (1LL << 30)) return QV_ERR_TOO_LARGE;
+  const int paired = (long long)H * S * ((q_tiles + 1) / 2) >= device_sms() ? 1 : 0;
+  const long long q_pairs = paired ? (q_tiles + 1) / 2 : q_tiles;
+  if ((long long)H * S * q_pairs > (1LL << 30)) return QV_ERR_TOO_LARGE;
   CUtensorMap mq, mkv;
   if (!make_map(&mq, q, T, H * hd, ld_q, QT)) return QV_ERR_UNSUPPORTED;
   if (!make_map(&mkv, cache, cache_pages * 2 * Hkv * page, hd, hd, 16)) return QV_ERR_UNSUPPORTED;
@@ -481,7 +544,7 @@ extern "C" int qv_attn_prefill_tc(void* out, int ld_out, const void* q, int ld_q
   a.out = (bf16*)out; a.seg_q_start = seg_q_start; a.seg_pos0 = seg_pos0; a.block_table = block_table; a.err = err;
   a.ld_out = ld_out; a.max_blocks = max_blocks; a.H = H; a.Hkv = Hkv; a.page = page; a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f;
-  a.segments = S; a.q_tiles = (int)q_tiles; a.items = (int)(H * S * q_tiles);
-  if (hd == 128) return launch<128>(mq, mkv, a, (cudaStream_t)stream);
-  return launch<64>(mq, mkv, a, (cudaStream_t)stream);
+  a.segments = S; a.q_pairs = (int)q_pairs; a.items = (int)(H * S * q_pairs); a.paired = paired;
+  if (hd == 128) return paired ? launch<128, true>(mq, mkv, a, (cudaStream_t)stream) : launch<128, false>(mq, mkv, a, (cudaStream_t)stream);
+  return paired ? launch<64, true>(mq, mkv, a, (cudaStream_t)stream) : launch<64, false>(mq, mkv, a, (cudaStream_t)stream);
 }
