@@ -340,8 +340,13 @@ def test_attention_bf16_refuses_what_it_cannot_do():
 
 
 @pytest.mark.parametrize("H,Hkv,hd,page,window", [(8, 2, 64, 16, 0), (32, 8, 128, 16, 0), (16, 1, 128, 16, 0), (4, 2, 64, 16, 37),
-                                                  (12, 4, 128, 64, 0), (6, 3, 128, 32, 150)])
+                                                  (12, 4, 128, 64, 0), (6, 3, 128, 32, 150), (32, 8, 64, 16, 0), (32, 4, 128, 16, 200),
+                                                  (40, 40, 64, 32, 90)])
 def test_attention_prefill_tcgen05(H, Hkv, hd, page, window):
+    """Segments of unequal lengths, some starting deep in their request.  With few heads the launch has fewer
+    work items than SMs and takes query tiles one by one; with 32 or 40 heads it takes them in pairs (the
+    300-row and 129-row segments then end in a pair with one tile only, and rows of other segments lie in the
+    tiles' unused halves)."""
     d = _segments([(70, 70), (1, 33), (300, 420), (2, 2), (128, 128), (129, 257), (16, 48), (1, 1)], H, Hkv, hd, page, seed=91, window=window)
     out = torch.full_like(d["q"], float("nan"))
     assert ops.attention_prefill_tc(out, d["q"], d["cache"], d["qstart"], d["pos0"], d["bt"], d["S"], d["max_q"], H, Hkv, hd,
@@ -401,7 +406,8 @@ def test_attention_decode_bf16_at_8192_keys(H, Hkv, hd, variant):
 
 
 @pytest.mark.parametrize("H,Hkv,hd,lens", [(32, 8, 128, [(2048, 2048)]), (8, 2, 128, [(2048, 4096), (100, 100)]),
-                                           (8, 2, 64, [(2048, 2048), (1, 700)])])
+                                           (8, 2, 64, [(2048, 2048), (1, 700)]), (32, 8, 64, [(2048, 2048)]),
+                                           (16, 4, 128, [(1920, 4096), (700, 700)])])
 def test_attention_prefill_tcgen05_at_2048_tokens(H, Hkv, hd, lens):
     """A whole 2,048-token prompt (the benchmark's prefill), and a 2,048-token portion that follows
     2,048 cached tokens, against float64."""
