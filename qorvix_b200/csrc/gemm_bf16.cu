@@ -464,12 +464,60 @@ __device__ __forceinline__ void rope_store_row(const RopeArgs& ra, bf16* C, int 
 }
 
 // ---------------------------------------------------------------- many tokens: persistent kernel
-// One CTA per SM walks over 128 x BN output tiles (tile = blockIdx.x, + gridDim.x, ...; token tiles
-// fastest, so that CTAs running at the same time share a weight tile in L2).  The accumulator is
-// double-buffered in tensor memory (2 x BN columns): while the four epilogue warps drain tile i,
-// the MMA warp already accumulates tile i+1, and the TMA warp runs ahead of both through the
-// shared-memory ring.
-template <int BN, int STAGES, typename TC, bool SWIGLU, bool ROPE = false>
+// One CTA per SM; tiles go round the CTAs (tile = blockIdx.x, + gridDim.x, ...; token tiles fastest, so
+// that CTAs running at the same time share a weight tile in L2).  A product with fewer tiles than SMs
+// (a few hundred tokens times a narrow weight matrix) would leave SMs idle and pay one CTA's whole walk
+// along K; there the tiles are shared: their k blocks, tile by tile, are cut into equal contiguous
+// shares, one per SM.  A share usually begins inside one tile and ends inside the next.  The CTA that
+// has a tile's first k blocks owns the tile; a CTA that has only later k blocks of it leaves its sums
+// (float32, from tensor memory) in its slot of a workspace and raises its flag; the owner waits for
+// the flags of the CTAs after it (they did that work first of all, while the owner did its own part),
+// adds their sums into its accumulator in tensor memory, in CTA order, and runs the epilogue.
+// The accumulator is double-buffered in tensor memory (2 x BN columns): while the four epilogue
+// warps drain one piece of work, the MMA warp already accumulates the next, and the TMA warp runs
+// ahead of both through the shared-memory ring.
+struct Segment {
+  int tile, kb0, kb1;                                // k blocks [kb0, kb1) of a tile
+};
+template <bool SHARED>
+struct Share {                                       // a CTA's work: a run of k-block units of the shared tiles, or whole tiles
+  long long u, end;
+  int num_kb, next_tile, stride, total_tiles;
+  __device__ __forceinline__ Share(int cta, int ctas, int tiles, int kbs) {
+    const long long units = SHARED ? (long long)tiles * kbs : 0;
+    u = units * cta / ctas;
+    end = units * (cta + 1) / ctas;
+    num_kb = kbs;
+    next_tile = SHARED ? tiles : cta;
+    stride = ctas;
+    total_tiles = tiles;
+  }
+  __device__ __forceinline__ bool next(Segment& sg) {
+    if (SHARED) {
+      if (u >= end) return false;
+      sg.tile = (int)(u / num_kb);
+      sg.kb0 = (int)(u - (long long)sg.tile * num_kb);
+      const long long left = end - u;
+      const int room = num_kb - sg.kb0;
+      sg.kb1 = sg.kb0 + (int)(left < room ? left : room);
+      u += sg.kb1 - sg.kb0;
+      return true;
+    }
+    if (next_tile >= total_tiles) return false;
+    sg.tile = next_tile;
+    sg.kb0 = 0;
+    sg.kb1 = num_kb;
+    next_tile += stride;
+    return true;
+  }
+};
+
+#define SK_SLOT_FLOATS (BM * 256)                    // a CTA's slot in the workspace: one 128 x 256 accumulator
+// where a CTA leaves the sums of a tile it only did part of (one slot per CTA), and the words that say they are there
+__device__ float* d_split_ws = nullptr;
+__device__ int* d_split_flags = nullptr;
+
+template <int BN, int STAGES, typename TC, bool SWIGLU, bool ROPE = false, bool SHARED = false>
 __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                  const __grid_constant__ CUtensorMap map_w,
                                                                  const GemmArgs args, const RopeArgs rope) {
@@ -491,6 +539,7 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
   const int total_tiles = tiles_m * tiles_n;
   const int num_kb = (args.K + BK - 1) / BK;
+  const int ctas = (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -534,28 +583,29 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
       };
       // the first stages' weight tiles do not depend on the kernel ahead
       int it = 0;
-      bool first = true;
-      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * bn;
-        int kb = 0;
+      bool first = true, ok = true;
+      Share<SHARED> sh(blockIdx.x, ctas, total_tiles, num_kb);
+      Segment sg;
+      while (ok && sh.next(sg)) {
+        const int m0 = (sg.tile % tiles_m) * BM, n0 = (sg.tile / tiles_m) * bn;
+        int kb = sg.kb0;
         if (first) {
-          const int pre = num_kb < STAGES ? num_kb : STAGES;
-          for (int k = 0; k < pre; ++k) load_w(k, k, n0);
+          const int len = sg.kb1 - sg.kb0;
+          const int pre = len < STAGES ? len : STAGES;
+          for (int k = 0; k < pre; ++k) load_w(k, sg.kb0 + k, n0);
           pdl_wait();
-          for (int k = 0; k < pre; ++k) tma_load_2d(tiles + k * STAGE_BYTES, &map_x, &full[k], k * BK, m0);
-          kb = pre;
+          for (int k = 0; k < pre; ++k) tma_load_2d(tiles + k * STAGE_BYTES, &map_x, &full[k], (sg.kb0 + k) * BK, m0);
+          kb = sg.kb0 + pre;
           it = pre;
           first = false;
         }
-        bool ok = true;
-        for (; kb < num_kb; ++kb, ++it) {
+        for (; kb < sg.kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, args.err, 1)) { ok = false; break; }
           load_w(s, kb, n0);
           tma_load_2d(tiles + s * STAGE_BYTES, &map_x, &full[s], kb * BK, m0);
         }
-        if (!ok) break;
       }
       if (first) pdl_wait();
     }
@@ -564,14 +614,16 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
       const uint32_t idesc = umma_idesc(BM, bn);
       int it = 0, local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      Share<SHARED> sh(blockIdx.x, ctas, total_tiles, num_kb);
+      Segment sg;
+      while (ok && sh.next(sg)) {
         const int b = local & 1;
-        // the epilogue must have drained this accumulator (two tiles ago)
+        // the epilogue must have drained this accumulator (two pieces of work ago)
         ok = mbar_wait(&acc_empty[b], ((local >> 1) & 1) ^ 1, args.err, 4);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           ok = mbar_wait(&full[s], ph, args.err, 2);
@@ -581,41 +633,130 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
           const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk)
-            umma_f16(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            umma_f16(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (kb > sg.kb0 || kk > 0) ? 1u : 0u);
           umma_commit(&empty[s]);
         }
         umma_commit(&acc_full[b]);
+        ++local;
       }
     }
   } else {
-    pdl_wait();                                      // C may still be in use by the kernel ahead
+    pdl_wait();                                      // C (and the workspace) may still be in use by the kernel ahead
     const int q = warp & 3;
     TC* C = (TC*)args.C;
     int local = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+    const long long units = (long long)total_tiles * num_kb;       // shared: all tiles are
+    float* const sk_ws = SHARED ? d_split_ws : nullptr;
+    int* const sk_flags = SHARED ? d_split_flags : nullptr;
+    Share<SHARED> sh(blockIdx.x, ctas, total_tiles, num_kb);
+    Segment sg;
+    while (sh.next(sg)) {
       const int b = local & 1;
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * bn;
+      const int m0 = (sg.tile % tiles_m) * BM, n0 = (sg.tile / tiles_m) * bn;
       // every thread polls: the arrivals below need all 128 of them, timed out or not
-      const bool ok = mbar_wait(&acc_full[b], (local >> 1) & 1, args.err, 3);
+      bool ok = mbar_wait(&acc_full[b], (local >> 1) & 1, args.err, 3);
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
+      const int row_in_tile = q * 32 + lane;
+      const int row = m0 + row_in_tile;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN);
-      if (ok && ROPE) {
-        if (rope.hd == 128) rope_store_row<128>(rope, (bf16*)args.C, args.ldc, taddr, row, row < M, n0, bn, N);
-        else rope_store_row<64>(rope, (bf16*)args.C, args.ldc, taddr, row, row < M, n0, bn, N);
-      } else if (ok) {
+      if (SHARED && ok && sg.kb0 > 0) {
+        // only later k blocks of the tile are this CTA's: its sums go to its slot, for the tile's owner
+        // (as [32-column chunk][float4 of the chunk][row], so that a warp's stores and the owner's loads are contiguous)
+        float4* slot = (float4*)(sk_ws + (size_t)blockIdx.x * SK_SLOT_FLOATS) + row_in_tile;
 #pragma unroll 1
         for (int c0 = 0; c0 < bn; c0 += 32) {
           uint32_t r[32];
-          tmem_ld32(taddr + c0, r);                  // a last chunk of 16 columns reads on into unused ones
+          tmem_ld32(taddr + c0, r);
           tmem_wait_ld();
-          if (row >= M || n0 + c0 >= N) continue;
-          store_chunk<TC, SWIGLU>(C, args.ldc, row, n0 + c0, (N - (n0 + c0)) < (bn - c0) ? (N - (n0 + c0)) : (bn - c0), r);
+          float4* dst = slot + (size_t)(c0 >> 5) * 8 * BM;
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            dst[v * BM] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+        }
+        __threadfence();                             // the sums before the flag
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (q == 0 && lane == 0) atomicExch(sk_flags + blockIdx.x, 1);
+      } else if (ok) {
+        if (SHARED && sg.kb1 < num_kb) {
+          // The tile's later k blocks are the following CTAs' (every CTA has some: the host shares tiles only
+          // then).  They did that work first of all, while this CTA did its own part, so the wait for
+          // their flags is short; it is bounded like every other.  Their sums are added to this
+          // accumulator in tensor memory, chunk by chunk and in CTA order, before the epilogue reads it.
+          int n = 0;
+          for (long long at = units * (blockIdx.x + 1) / ctas; at < (long long)(sg.tile + 1) * num_kb; at = units * (blockIdx.x + 1 + n) / ctas) ++n;
+          for (int j = 0; j < n; ++j) {
+            volatile int* flag = sk_flags + blockIdx.x + 1 + j;
+            uint32_t spins = 0;
+            while (*flag == 0 && ++spins < WAIT_LIMIT) {}
+            if (*flag == 0) ok = false;
+          }
+          {  // all 128 threads go on, or none: one that gave up takes the others with it
+            uint32_t seen = ok, all_seen;
+            asm volatile("{ .reg .pred p, q; setp.ne.u32 p, %1, 0; bar.red.and.pred q, 1, 128, p; selp.u32 %0, 1, 0, q; }"
+                         : "=r"(all_seen) : "r"(seen) : "memory");
+            ok = all_seen != 0;
+            if (!ok && q == 0 && lane == 0) atomicExch(args.err, 7);
+          }
+          if (ok) {
+            __threadfence();                         // the flags before the sums
+            const float4* first = (const float4*)(sk_ws + (size_t)(blockIdx.x + 1) * SK_SLOT_FLOATS) + row_in_tile;
+            const int items = ((bn + 31) >> 5) * n;  // (chunk, contributor) pairs, contributors fastest
+            // two pairs' loads are in flight while a third is added: the trip to L2 is what this loop waits for
+            auto issue = [&](int i, float4* p) {
+              const int ch = i / n, j = i - ch * n;
+              const float4* src = first + (size_t)j * (SK_SLOT_FLOATS / 4) + (size_t)ch * 8 * BM;
+#pragma unroll
+              for (int v = 0; v < 8; ++v) p[v] = __ldcg(src + v * BM);
+            };
+            uint32_t r[32];
+            auto consume = [&](int i, const float4* p) {
+              const int ch = i / n, j = i - ch * n;
+              if (j == 0) { tmem_ld32(taddr + ch * 32, r); tmem_wait_ld(); }
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                r[4 * v] = __float_as_uint(__uint_as_float(r[4 * v]) + p[v].x);
+                r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + p[v].y);
+                r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) + p[v].z);
+                r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) + p[v].w);
+              }
+              if (j == n - 1) tmem_st32(taddr + ch * 32, r);
+            };
+            float4 pa[8], pb[8], pc[8];
+            issue(0, pa);
+            if (1 < items) issue(1, pb);
+#pragma unroll 1
+            for (int i = 0; i < items; i += 3) {
+              if (i + 2 < items) issue(i + 2, pc);
+              consume(i, pa);
+              if (i + 3 < items) issue(i + 3, pa);
+              if (i + 1 < items) consume(i + 1, pb);
+              if (i + 4 < items) issue(i + 4, pb);
+              if (i + 2 < items) consume(i + 2, pc);
+            }
+            tmem_wait_st();
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");      // every thread has read the slots: their flags go down for the next launch
+          if (q == 0 && lane == 0)
+            for (int j = 0; j < n; ++j) atomicExch(sk_flags + blockIdx.x + 1 + j, 0);
+        }
+        if (ok && ROPE) {
+          if (rope.hd == 128) rope_store_row<128>(rope, (bf16*)args.C, args.ldc, taddr, row, row < M, n0, bn, N);
+          else rope_store_row<64>(rope, (bf16*)args.C, args.ldc, taddr, row, row < M, n0, bn, N);
+        } else if (ok) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < bn; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(taddr + c0, r);                  // a last chunk of 16 columns reads on into unused ones
+            tmem_wait_ld();
+            if (row >= M || n0 + c0 >= N) continue;
+            store_chunk<TC, SWIGLU>(C, args.ldc, row, n0 + c0, (N - (n0 + c0)) < (bn - c0) ? (N - (n0 + c0)) : (bn - c0), r);
+          }
         }
       }
       tc_fence_before();
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[b])) : "memory");
       if (!ok) break;
+      ++local;
     }
     tc_fence_before();
   }
@@ -652,23 +793,61 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mn, const GemmArgs& args, d
   return qv_launch_cluster(gemm_tc_kernel<BN, STAGES, TC, SWIGLU>, grid, dim3(192), (size_t)smem, st, dim3(1, 1, grid.z), mw, mn, args, norm);
 }
 
+float* g_split_ws = nullptr;             // see qv_gemm_bf16_set_split_workspace
+int* g_split_flags = nullptr;
+int g_split_ctas = 0;
+
+// Are the tiles of a product shared between the CTAs?  Where they fill at most three quarters of the
+// SMs, each tile is cut into no more than eight pieces, and a tile's walk along K is long (8,192 or
+// more): handing over and adding the partial sums costs ~10 us, which a shorter walk does not give back
+// (measured: 4096 x 14336 at 128 tokens 72 -> 36 us, at 384 tokens 76 -> 64 us; 4096 x 4096 at 256 tokens
+// 24 -> 34 us), nor do tiles of 256 columns, whose partial sums are twice as large (5120 x 13824 at 512
+// tokens 90 -> 98 us).
+bool share_tiles(int total_tiles, int num_kb, int bn) {
+  const int sms = device_sms();
+  return g_split_ws != nullptr && g_split_ctas >= sms && bn <= 128 && total_tiles * 4 <= sms * 3 && total_tiles * 8 >= sms && num_kb >= 128;
+}
+
+template <int BN, int STAGES, typename TC, bool SWIGLU, bool ROPE, bool SHARED>
+int launch_persistent_kernel(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& args, int ctas, cudaStream_t st, const RopeArgs& rope) {
+  constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  static bool configured = false;
+  auto kernel = gemm_tc_persistent_kernel<BN, STAGES, TC, SWIGLU, ROPE, SHARED>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return qv_launch(kernel, dim3(ctas), dim3(192), (size_t)smem, st, mx, mw, args, rope);
+}
+
 template <int BN, int STAGES, typename TC, bool SWIGLU, bool ROPE = false>
 int launch_persistent(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& args, int total_tiles, cudaStream_t st,
                       const RopeArgs& rope = RopeArgs()) {
-  constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
-  static bool configured = false;
-  static int sms = 0;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, TC, SWIGLU, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    sms = device_sms();
-    configured = true;
+  const int sms = device_sms();
+  // tiles are shared only by products with the plain epilogue (the narrow, long ones are output and down projections)
+  if (!SWIGLU && !ROPE && share_tiles(total_tiles, (args.K + BK - 1) / BK, args.bn)) {
+    return launch_persistent_kernel<BN, STAGES, TC, false, false, true>(mx, mw, args, sms, st, rope);
   }
-  const int ctas = total_tiles < sms ? total_tiles : sms;
-  return qv_launch(gemm_tc_persistent_kernel<BN, STAGES, TC, SWIGLU, ROPE>, dim3(ctas), dim3(192), (size_t)smem, st, mx, mw, args, rope);
+  return launch_persistent_kernel<BN, STAGES, TC, SWIGLU, ROPE, false>(mx, mw, args, total_tiles < sms ? total_tiles : sms, st, rope);
 }
 
 }  // namespace
+
+// The workspace through which CTAs of the persistent kernel hand partial sums of a shared tile to its
+// owner: `ctas` slots of 128 x 256 floats and `ctas` flag words that are zero (the kernel leaves them
+// zero).  It belongs to the caller, is used by every later product of many tokens that shares tiles and
+// must outlive them; such products must not run at the same time on different streams.  Null: tiles are
+// never shared.
+extern "C" void qv_gemm_bf16_set_split_workspace(float* slots, int* flags, int ctas) {
+  g_split_ws = slots;
+  g_split_flags = flags;
+  g_split_ctas = slots && flags ? ctas : 0;
+  // the kernels read the addresses from device words (set here, once; not on the launch path)
+  if (cudaMemcpyToSymbol(d_split_ws, &slots, sizeof(slots)) != cudaSuccess || cudaMemcpyToSymbol(d_split_flags, &flags, sizeof(flags)) != cudaSuccess)
+    g_split_ctas = 0;
+}
+extern "C" long long qv_gemm_bf16_split_slot_bytes() { return (long long)SK_SLOT_FLOATS * 4; }
 
 // Columns of the persistent kernel's tiles: 0 (default) chooses per product, else the given width
 // (a multiple of 16, of 32 with the fused activation, at most 256; for comparison and tests).
@@ -679,8 +858,9 @@ extern "C" void qv_gemm_bf16_set_prefill_bn(int v) { g_prefill_bn = v; }
 // columns beside its bn columns (measured: the shared-memory fill, not the MMA, sets the pace), so
 // the widest tile wins unless half-width tiles still fit in one wave of CTAs, which then finishes
 // sooner (4096 x 14336 at 512 tokens: 76.9 us at 128 columns, 88.1 us at 256).
-static int choose_tile_width(int tiles_m, int N, int step) {
+static int choose_tile_width(int tiles_m, int N, int K, int step) {
   (void)step;
+  (void)K;
   return tiles_m * ((N + 127) / 128) <= device_sms() ? 128 : 256;
 }
 
@@ -747,7 +927,7 @@ static int gemm_bf16_entry(void* C, const void* A, const void* W, const void* pa
   args.packed = (const uint8_t*)packed;
   args.rows_wide = M; args.rows_narrow = N; args.kblocks_per_split = total_kb; args.splits = 1;
   const int step = epilogue == 1 ? 32 : 16;
-  const int bn = g_prefill_bn > 0 ? g_prefill_bn : choose_tile_width((M + BM - 1) / BM, N, step);
+  const int bn = g_prefill_bn > 0 ? g_prefill_bn : choose_tile_width((M + BM - 1) / BM, N, K, step);
   // persistent kernel, 128 x bn tiles, accumulator double-buffered in tensor memory
   if (bn < step || bn > 256 || bn % step) return QV_ERR_UNSUPPORTED;
   args.bn = bn;
@@ -789,7 +969,7 @@ extern "C" int qv_gemm_bf16_qkv_rope(void* C, const void* A, const void* packed,
   ra.cache = (bf16*)cache; ra.table_rows = table_rows; ra.max_blocks = max_blocks;
   ra.H = H; ra.Hkv = Hkv; ra.hd = hd; ra.page_size = page_size;
   args.rows_wide = M; args.rows_narrow = N; args.kblocks_per_split = (K + BK - 1) / BK; args.splits = 1;
-  args.bn = g_prefill_bn > 0 ? g_prefill_bn : choose_tile_width((M + BM - 1) / BM, N, 16);
+  args.bn = g_prefill_bn > 0 ? g_prefill_bn : choose_tile_width((M + BM - 1) / BM, N, K, 16);
   if (args.bn > 256 || args.bn % hd) return QV_ERR_UNSUPPORTED;      // whole heads per tile
   CUtensorMap mx;
   if (!make_map(&mx, A, M, K, lda, BM)) return QV_ERR_UNSUPPORTED;

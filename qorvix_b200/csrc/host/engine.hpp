@@ -88,6 +88,17 @@ class Engine {
     cuda_check(cudaMalloc(&err_word_, sizeof(int)), "cudaMalloc");
     cuda_check(cudaMemsetAsync(err_word_, 0, sizeof(int), stream_), "cudaMemsetAsync");
     k_.attn_set_error_word(err_word_);
+    const char* share = getenv("QORVIX_SHARE_TILES");
+    if (dt_ == DT_BF16 && !(share && share[0] == '0')) {
+      // where CTAs of the many-token product hand partial sums of a shared tile to its owner: a slot and a flag per SM
+      int dev = 0, sms = 0;
+      cuda_check(cudaGetDevice(&dev), "cudaGetDevice");
+      cuda_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute");
+      cuda_check(cudaMalloc(&split_slots_, (size_t)sms * (size_t)k_.gemm_split_slot_bytes()), "cudaMalloc");
+      cuda_check(cudaMalloc(&split_flags_, (size_t)sms * sizeof(int)), "cudaMalloc");
+      cuda_check(cudaMemsetAsync(split_flags_, 0, (size_t)sms * sizeof(int), stream_), "cudaMemsetAsync");
+      k_.gemm_set_split_workspace(split_slots_, split_flags_, sms);
+    }
     page_ = opt.page_size;
     const long long pool_tokens = (opt.max_tokens + page_ - 1) / page_ * page_;
     const long long limit = desc_.max_position > 0 ? desc_.max_position : pool_tokens;
@@ -109,6 +120,7 @@ class Engine {
       if (g.second.graph) cudaGraphDestroy(g.second.graph);
       if (g.second.host) cudaFreeHost(g.second.host);
     }
+    if (split_slots_) { k_.gemm_set_split_workspace(nullptr, nullptr, 0); cudaFree(split_slots_); cudaFree(split_flags_); }
     for (void* p : owned_) cudaFree(p);
     for (auto& b : bufs_) if (b.second.ptr) cudaFree(b.second.ptr);
     if (pinned_) cudaFreeHost(pinned_);
@@ -273,6 +285,8 @@ class Engine {
   ModelW w_;
   cudaStream_t stream_ = nullptr;
   int* err_word_ = nullptr;
+  float* split_slots_ = nullptr;
+  int* split_flags_ = nullptr;
   int page_ = 16, num_pages_ = 0;
   long long max_model_len_ = 0;
   void* cache_ = nullptr;

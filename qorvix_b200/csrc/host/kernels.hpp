@@ -43,6 +43,8 @@ struct Kernels {
                          int, int, int, int, float, int*, void*) = nullptr;
   void (*attn_set_decode_variant)(int) = nullptr;
   void (*attn_set_error_word)(int*) = nullptr;
+  void (*gemm_set_split_workspace)(float*, int*, int) = nullptr;
+  long long (*gemm_split_slot_bytes)() = nullptr;
   int (*attn_decode_bf16)(void*, int, const void*, int, const void*, const int*, const int*, const int*, int, int, int, int, int, int, int,
                           float, int, float*, void*) = nullptr;
   // sampling
@@ -74,6 +76,7 @@ struct Kernels {
     QV_SYM(gb, gemm_bf16_tc, "qv_gemm_bf16_tc"); QV_SYM(gb, packed_weight_bytes, "qv_packed_weight_bytes");
     QV_SYM(gb, pack_weight_tiles, "qv_pack_weight_tiles"); QV_SYM(gb, gemm_bf16_packed, "qv_gemm_bf16_packed");
     QV_SYM(gb, gemm_bf16_qkv_rope, "qv_gemm_bf16_qkv_rope"); QV_SYM(gb, gemm_bf16_norm, "qv_gemm_bf16_norm");
+    QV_SYM(gb, gemm_set_split_workspace, "qv_gemm_bf16_set_split_workspace"); QV_SYM(gb, gemm_split_slot_bytes, "qv_gemm_bf16_split_slot_bytes");
     void* ag = open("attention_generic");
     QV_SYM(ag, attention_generic, "qv_attention_generic");
     void* ab = open("attention_bf16");

@@ -5,6 +5,7 @@ library kernel; a missing or unbuildable library raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -45,6 +46,8 @@ _ARGTYPES = {
     "qv_gemm_bf16_qkv_rope": [_V, _V, _V, _I, _I, _I, _I, _V, _V, _I, _V, _V, _V, _I, _V, _I, _I, _I, _I, _V],
     "qv_gemm_bf16_norm": [_V, _V, _V, _I, _I, _I, _I, _I, _I, _V, _I, _V, _I, _V, _V, _V, _I, _F, _F, _V],
     "qv_gemm_bf16_set_prefill_bn": [_I],
+    "qv_gemm_bf16_set_split_workspace": [_V, _V, _I],
+    "qv_gemm_bf16_split_slot_bytes": [],
     "qv_attention_generic": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V],
     "qv_attn_prefill_bf16": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V],
     "qv_attn_prefill_tc": [_V, _I, _V, _I, _I, _V, _L, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _F, _V, _V],
@@ -54,7 +57,7 @@ _ARGTYPES = {
     "qv_argmax": [_V, _V, _I, _I, _L, _V],
     "qv_sample": [_V, _V, _I, _I, _L, _V, _V, _V, _V, _V, _V, _I, _V, _V, _V, _V],
 }
-_RESTYPES = {"qv_error_string": ctypes.c_char_p, "qv_packed_weight_bytes": c_longlong}
+_RESTYPES = {"qv_error_string": ctypes.c_char_p, "qv_packed_weight_bytes": c_longlong, "qv_gemm_bf16_split_slot_bytes": c_longlong}
 _typed_libs = {}
 
 
@@ -234,6 +237,36 @@ def _tc_buffers(device):
     return st
 
 
+_split_registered = [None]      # the workspace the library knows (its address), 0 after it was told to share no tiles
+_split_enabled = [os.environ.get("QORVIX_SHARE_TILES", "1") != "0"]
+
+
+def _gemm_buffers(device):
+    """`_tc_buffers` plus, for the products: the workspace through which CTAs of the many-token
+    kernel hand the partial sums of a tile they share to its owner (one slot and one flag per SM),
+    registered with the library once; products run on one stream at a time."""
+    st = _tc_buffers(device)
+    if not _split_enabled[0]:
+        return st
+    if "split_slots" not in st:
+        ctas = sm_count()
+        st["split_slots"] = torch.empty(ctas * int(_lib("gemm_bf16").qv_gemm_bf16_split_slot_bytes()) // 4, dtype=torch.float32, device=device)
+        st["split_flags"] = torch.zeros(ctas, dtype=torch.int32, device=device)
+    key = st["split_slots"].data_ptr()
+    if _split_registered[0] != key:
+        _lib("gemm_bf16").qv_gemm_bf16_set_split_workspace(_ptr(st["split_slots"]), _ptr(st["split_flags"]), st["split_flags"].numel())
+        _split_registered[0] = key
+    return st
+
+
+def gemm_share_tiles(enabled: bool) -> None:
+    """Switches the sharing of tiles between CTAs of the many-token kernel off, or on again (for comparison)."""
+    _split_enabled[0] = bool(enabled)
+    if not enabled and _split_registered[0]:
+        _lib("gemm_bf16").qv_gemm_bf16_set_split_workspace(None, None, 0)
+        _split_registered[0] = 0
+
+
 def gemm_bf16_tc(c, a, w, force_splits: int = 0, swiglu: bool = False) -> bool:
     """c[M,N] (bf16 or f32) = a[M,K] @ w[N,K]^T on the tcgen05 tensor cores.  With `swiglu`, w holds
     gate and up rows interleaved in groups of 16 and c[M,N/2] = silu(gate) * up.  False when the
@@ -244,7 +277,7 @@ def gemm_bf16_tc(c, a, w, force_splits: int = 0, swiglu: bool = False) -> bool:
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
     assert c.shape == ((M, N // 2) if swiglu else (M, N))
     assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
-    st = _tc_buffers(a.device)
+    st = _gemm_buffers(a.device)
     rc = _lib("gemm_bf16").qv_gemm_bf16_tc(
         _ptr(c), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), dt_code(c.dtype),
         _ptr(st["err"]), force_splits, 1 if swiglu else 0, _stream())
@@ -272,7 +305,7 @@ def gemm_bf16_packed(c, a, packed, N: int, force_splits: int = 0, swiglu: bool =
     M, K = a.shape
     assert a.dtype == torch.bfloat16 and packed.dtype == torch.bfloat16
     assert c.shape == ((M, N // 2) if swiglu else (M, N)) and a.stride(1) == 1 and c.stride(1) == 1
-    st = _tc_buffers(a.device)
+    st = _gemm_buffers(a.device)
     rc = _lib("gemm_bf16").qv_gemm_bf16_packed(
         _ptr(c), _ptr(a), _ptr(packed), M, N, K, a.stride(0), c.stride(0), dt_code(c.dtype), _ptr(st["err"]),
         force_splits, 1 if swiglu else 0, _stream())
@@ -303,7 +336,7 @@ def gemm_bf16_norm(c, a, packed, N: int, swiglu: bool = False, residual=None, no
     if ssq_in is not None:
         assert ssq_in.dtype == torch.float32 and ssq_in.is_contiguous() and ssq_in.shape[1] == 64 and stream_width > 0
         tiles_in = ssq_in.shape[0]
-    st = _tc_buffers(a.device)
+    st = _gemm_buffers(a.device)
     rc = _lib("gemm_bf16").qv_gemm_bf16_norm(
         _ptr(c), _ptr(a), _ptr(packed), M, N, K, a.stride(0), c.stride(0), dt_code(c.dtype), _ptr(st["err"]),
         1 if swiglu else 0, _ptr(residual), residual.stride(0) if residual is not None else 0, _ptr(norm_weight),
@@ -355,7 +388,7 @@ def gemm_qkv_rope(qkv, x, packed, cache_layer, cos_sin, tok_pos, tok_seg, block_
     assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (2, Hkv, page, hd)
     assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
     _i32(tok_pos, "tok_pos"); _i32(tok_seg, "tok_seg"); _i32(block_table, "block_table")
-    st = _tc_buffers(x.device)
+    st = _gemm_buffers(x.device)
     rc = _lib("gemm_bf16").qv_gemm_bf16_qkv_rope(
         _ptr(qkv), _ptr(x), _ptr(packed), M, K, x.stride(0), qkv.stride(0), _ptr(st["err"]), _ptr(cos_sin),
         cos_sin.shape[0], _ptr(tok_pos), _ptr(tok_seg), _ptr(block_table), block_table.shape[-1], _ptr(cache_layer),

@@ -126,7 +126,8 @@ class NativeExecutor:
             return None
         first = model.blocks[0].mixer
         arr = (_Layer * len(layers))(*layers)
-        err = ops._tc_buffers(rt.device)["err"]
+        # the products' workspace is registered with their library here: whole steps never pass through ops' wrappers
+        err = (ops._gemm_buffers if rt.dtype == torch.bfloat16 else ops._tc_buffers)(rt.device)["err"]
         desc = _Model(dt=ops.dt_code(rt.dtype), d=model.spec.hidden_size, H=first.H, Hkv=first.Hkv, hd=first.hd, f=model.blocks[0].feed_forward.f,
                       V=model.spec.vocab_size, page=cache.page_size, rot=first.position.rotary_dim, table_rows=table.shape[0], sms=ops.sm_count(),
                       emb_dt=ops.dt_code(model.embedding.dtype), n_layers=len(layers), pad=0, eps=model.final_norm.eps, scale=first.scale,

@@ -139,6 +139,7 @@ def main() -> int:
     ap.add_argument("--ctx", type=int, default=1024)
     ap.add_argument("--prefill", type=int, default=2048)
     ap.add_argument("--only", default="", help="just the cases whose name contains this (e.g. prefill_attention, decode_attention, decode_o)")
+    ap.add_argument("--whole-tiles", action="store_true", help="many-token products without sharing tiles between CTAs (for comparison)")
     ap.add_argument("--hbm-gbs", type=float, default=6650.0)
     ap.add_argument("--bf16-tflops", type=float, default=1590.0)
     args = ap.parse_args()
@@ -147,6 +148,8 @@ def main() -> int:
     raw = json.load(open(args.config))
     cfg = lookup_architecture(architecture_of(raw)).config_from_dict(raw)
     peaks = {"hbm_gbs": args.hbm_gbs, "bf16_tflops": args.bf16_tflops}
+    if args.whole_tiles:
+        ops.gemm_share_tiles(False)
     for name, fig in headline_kernels(cfg, args.batch, args.ctx, args.prefill, peaks, only=args.only).items():
         print(f"{name:34s} {json.dumps(fig)}", flush=True)
     return 0

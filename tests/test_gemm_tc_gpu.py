@@ -34,6 +34,31 @@ def test_many_tokens(M, N, K, out_dtype):
     check(M, N, K, out_dtype)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(256, 4096, 14336), (130, 2560, 8192), (384, 2048, 16384), (200, 2000, 9000), (700, 1500, 8200),
+                                   (96, 4096, 14336), (512, 4096, 4096), (544, 5120, 5120)])
+def test_tiles_shared_between_ctas_give_the_sums_of_whole_tiles(M, N, K, out_dtype):
+    """A product with a long walk along K whose tiles fill at most three quarters of the SMs shares them (the
+    first six shapes; the last two are not shared): a CTA that has only later k blocks of a tile leaves its
+    float32 sums in the workspace, the tile's owner adds them to its own.  The
+    result stays within the product's tolerance, is the same on every launch (the flags come down again), and
+    equals the unshared product up to the rounding of a few float32 additions per element."""
+    check(M, N, K, out_dtype)
+    a, w = rnd(M, K, seed=3), rnd(N, K, seed=4, scale=0.05)
+    outs = []
+    for shared in (True, True, False):
+        ops.gemm_share_tiles(shared)
+        c = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+        assert ops.gemm_bf16_tc(c, a, w)
+        outs.append(c)
+    ops.gemm_share_tiles(True)
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    assert torch.equal(outs[0], outs[1])
+    whole = outs[2].double()
+    assert (outs[0].double() - whole).abs().max().item() <= (2e-5 if out_dtype == torch.float32 else 2e-2) * max(1.0, whole.abs().max().item())
+
+
 @pytest.mark.parametrize("bn", [16, 48, 112, 128, 144, 240, 256])
 @pytest.mark.parametrize("M,N,K", [(300, 1000, 520), (129, 272, 64), (512, 5120, 1024), (200, 336, 136)])
 def test_many_tokens_at_every_tile_width(M, N, K, bn):
