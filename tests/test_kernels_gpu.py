@@ -405,6 +405,35 @@ def test_attention_decode_bf16_at_8192_keys(H, Hkv, hd, variant):
         ops.attention_set_decode_variant(None)
 
 
+@pytest.mark.parametrize("variant", [0, 1])
+def test_attention_decode_bf16_at_32768_keys(variant):
+    """Single tokens over 32,768 and 9,000 cached keys (2,048 block-table entries a row) with the slice counts the
+    dispatcher picks for such a step; far keys in the first, a middle and the last page are made to dominate."""
+    H, Hkv, hd, page = 8, 2, 128, 16
+    d = _segments([(1, 32768), (1, 9000)], H, Hkv, hd, page, seed=777)
+    q = d["q"].view(2, H, hd)
+    for s_i, far, head in ((0, 3, 0), (0, 32767, 5), (1, 4500, 1)):
+        pages = d["bt"][s_i].tolist()
+        kvh = head // (H // Hkv)
+        d["cache"][pages[far // page], 0, kvh, far % page] = (q[s_i, head].float() * 6.0).to(torch.bfloat16)
+        d["cache"][pages[far // page], 1, kvh, far % page] = 50.0
+    ops.attention_set_decode_variant(variant)
+    try:
+        for splits in (ops.decode_splits(2, Hkv, 32768), ops.decode_splits(2, Hkv, 32768, known=False), 1):
+            out = torch.full_like(d["q"], float("nan"))
+            assert ops.attention_decode_bf16(out, d["q"], d["cache"], d["pos"], d["seg"], d["bt"], H, Hkv, hd, page, 0,
+                                             1.0 / math.sqrt(hd), splits)
+            ops.check_kernel_errors()
+            o = out.view(2, H, hd).float()
+            assert float(o[0, 0].min()) > 49.0 and float(o[0, 5].min()) > 49.0 and float(o[1, 1].min()) > 49.0, f"splits {splits}: a far key was missed"
+            untouched = torch.zeros(2, H, dtype=torch.bool)
+            untouched[1, 4:8] = True                                  # the only kv head without a planted key
+            ref = d["ref"].view(2, H, hd)
+            assert torch.allclose(out.view(2, H, hd).double().cpu()[untouched], ref[untouched], rtol=2e-2, atol=2e-2), f"splits {splits}"
+    finally:
+        ops.attention_set_decode_variant(None)
+
+
 @pytest.mark.parametrize("H,Hkv,hd,lens", [(32, 8, 128, [(2048, 2048)]), (8, 2, 128, [(2048, 4096), (100, 100)]),
                                            (8, 2, 64, [(2048, 2048), (1, 700)]), (32, 8, 64, [(2048, 2048)]),
                                            (16, 4, 128, [(1920, 4096), (700, 700)])])
