@@ -259,6 +259,12 @@ def _gemm_buffers(device):
     return st
 
 
+def prepare_products(device) -> None:
+    """Allocates and registers what the bfloat16 products need beside their operands (error word, workspace
+    of shared tiles), so that no first call inside a stream capture has to."""
+    _gemm_buffers(torch.device(device))
+
+
 def gemm_share_tiles(enabled: bool) -> None:
     """Switches the sharing of tiles between CTAs of the many-token kernel off, or on again (for comparison)."""
     _split_enabled[0] = bool(enabled)

@@ -17,6 +17,7 @@ import torch
 
 from ..cache import CacheManager, OutOfPages, OutOfSlots
 from ..config import load_config, lookup_architecture
+from ..csrc import ops
 from ..models.text_model import TextModel
 from ..parts.base import Runtime
 from ..weights import Checkpoint, TensorSource
@@ -61,6 +62,8 @@ class ModelRunner:
         self.max_model_len = int(max_model_len) if max_model_len else min(limit, pool_tokens)
         self.rt = Runtime(device=self.device, dtype=self.dtype, max_positions=self.max_model_len,
                           page_size=self.page_size)
+        if self.dtype == torch.bfloat16:
+            ops.prepare_products(self.device)
         self.model = TextModel(self.spec, source, self.rt)
         self.cache = CacheManager(self.model.cache_needs(), max_tokens=pool_tokens, page_size=self.page_size,
                                   max_requests=max_requests, device=self.device, dtype=self.dtype)
