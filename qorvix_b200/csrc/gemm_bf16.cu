@@ -798,14 +798,14 @@ int* g_split_flags = nullptr;
 int g_split_ctas = 0;
 
 // Are the tiles of a product shared between the CTAs?  Where they fill at most three quarters of the
-// SMs, each tile is cut into no more than eight pieces, and a tile's walk along K is long (8,192 or
-// more): handing over and adding the partial sums costs ~10 us, which a shorter walk does not give back
-// (measured: 4096 x 14336 at 128 tokens 72 -> 36 us, at 384 tokens 76 -> 64 us; 4096 x 4096 at 256 tokens
-// 24 -> 34 us), nor do tiles of 256 columns, whose partial sums are twice as large (5120 x 13824 at 512
-// tokens 90 -> 98 us).
+// SMs, each tile is cut into no more than eight pieces, the tiles have 128 columns and a tile's walk along
+// K is long enough (4,096 or more): handing over and adding the partial sums costs ~10 us.  Measured, whole
+// against shared: 4096 x 14336 at 128 tokens 72 -> 36 us, at 384 tokens 76 -> 64 us; 4096 x 4096 at 128 tokens
+// 23.9 -> 21.6 us, at 384 tokens no change; 2048 x 2048 at 256 tokens (K too short) 14.3 -> 18.4 us; tiles of 256
+// columns, whose partial sums are twice as large, 5120 x 13824 at 512 tokens 90 -> 98 us.
 bool share_tiles(int total_tiles, int num_kb, int bn) {
   const int sms = device_sms();
-  return g_split_ws != nullptr && g_split_ctas >= sms && bn <= 128 && total_tiles * 4 <= sms * 3 && total_tiles * 8 >= sms && num_kb >= 128;
+  return g_split_ws != nullptr && g_split_ctas >= sms && bn <= 128 && total_tiles * 4 <= sms * 3 && total_tiles * 8 >= sms && num_kb >= 64;
 }
 
 template <int BN, int STAGES, typename TC, bool SWIGLU, bool ROPE, bool SHARED>

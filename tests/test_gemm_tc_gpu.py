@@ -36,10 +36,10 @@ def test_many_tokens(M, N, K, out_dtype):
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(256, 4096, 14336), (130, 2560, 8192), (384, 2048, 16384), (200, 2000, 9000), (700, 1500, 8200),
-                                   (96, 4096, 14336), (512, 4096, 4096), (544, 5120, 5120)])
+                                   (96, 4096, 14336), (256, 4096, 4096), (130, 6144, 4104), (512, 4096, 4096), (544, 5120, 5120)])
 def test_tiles_shared_between_ctas_give_the_sums_of_whole_tiles(M, N, K, out_dtype):
     """A product with a long walk along K whose tiles fill at most three quarters of the SMs shares them (the
-    first six shapes; the last two are not shared): a CTA that has only later k blocks of a tile leaves its
+    first eight shapes; the last two are not shared): a CTA that has only later k blocks of a tile leaves its
     float32 sums in the workspace, the tile's owner adds them to its own.  The
     result stays within the product's tolerance, is the same on every launch (the flags come down again), and
     equals the unshared product up to the rounding of a few float32 additions per element."""
