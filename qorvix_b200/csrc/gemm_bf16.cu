@@ -8,7 +8,9 @@
 //     rows the other; a persistent kernel, one CTA per SM walking over the tiles, with the
 //     accumulator double-buffered in tensor memory so that one tile's epilogue overlaps the next
 //     tile's main loop.  The epilogue may apply SwiGLU (gate/up projection) or rotate the query and
-//     key heads and write keys and values into the paged cache (QKV projection).
+//     key heads and write keys and values into the paged cache (QKV projection).  A product with
+//     fewer tiles than SMs and a long K shares its tiles' k blocks between all SMs (partial sums
+//     through a float32 workspace, added in a fixed order).
 //   * few tokens (decode, M <= 64): operands are swapped.  128 weight rows are the 128-row MMA
 //     operand and the tokens (padded to 16/32/64) the narrow one, so every weight byte is
 //     streamed from HBM exactly once through a deep TMA ring.  Matrices with few row tiles are
