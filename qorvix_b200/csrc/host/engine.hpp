@@ -549,11 +549,12 @@ class Engine {
     int* tok = h; int* pos = h + T; int* seg = h + 2 * T;
     int* qstart = h + 3 * T; int* pos0 = qstart + S + 1; int* want = pos0 + S; int* table = want + R;
     std::vector<int> first_row((size_t)S);
-    int row = 0, at = 0, wrow = 0;
+    int row = 0, at = 0, wrow = 0, portion_ctx = 0;
     for (int i = 0; i < S; ++i) {
       const StepEntry& e = entries[(size_t)order[(size_t)i]];
       const int p0 = length(e.id), n = (int)e.tokens.size();
       qstart[i] = at; pos0[i] = p0;
+      if (n > 1) portion_ctx = std::max(portion_ctx, p0 + n);
       for (int t = 0; t < n; ++t) { tok[at + t] = e.tokens[(size_t)t]; pos[at + t] = p0 + t; seg[at + t] = i; }
       first_row[(size_t)order[(size_t)i]] = wrow;
       for (int wv : e.want) want[wrow++] = at + wv;
@@ -572,6 +573,7 @@ class Engine {
     h2d_bytes_ += (long long)total * 4;
     StepIO io;
     io.T = T; io.S = S; io.R = R; io.n1 = n1; io.max_q_len = max_q; io.max_ctx_len = max_ctx; io.rest_max_q = rest_q; io.captured = 0;
+    io.portion_max_ctx = portion_ctx;
     io.token_ids = dev; io.tok_pos = dev + T; io.tok_seg = dev + 2 * T; io.seg_q_start = dev + 3 * T; io.seg_pos0 = dev + 3 * T + S + 1;
     io.want_rows = dev + 3 * T + 2 * S + 1; io.block_table = dev + 3 * T + 2 * S + 1 + R; io.max_blocks = width;
     float* logits = R > 0 ? (float*)buffer("logits", (size_t)R * w_.V * 4) : nullptr;

@@ -53,6 +53,7 @@ struct StepIO {
   int T = 0, S = 0, R = 0;
   int n1 = 0;                      // leading segments of one token
   int max_q_len = 0, max_ctx_len = 0, rest_max_q = 0;   // rest_max_q: longest segment after the first n1
+  int portion_max_ctx = 0;                              // longest context among the segments of more than one token (0: not known)
   int captured = 0;                // the step is captured or replayed as a graph: choices must not depend on contexts
   const int* token_ids = nullptr;
   const int* tok_pos = nullptr;
@@ -278,7 +279,7 @@ class Executor {
     const int* p0 = io.seg_pos0 + first_seg;
     const int* bt = io.block_table + (size_t)first_seg * io.max_blocks;
     if (max_q >= 32) {
-      const int rc = k_->attn_prefill_tc(out, ld_out, q, ld_q, io.T, w.cache, w.cache_pages, qs, p0, bt, io.max_blocks, S, max_q, m.H, m.Hkv,
+      const int rc = k_->attn_prefill_tc(out, ld_out, q, ld_q, io.T, w.cache, w.cache_pages, qs, p0, bt, io.max_blocks, S, max_q, io.portion_max_ctx, m.H, m.Hkv,
                                          m.hd, m.page, w.window, m.scale, err_, st);
       if (rc != ERR_UNSUPPORTED) { check(rc, "attention_prefill_tc"); ++route_counts()[ROUTE_PREFILL_TC]; return true; }
     }

@@ -35,7 +35,7 @@ struct QvxModel {
 };
 
 struct QvxStep {
-  int T, S, R, n1, max_q_len, max_ctx_len, rest_max_q, captured, max_blocks, pad;
+  int T, S, R, n1, max_q_len, max_ctx_len, rest_max_q, captured, max_blocks, portion_max_ctx;
   const int* token_ids;
   const int* tok_pos;
   const int* tok_seg;
@@ -104,7 +104,7 @@ long long qvx_forward(void* hv, const QvxStep* s, void* workspace, long long wor
   try {
     qv::StepIO io;
     io.T = s->T; io.S = s->S; io.R = s->R; io.n1 = s->n1; io.max_q_len = s->max_q_len; io.max_ctx_len = s->max_ctx_len;
-    io.rest_max_q = s->rest_max_q; io.captured = s->captured; io.max_blocks = s->max_blocks;
+    io.rest_max_q = s->rest_max_q; io.captured = s->captured; io.max_blocks = s->max_blocks; io.portion_max_ctx = s->portion_max_ctx;
     io.token_ids = s->token_ids; io.tok_pos = s->tok_pos; io.tok_seg = s->tok_seg; io.seg_q_start = s->seg_q_start; io.seg_pos0 = s->seg_pos0;
     io.block_table = s->block_table; io.want_rows = s->want_rows; io.logits = s->logits;
     qv::Arena ws;

@@ -40,7 +40,7 @@ struct Kernels {
   int (*attn_prefill_bf16)(void*, int, const void*, int, const void*, const int*, const int*, const int*, int, int, int, int, int, int, int,
                            int, float, int, void*) = nullptr;
   int (*attn_prefill_tc)(void*, int, const void*, int, int, const void*, long long, const int*, const int*, const int*, int, int, int, int,
-                         int, int, int, int, float, int*, void*) = nullptr;
+                         int, int, int, int, int, float, int*, void*) = nullptr;
   void (*attn_set_decode_variant)(int) = nullptr;
   void (*attn_set_error_word)(int*) = nullptr;
   void (*gemm_set_split_workspace)(float*, int*, int) = nullptr;

@@ -50,7 +50,7 @@ _ARGTYPES = {
     "qv_gemm_bf16_split_slot_bytes": [],
     "qv_attention_generic": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V],
     "qv_attn_prefill_bf16": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V],
-    "qv_attn_prefill_tc": [_V, _I, _V, _I, _I, _V, _L, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _F, _V, _V],
+    "qv_attn_prefill_tc": [_V, _I, _V, _I, _I, _V, _L, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _V, _V],
     "qv_attn_set_decode_variant": [_I],
     "qv_attn_set_error_word": [_V],
     "qv_attn_decode_bf16": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V, _V],
@@ -500,9 +500,10 @@ def attention_prefill_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_tab
 
 
 def attention_prefill_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, Hkv, hd, page,
-                         window, scale) -> bool:
+                         window, scale, max_ctx_len: int = 0) -> bool:
     """Flash attention of prompt portions with tcgen05 tensor-core products (head sizes 64 and 128).
-    False when the kernel refuses the sizes."""
+    max_ctx_len: the longest context (cached + new tokens) among the portions, where the host knows it; it
+    only steers how the kernel cuts its work.  False when the kernel refuses the sizes."""
     _need_cuda(out, q, cache_layer, seg_q_start, seg_pos0, block_table)
     assert q.dtype == out.dtype == cache_layer.dtype == torch.bfloat16
     assert q.stride(1) == 1 and out.stride(1) == 1 and cache_layer.is_contiguous()
@@ -511,8 +512,8 @@ def attention_prefill_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table
     st = _tc_buffers(q.device)
     rc = _lib("attention_tc").qv_attn_prefill_tc(
         _ptr(out), out.stride(0), _ptr(q), q.stride(0), q.shape[0], _ptr(cache_layer), cache_layer.shape[0],
-        _ptr(seg_q_start), _ptr(seg_pos0), _ptr(block_table), block_table.shape[-1], S, max_q_len, H, Hkv, hd, page,
-        window, scale, _ptr(st["err"]), _stream())
+        _ptr(seg_q_start), _ptr(seg_pos0), _ptr(block_table), block_table.shape[-1], S, max_q_len, int(max_ctx_len), H, Hkv,
+        hd, page, window, scale, _ptr(st["err"]), _stream())
     if rc == -2:
         return False
     _check(rc, "attention_prefill_tc")
@@ -588,10 +589,10 @@ def attention_set_decode_variant(variant) -> None:
 
 
 def _attention_portions_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, Hkv, hd, page,
-                             window, scale) -> bool:
+                             window, scale, max_ctx_len=0) -> bool:
     """Prompt portions: tcgen05 kernel for long portions at head sizes 64/128, else mma.sync kernels."""
     if max_q_len >= 32 and attention_prefill_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len,
-                                                H, Hkv, hd, page, window, scale):
+                                                H, Hkv, hd, page, window, scale, max_ctx_len):
         return True
     return attention_prefill_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, Hkv, hd,
                                   page, window, scale)
@@ -614,16 +615,18 @@ def attention(out, q, cache_layer, ctx, block_table, H, Hkv, hd, page, window, s
             while n1 < ctx.num_segments and ctx.seg_len[n1] == 1:
                 n1 += 1
             S = ctx.num_segments
+            # the longest context among the segments of more than one token (what the flash kernel cuts its work by)
+            deep = max((p0 + n for p0, n in zip(ctx.seg_start_pos, ctx.seg_len) if n > 1), default=0)
             if n1 >= 4 and n1 < S:
                 rest_q = max(ctx.seg_len[n1:])
                 splits = decode_splits(n1, Hkv, ctx.max_ctx_len, known=not ctx.captured)
                 ok = attention_decode_bf16(out[:n1], q[:n1], cache_layer, ctx.tok_pos, ctx.tok_seg, block_table, H, Hkv,
                                            hd, page, window, scale, splits)
                 if ok and _attention_portions_bf16(out, q, cache_layer, ctx.seg_q_start[n1:], ctx.seg_pos0[n1:],
-                                                   block_table[n1:], S - n1, rest_q, H, Hkv, hd, page, window, scale):
+                                                   block_table[n1:], S - n1, rest_q, H, Hkv, hd, page, window, scale, deep):
                     return
             elif _attention_portions_bf16(out, q, cache_layer, ctx.seg_q_start, ctx.seg_pos0, block_table, S,
-                                          ctx.max_q_len, H, Hkv, hd, page, window, scale):
+                                          ctx.max_q_len, H, Hkv, hd, page, window, scale, deep):
                 return
     attention_generic(out, q, cache_layer, ctx.tok_pos, ctx.tok_seg, block_table, H, Hkv, hd, page, window, scale)
 

@@ -37,7 +37,7 @@ class _Model(Structure):
 
 
 class _Step(Structure):
-    _fields_ = [(n, c_int) for n in ("T", "S", "R", "n1", "max_q_len", "max_ctx_len", "rest_max_q", "captured", "max_blocks", "pad")] + [
+    _fields_ = [(n, c_int) for n in ("T", "S", "R", "n1", "max_q_len", "max_ctx_len", "rest_max_q", "captured", "max_blocks", "portion_max_ctx")] + [
         (n, c_void_p) for n in ("token_ids", "tok_pos", "tok_seg", "seg_q_start", "seg_pos0", "block_table", "want_rows", "logits")]
 
 
@@ -152,12 +152,13 @@ class NativeExecutor:
         while n1 < S and ctx.seg_len[n1] == 1:
             n1 += 1
         rest = max(ctx.seg_len[n1:], default=0)
+        deep = max((p0 + n for p0, n in zip(ctx.seg_start_pos, ctx.seg_len) if n > 1), default=0)
         bt = ctx.block_tables[self.group]
         logits = torch.empty((R, self.vocab), device=self.rt.device, dtype=torch.float32) if R else None
         nbytes = _lib.qvx_workspace_bytes(self._h, T, R, n1)
         ws = torch.empty(nbytes, device=self.rt.device, dtype=torch.uint8)
         step = _Step(T=T, S=S, R=R, n1=n1, max_q_len=ctx.max_q_len, max_ctx_len=ctx.max_ctx_len, rest_max_q=rest,
-                     captured=1 if ctx.captured else 0, max_blocks=bt.shape[-1], pad=0, token_ids=ctx.token_ids.data_ptr(),
+                     captured=1 if ctx.captured else 0, max_blocks=bt.shape[-1], portion_max_ctx=deep, token_ids=ctx.token_ids.data_ptr(),
                      tok_pos=ctx.tok_pos.data_ptr(), tok_seg=ctx.tok_seg.data_ptr(), seg_q_start=ctx.seg_q_start.data_ptr(),
                      seg_pos0=ctx.seg_pos0.data_ptr(), block_table=bt.data_ptr(), want_rows=ctx.want_rows.data_ptr() if R else None,
                      logits=logits.data_ptr() if R else None)
