@@ -405,6 +405,37 @@ def test_attention_decode_bf16_at_8192_keys(H, Hkv, hd, variant):
         ops.attention_set_decode_variant(None)
 
 
+@pytest.mark.parametrize("seed", [11, 12, 13])
+def test_attention_prefill_tcgen05_on_random_mixes_of_segments(seed):
+    """Random head counts, page sizes, windows, segment lengths and depths (few heads: tiles taken singly; 32
+    or 40 heads: in pairs), with and without the hint of the portions' longest context, twice each, against
+    float64: what a warp running ahead of the others, a tile without its pair or a phase counted wrongly
+    would break."""
+    import random
+    rnd = random.Random(seed)
+    for case in range(6):
+        hd = rnd.choice([64, 128])
+        Hkv, group = rnd.choice([(1, 4), (2, 2), (4, 5), (8, 4), (10, 4)])
+        H = Hkv * group
+        page = rnd.choice([16, 32, 64])
+        window = rnd.choice([0, 0, rnd.randint(20, 400)])
+        lens = []
+        for _ in range(rnd.randint(1, 4)):
+            qlen = rnd.choice([1, 33, 100, 128, 129, 256, 300, 511, 640])
+            lens.append((qlen, qlen + rnd.choice([0, 0, 5, 128, 500, 1000])))
+        if max(q for q, _ in lens) < 32:
+            lens[0] = (77, 300)
+        d = _segments(lens, H, Hkv, hd, page, seed=seed * 100 + case, window=window)
+        for hint in (0, d["max_ctx"]):
+            for _ in range(2):
+                out = torch.full_like(d["q"], float("nan"))
+                assert ops.attention_prefill_tc(out, d["q"], d["cache"], d["qstart"], d["pos0"], d["bt"], d["S"], d["max_q"], H, Hkv,
+                                                hd, page, window, 1.0 / math.sqrt(hd), max_ctx_len=hint)
+                torch.cuda.synchronize()
+                ops.check_kernel_errors()
+                assert torch.allclose(out.double().cpu(), d["ref"], rtol=2e-2, atol=2e-2), (H, Hkv, hd, page, window, lens, hint)
+
+
 @pytest.mark.parametrize("H,Hkv,hd", [(32, 8, 128), (32, 8, 64)])
 def test_attention_prefill_tcgen05_of_portions_deep_in_their_requests(H, Hkv, hd):
     """Told the portions' longest context, the kernel takes the query tiles of deep portions in pairs where it
