@@ -41,7 +41,8 @@
 // and reports through *err instead of hanging.
 #include "tc_common.cuh"
 
-#define K_ST 2              // stages of keys in shared memory
+#define K_ST_PAIRS 2        // stages of keys in shared memory with two query tiles an item ...
+#define K_ST_SINGLE 3       // ... and with one (the second tile's room holds a stage more)
 #define V_ST 2              // stages of values
 #define RESCALE_STEP 8.0f
 #define QT 128              // query rows per tile
@@ -134,7 +135,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_prefill_tc_kernel(const __g
   static_assert(2 * KT + 2 * HD <= 512, "S and O of both query tiles must fit tensor memory");
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = base;                                // tiles A and B
-  uint8_t* sK = sQ + 2 * Q_BYTES;                    // K_ST stages
+  constexpr int K_ST = PAIRED ? K_ST_PAIRS : K_ST_SINGLE;
+  uint8_t* sK = sQ + (PAIRED ? 2 : 1) * Q_BYTES;     // K_ST stages
   uint8_t* sV = sK + K_ST * K_BYTES;                 // V_ST stages
   uint64_t* bars = (uint64_t*)(sV + V_ST * K_BYTES);
   uint64_t* q_full = bars;                           // [2]: one per query tile, like the next four
@@ -180,15 +182,19 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_prefill_tc_kernel(const __g
   Walk<PAIRED> walk{0, (int)blockIdx.x, (int)gridDim.x};
   Item t;
 
-  if (warp == 0) {
-    // The whole warp requests: a tile of keys and values is 8 blocks of 16 keys (a page may hold no
-    // more), each in NH halves of 64 dims, i.e. up to 32 small TMA loads; the lanes issue one each.
-    const int which = lane / (8 * NH);               // 0: keys, 1: values (lanes beyond have nothing to do)
+  if (warp == 0 || (!PAIRED && warp == 3)) {
+    // A tile of keys or values is 8 blocks of 16 keys (a page may hold no more), each in NH halves of 64
+    // dims: up to 16 small TMA loads, which the lanes issue one each (one thread issuing them all took as
+    // long as the tile's softmax).  With pairs warp 0 requests both, keys on its first lanes and values on
+    // the next.  A tile alone has its S computed ahead, and its next Q.K^T found the keys late while they
+    // shared a warp with the values (a free stage of values comes two products after a free stage of
+    // keys): there warp 0 requests the keys and warp 3 the values, each at the pace of its own ring.
+    const int which = PAIRED ? lane / (8 * NH) : (warp == 0 ? 0 : 1);   // 0: keys, 1: values (lanes beyond have nothing to do)
     const int blk = (lane % (8 * NH)) / NH, hf = lane % NH;
-    if (which < 2) {
+    if (which < 2 && (PAIRED || lane < 8 * NH)) {
       // the lanes that load keys and the lanes that load values each follow their own barriers
-      const int leader = which * 8 * NH;
-      const unsigned group = ((1u << (8 * NH)) - 1u) << leader;
+      const int leader = PAIRED ? which * 8 * NH : 0;
+      const unsigned group = (8 * NH == 32) ? 0xffffffffu : (((1u << (8 * NH)) - 1u) << leader);
       uint64_t* full = which ? v_full : k_full;
       uint64_t* empty = which ? v_empty : k_empty;
       const int stages = which ? V_ST : K_ST;
@@ -506,7 +512,8 @@ int device_sms() {
 template <int HD, bool PAIRED>
 int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const AttnArgs& args, cudaStream_t st) {
   // two Q tiles, the rings of keys and values, 256 bytes of barriers, 2 KB for what a row's threads exchange, 1 KB to align
-  constexpr int smem = 2 * QT * HD * 2 + (K_ST + V_ST) * KT * HD * 2 + 256 + 2048 + 1024;
+  constexpr int smem = 2 * QT * HD * 2 + (K_ST_PAIRS + V_ST) * KT * HD * 2 + 256 + 2048 + 1024;
+  static_assert(QT * HD * 2 + (K_ST_SINGLE + V_ST) * KT * HD * 2 <= 2 * QT * HD * 2 + (K_ST_PAIRS + V_ST) * KT * HD * 2, "one layout's room serves both");
   static_assert(smem <= 227 * 1024, "more shared memory than a CTA can have");
   static bool configured = false;
   auto kernel = attn_prefill_tc_kernel<HD, PAIRED>;
@@ -533,15 +540,17 @@ extern "C" int qv_attn_prefill_tc(void* out, int ld_out, const void* q, int ld_q
   if ((hd != 64 && hd != 128) || Hkv <= 0 || H % Hkv || page % 16 || (ld_q & 7) || (ld_out & 7) || ((uintptr_t)q & 15) ||
       ((uintptr_t)cache & 15) || ((uintptr_t)out & 15))
     return QV_ERR_UNSUPPORTED;
-  // Two query tiles an item (their softmax warps take turns), unless that leaves SMs without an item.  Portions
-  // that lie deep in their requests (max_ctx_len, the longest context among them, at least twice the longest
-  // portion; 0: not known) have items of about equal length: there one round of pairs beats two rounds of
-  // single tiles (1,024 tokens ending at 4,096: 98.5 against 126.8 us), while for a prompt from its start,
-  // whose items grow from one key tile to many, single tiles balance better (1,024 tokens: 27.7 against 31.4 us).
+  // Two query tiles an item where that still gives every SM an item, for prompts from (near) their start, whose
+  // items grow from one key tile to many: pairs read keys and values once for two tiles and halve the number
+  // of items (2,048 tokens 61.0 against 65.4 us, 4,096 tokens 195 against 200 us; 1,024 tokens, 128 pairs
+  // on 148 SMs, 31 against 25 us).  Portions that lie deep in their requests (max_ctx_len, the longest
+  // context among them, at least twice the longest portion; 0: not known) have items of equal length, and a
+  // launch then costs its rounds of items: single tiles never need more rounds than pairs cost (1,536 tokens
+  // ending at 8,192: 264 against 328 us; 1,024 ending at 4,096: 93 against 98 us).
   const long long q_tiles = (max_q_len + QT - 1) / QT;
-  const long long items_single = (long long)H * S * q_tiles, items_paired = (long long)H * S * ((q_tiles + 1) / 2);
+  const long long items_paired = (long long)H * S * ((q_tiles + 1) / 2);
   const bool deep = max_ctx_len > 0 && max_ctx_len >= 2 * max_q_len;
-  const int paired = (items_paired >= device_sms() || (deep && items_single > device_sms())) ? 1 : 0;
+  const int paired = (items_paired >= device_sms() && !deep) ? 1 : 0;
   const long long q_pairs = paired ? (q_tiles + 1) / 2 : q_tiles;
   if ((long long)H * S * q_pairs > (1LL << 30)) return QV_ERR_TOO_LARGE;
   CUtensorMap mq, mkv;

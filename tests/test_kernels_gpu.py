@@ -438,12 +438,12 @@ def test_attention_prefill_tcgen05_on_random_mixes_of_segments(seed):
 
 @pytest.mark.parametrize("H,Hkv,hd", [(32, 8, 128), (32, 8, 64)])
 def test_attention_prefill_tcgen05_of_portions_deep_in_their_requests(H, Hkv, hd):
-    """Told the portions' longest context, the kernel takes the query tiles of deep portions in pairs where it
-    would take them singly otherwise (256 tiles on 148 SMs here): both ways against float64, two portions of
-    unequal length, one of them with an odd number of tiles."""
+    """Told the portions' longest context, the kernel takes the query tiles of deep portions one by one; not told,
+    in pairs (288 pairs here): both ways against float64, two portions of unequal length, one of them with an
+    odd number of tiles."""
     page = 16
-    d = _segments([(1024, 4096), (300, 2500)], H, Hkv, hd, page, seed=500 + hd)
-    for hint in (4096, 0):
+    d = _segments([(2048, 4200), (300, 2500)], H, Hkv, hd, page, seed=500 + hd)
+    for hint in (4200, 0):
         out = torch.full_like(d["q"], float("nan"))
         assert ops.attention_prefill_tc(out, d["q"], d["cache"], d["qstart"], d["pos0"], d["bt"], d["S"], d["max_q"], H, Hkv, hd,
                                         page, 0, 1.0 / math.sqrt(hd), max_ctx_len=hint)
