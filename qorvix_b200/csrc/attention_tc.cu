@@ -155,7 +155,9 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_prefill_tc_kernel(const __g
   // over the same bytes)
   uint8_t* xchg = (uint8_t*)(bars + 32);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the warp's number through a shuffle: the compiler then knows that it is the same in all lanes, and keeps what
+  // depends on it alone (the MMA warp's descriptors and counters) in uniform registers
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   pdl_wait();
   pdl_launch_dependents();
 
@@ -240,7 +242,11 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_prefill_tc_kernel(const __g
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      // The whole warp walks the items and waits; one elected lane issues the products.  (A branch on the lane
+      // number around all of this makes every operand of every product a per-thread value, to be moved to the
+      // uniform registers the instruction wants, one at a time: some 85 clocks a product.)
+      const bool leader = elect_one();
       constexpr uint32_t idesc_qk = umma_idesc(QT, KT, 0);
       constexpr uint32_t idesc_pv = umma_idesc(QT, HD, 1);
       int loads[2] = {0, 0};                         // Q tiles of A and of B seen so far
@@ -254,6 +260,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_prefill_tc_kernel(const __g
         if (n_pv[x] > 0 && !mbar_wait(&pv_done[x], (n_pv[x] - 1) & 1, a.err, 14)) return false;
         tc_fence_after();
         const uint32_t d = tmem + (uint32_t)(x * KT);
+        if (leader) {
 #pragma unroll
         for (int hf = 0; hf < NH; ++hf) {
           const uint64_t dq = umma_desc(smem_u32(sQ + qx * Q_BYTES + hf * HALF_BYTES));
@@ -264,6 +271,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_prefill_tc_kernel(const __g
         umma_commit(&s_full[x]);
         if (qx == 1 || t.n_b == 0) umma_commit(&k_empty[ks]);  // B (where there is one) is the last to read a key tile
         if (last) umma_commit(&q_empty[qx]);
+        }
+        __syncwarp();
         return true;
       };
       // O of query tile qx += P V over the item's key tile j, P from S buffer x
@@ -275,6 +284,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_prefill_tc_kernel(const __g
         // P [128 rows][128 keys] in tensor memory, two keys per column, each softmax warpgroup's 64 keys at the
         // start of its share of S; V [128 keys][HD] MN-major
         const uint32_t o = tmem_o + (uint32_t)(qx * HD), p = tmem + (uint32_t)(x * KT);
+        if (leader) {
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk) {
           const uint32_t v_addr = smem_u32(sV + vs * K_BYTES + (kk * 16) * 128);
@@ -282,8 +292,10 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_prefill_tc_kernel(const __g
           umma_f16_ts(o, p + p_col, umma_desc_mn(v_addr, HALF_BYTES), idesc_pv, (kk > 0 || j > 0) ? 1u : 0u);
         }
         umma_commit(&pv_done[x]);
-        ++n_pv[x];
         if (qx == 1 || t.n_b == 0) umma_commit(&v_empty[vs]);
+        }
+        __syncwarp();
+        ++n_pv[x];
         return true;
       };
       bool ok = true;
