@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
   float* rs_s = (float*)(ok_slots + 4);   // [64] a token's rsqrt(mean of squares + eps), with NormArgs::ssq_in
   float* rs_part = rs_s + 64;             // [128] the threads' shares of the sums behind rs_s
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;   // known to be uniform
   const int wide0 = blockIdx.x * BM;
   const int narrow0 = blockIdx.y * BN;
   const int split = blockIdx.z;
@@ -152,7 +152,9 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      // the whole warp walks the loop and waits; one elected lane issues (its operands then stay in uniform registers)
+      const bool leader = elect_one();
       constexpr uint32_t idesc = umma_idesc(BM, BN);
       bool ok = true;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
@@ -163,12 +165,16 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
         tc_fence_after();
         const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
         const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < BK / 16; ++kk)    // 16 k elements = 32 bytes = 2 descriptor units
-          umma_f16(tmem_base, da + 2 * kk, db + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&empty[s]);                  // frees the stage when these MMAs have read it
+          for (int kk = 0; kk < BK / 16; ++kk)    // 16 k elements = 32 bytes = 2 descriptor units
+            umma_f16(tmem_base, da + 2 * kk, db + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(&empty[s]);                  // frees the stage when these MMAs have read it
+        }
+        __syncwarp();
       }
-      umma_commit(accum);                        // accumulator complete (or nothing was issued)
+      if (leader) umma_commit(accum);              // accumulator complete (or nothing was issued)
+      __syncwarp();
     }
   } else {
     // epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31
@@ -535,7 +541,7 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
   uint64_t* acc_empty = acc_full + 2;                // [2]
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;   // known to be uniform
   const int M = args.rows_wide, N = args.rows_narrow;
   const int bn = args.bn;                            // columns of a tile: at most BN, the ring's room
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
@@ -612,7 +618,11 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
       if (first) pdl_wait();
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      // The whole warp walks the loop and waits; one elected lane issues.  (Under a branch on the lane number
+      // the products' operands are per-thread values, moved one at a time to the uniform registers the
+      // instruction wants: some 85 clocks a product, more than a product 128 columns wide takes.)
+      const bool leader = elect_one();
       const uint32_t idesc = umma_idesc(BM, bn);
       int it = 0, local = 0;
       bool ok = true;
@@ -633,12 +643,16 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
           tc_fence_after();
           const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
           const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
+          if (leader) {
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk)
-            umma_f16(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (kb > sg.kb0 || kk > 0) ? 1u : 0u);
-          umma_commit(&empty[s]);
+            for (int kk = 0; kk < BK / 16; ++kk)
+              umma_f16(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (kb > sg.kb0 || kk > 0) ? 1u : 0u);
+            umma_commit(&empty[s]);
+          }
+          __syncwarp();
         }
-        umma_commit(&acc_full[b]);
+        if (leader) umma_commit(&acc_full[b]);
+        __syncwarp();
         ++local;
       }
     }
