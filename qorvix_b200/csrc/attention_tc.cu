@@ -184,48 +184,49 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_prefill_tc_kernel(const __g
   Walk<PAIRED> walk{0, (int)blockIdx.x, (int)gridDim.x};
   Item t;
 
-  if (warp == 0 || (!PAIRED && warp == 3)) {
-    // A tile of keys or values is 8 blocks of 16 keys (a page may hold no more), each in NH halves of 64
-    // dims: up to 16 small TMA loads, which the lanes issue one each (one thread issuing them all took as
-    // long as the tile's softmax).  With pairs warp 0 requests both, keys on its first lanes and values on
-    // the next.  A tile alone has its S computed ahead, and its next Q.K^T found the keys late while they
-    // shared a warp with the values (a free stage of values comes two products after a free stage of
-    // keys): there warp 0 requests the keys and warp 3 the values, each at the pace of its own ring.
-    const int which = PAIRED ? lane / (8 * NH) : (warp == 0 ? 0 : 1);   // 0: keys, 1: values (lanes beyond have nothing to do)
-    const int blk = (lane % (8 * NH)) / NH, hf = lane % NH;
-    if (which < 2 && (PAIRED || lane < 8 * NH)) {
-      // the lanes that load keys and the lanes that load values each follow their own barriers
-      const int leader = PAIRED ? which * 8 * NH : 0;
-      const unsigned group = (8 * NH == 32) ? 0xffffffffu : (((1u << (8 * NH)) - 1u) << leader);
-      uint64_t* full = which ? v_full : k_full;
-      uint64_t* empty = which ? v_empty : k_empty;
-      const int stages = which ? V_ST : K_ST;
-      uint8_t* dst = (which ? sV : sK) + hf * HALF_BYTES + blk * 16 * 128;
-      int s = 0;                                     // the ring's stage, and how often it has been round
-      uint32_t lap = 0;
-      bool alive = true;
-      while (alive && walk.next(a, t)) {
-        const int last_block = t.k_last & ~15;
-        const int n = t.n_b > t.n_a ? t.n_b : t.n_a;
-        for (int j = 0; j < n; ++j) {
-          int key0 = (t.tile_begin + j) * KT + blk * 16;
-          if (key0 > last_block) key0 = last_block;            // keys nobody sees: any valid page will do
-          const int pg = t.bt[key0 / a.page];                  // fetched before the wait: its latency is the wait's
-          int ok = 1;
-          if (lane == leader) {
-            ok = mbar_wait(&empty[s], (lap & 1) ^ 1, a.err, 11) ? 1 : 0;
-            if (ok) mbar_expect_tx(&full[s], K_BYTES);
+  if (warp == 0 || warp == 3) {
+    // Warp 0 requests the keys, warp 3 the values, each at the pace of its own ring (in one warp the keys
+    // waited for a free stage of values, which comes later than a free stage of keys, and the next Q.K^T
+    // found them late).  A tile is 8 blocks of 16 keys (a page may hold no more), each in NH halves of 64
+    // dims: up to 16 small TMA loads.  The whole warp walks the items; lane b finds block b's rows in the
+    // cache, and an elected lane issues all the loads from values the compiler knows to be the same in all
+    // lanes (a lane that issues loads of its own pays for moving their operands to uniform registers).
+    const int which = warp == 0 ? 0 : 1;             // 0: keys, 1: values
+    const bool leader = elect_one();
+    uint64_t* full = which ? v_full : k_full;
+    uint64_t* empty = which ? v_empty : k_empty;
+    const int stages = which ? V_ST : K_ST;
+    uint8_t* ring = which ? sV : sK;
+    int s = 0;                                       // the ring's stage, and how often it has been round
+    uint32_t lap = 0;
+    bool alive = true;
+    while (alive && walk.next(a, t)) {
+      const int last_block = t.k_last & ~15;
+      const int n = t.n_b > t.n_a ? t.n_b : t.n_a;
+      for (int j = 0; j < n; ++j) {
+        int key0 = (t.tile_begin + j) * KT + (lane & 7) * 16;
+        if (key0 > last_block) key0 = last_block;              // keys nobody sees: any valid page will do
+        const int pg = t.bt[key0 / a.page];                    // fetched before the wait: its latency is the wait's
+        const int my_row = ((pg * 2 + which) * a.Hkv + t.kvh) * a.page + (key0 % a.page);
+        alive = mbar_wait(&empty[s], (lap & 1) ^ 1, a.err, 11);
+        if (!alive) break;
+        if (leader) mbar_expect_tx(&full[s], K_BYTES);
+#pragma unroll
+        for (int blk = 0; blk < KT / 16; ++blk) {
+          const int row = __shfl_sync(0xffffffffu, my_row, blk);
+          if (leader) {
+#pragma unroll
+            for (int hf = 0; hf < NH; ++hf)
+              tma_load_2d(ring + s * K_BYTES + hf * HALF_BYTES + blk * 16 * 128, &map_kv, &full[s], hf * 64, row);
           }
-          ok = __shfl_sync(group, ok, leader);
-          if (!ok) { alive = false; break; }
-          const int row = ((pg * 2 + which) * a.Hkv + t.kvh) * a.page + (key0 % a.page);
-          tma_load_2d(dst + s * K_BYTES, &map_kv, &full[s], hf * 64, row);
-          if (++s == stages) { s = 0; ++lap; }
         }
+        __syncwarp();
+        if (++s == stages) { s = 0; ++lap; }
       }
     }
   } else if (warp == 2) {
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();
       int loads[2] = {0, 0};                         // of tile A and of tile B so far: their barriers' phases
       bool alive = true;
       while (alive && walk.next(a, t)) {
@@ -234,9 +235,12 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_prefill_tc_kernel(const __g
           // the last Q.K^T of the tile loaded before has read the old Q
           alive = mbar_wait(&q_empty[x], (loads[x] & 1) ^ 1, a.err, 10);
           if (!alive) break;
-          mbar_expect_tx(&q_full[x], Q_BYTES);
-          for (int f = 0; f < NH; ++f)
-            tma_load_2d(sQ + x * Q_BYTES + f * HALF_BYTES, &map_q, &q_full[x], t.h * HD + f * 64, t.q0 + t.tile0 + x * QT);
+          if (leader) {
+            mbar_expect_tx(&q_full[x], Q_BYTES);
+            for (int f = 0; f < NH; ++f)
+              tma_load_2d(sQ + x * Q_BYTES + f * HALF_BYTES, &map_q, &q_full[x], t.h * HD + f * 64, t.q0 + t.tile0 + x * QT);
+          }
+          __syncwarp();
           ++loads[x];
         }
       }

@@ -121,7 +121,9 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
   float norm_w0 = 0.f;
 
   if (warp == 0) {
-    if (lane == 0) {
+    {
+      // (the whole warp walks the loop and waits, an elected lane requests: see the MMA warp)
+      const bool leader = elect_one();
       // Weights are never written by a kernel, so the first stages' weight tiles are requested
       // before waiting for the kernel ahead in the stream; the activation tiles after.
       const CUtensorMap* w_map = &map_wide;
@@ -132,23 +134,32 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
       // a packed weight matrix is read tile by tile with contiguous 16 KB copies; its tiles are 128
       // rows, so the weight side of this kernel's tile must be 128 rows too (the host sees to that)
       const uint8_t* wp = args.packed ? args.packed + ((size_t)blockIdx.x * total_kb + kb0) * (size_t)A_BYTES : nullptr;
-      for (int kb = 0; kb < pre; ++kb) {
-        mbar_expect_tx(&full[kb], STAGE_BYTES);
-        if (wp) bulk_load_1d(tiles + kb * STAGE_BYTES + w_off, wp + (size_t)kb * A_BYTES, &full[kb], A_BYTES);
-        else tma_load_2d(tiles + kb * STAGE_BYTES + w_off, w_map, &full[kb], (kb0 + kb) * BK, w_row0);
+      if (leader) {
+        for (int kb = 0; kb < pre; ++kb) {
+          mbar_expect_tx(&full[kb], STAGE_BYTES);
+          if (wp) bulk_load_1d(tiles + kb * STAGE_BYTES + w_off, wp + (size_t)kb * A_BYTES, &full[kb], A_BYTES);
+          else tma_load_2d(tiles + kb * STAGE_BYTES + w_off, w_map, &full[kb], (kb0 + kb) * BK, w_row0);
+        }
       }
+      __syncwarp();
       pdl_wait();
-      for (int kb = 0; kb < pre; ++kb)
-        tma_load_2d(tiles + kb * STAGE_BYTES + x_off, x_map, &full[kb], (kb0 + kb) * BK, x_row0);
+      if (leader) {
+        for (int kb = 0; kb < pre; ++kb)
+          tma_load_2d(tiles + kb * STAGE_BYTES + x_off, x_map, &full[kb], (kb0 + kb) * BK, x_row0);
+      }
+      __syncwarp();
       for (int kb = pre; kb < num_kb; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = (kb / STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, args.err, 1)) break;
-        mbar_expect_tx(&full[s], STAGE_BYTES);
-        uint8_t* a = tiles + s * STAGE_BYTES;
-        if (wp) bulk_load_1d(a + w_off, wp + (size_t)kb * A_BYTES, &full[s], A_BYTES);
-        else tma_load_2d(a + w_off, w_map, &full[s], (kb0 + kb) * BK, w_row0);
-        tma_load_2d(a + x_off, x_map, &full[s], (kb0 + kb) * BK, x_row0);
+        if (leader) {
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          uint8_t* a = tiles + s * STAGE_BYTES;
+          if (wp) bulk_load_1d(a + w_off, wp + (size_t)kb * A_BYTES, &full[s], A_BYTES);
+          else tma_load_2d(a + w_off, w_map, &full[s], (kb0 + kb) * BK, w_row0);
+          tma_load_2d(a + x_off, x_map, &full[s], (kb0 + kb) * BK, x_row0);
+        }
+        __syncwarp();
       }
     }
   } else if (warp == 1) {
@@ -566,7 +577,9 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
   pdl_launch_dependents();
 
   if (warp == 0) {
-    if (lane == 0) {
+    {
+      // (the whole warp walks the loop and waits, an elected lane requests: see the MMA warp)
+      const bool leader = elect_one();
       // Arms stage s and requests the bn weight rows from n0 for k block kb: one tensor tile, or,
       // from a packed matrix, the rows' share of each 16 KB tile they lie in (eight rows are 1 KB
       // of a tile, so rows from a multiple of 16 are a contiguous piece that lands on a swizzle
@@ -574,6 +587,7 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
       const int w_rows = ((N + BM - 1) / BM) * BM;
       auto load_w = [&](int s, int kb, int n0) {
         uint8_t* dst = tiles + s * STAGE_BYTES + A_BYTES;
+        if (!leader) return;
         if (args.packed) {
           const int end = n0 + bn < w_rows ? n0 + bn : w_rows;
           mbar_expect_tx(&full[s], A_BYTES + (end - n0) * (BK * 2));
@@ -602,7 +616,9 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
           const int pre = len < STAGES ? len : STAGES;
           for (int k = 0; k < pre; ++k) load_w(k, sg.kb0 + k, n0);
           pdl_wait();
-          for (int k = 0; k < pre; ++k) tma_load_2d(tiles + k * STAGE_BYTES, &map_x, &full[k], (sg.kb0 + k) * BK, m0);
+          if (leader)
+            for (int k = 0; k < pre; ++k) tma_load_2d(tiles + k * STAGE_BYTES, &map_x, &full[k], (sg.kb0 + k) * BK, m0);
+          __syncwarp();
           kb = sg.kb0 + pre;
           it = pre;
           first = false;
@@ -612,7 +628,8 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, args.err, 1)) { ok = false; break; }
           load_w(s, kb, n0);
-          tma_load_2d(tiles + s * STAGE_BYTES, &map_x, &full[s], kb * BK, m0);
+          if (leader) tma_load_2d(tiles + s * STAGE_BYTES, &map_x, &full[s], kb * BK, m0);
+          __syncwarp();
         }
       }
       if (first) pdl_wait();
