@@ -558,15 +558,19 @@ extern "C" int qv_attn_prefill_tc(void* out, int ld_out, const void* q, int ld_q
     return QV_ERR_UNSUPPORTED;
   // Two query tiles an item where that still gives every SM an item, for prompts from (near) their start, whose
   // items grow from one key tile to many: pairs read keys and values once for two tiles and halve the number
-  // of items (2,048 tokens 61.0 against 65.4 us, 4,096 tokens 195 against 200 us; 1,024 tokens, 128 pairs
-  // on 148 SMs, 31 against 25 us).  Portions that lie deep in their requests (max_ctx_len, the longest
+  // of items (2,048 tokens 50.2 against 56.1 us, 4,096 tokens 151 against 167 us; 1,024 tokens, 128 pairs
+  // on 148 SMs, 26.5 against 21.3 us).  Portions that lie deep in their requests (max_ctx_len, the longest
   // context among them, at least twice the longest portion; 0: not known) have items of equal length, and a
-  // launch then costs its rounds of items: single tiles never need more rounds than pairs cost (1,536 tokens
-  // ending at 8,192: 264 against 328 us; 1,024 ending at 4,096: 93 against 98 us).
+  // launch then costs its rounds of items, a round of pairs about two rounds of single tiles: pairs where
+  // they need no more than half the rounds (2,048 tokens ending at 8,192: 4 rounds against 2, 277 against
+  // 248 us), single tiles else (1,536 ending at 8,192: 3 rounds against 2, 217 against 246 us).
+  const long long sms = device_sms();
   const long long q_tiles = (max_q_len + QT - 1) / QT;
+  const long long items_single = (long long)H * S * q_tiles;
   const long long items_paired = (long long)H * S * ((q_tiles + 1) / 2);
   const bool deep = max_ctx_len > 0 && max_ctx_len >= 2 * max_q_len;
-  const int paired = (items_paired >= device_sms() && !deep) ? 1 : 0;
+  const long long rounds_single = (items_single + sms - 1) / sms, rounds_paired = (items_paired + sms - 1) / sms;
+  const int paired = (items_paired >= sms && (!deep || 2 * rounds_paired <= rounds_single)) ? 1 : 0;
   const long long q_pairs = paired ? (q_tiles + 1) / 2 : q_tiles;
   if ((long long)H * S * q_pairs > (1LL << 30)) return QV_ERR_TOO_LARGE;
   CUtensorMap mq, mkv;
