@@ -11,11 +11,13 @@
 // with so few tiles that pairs would leave SMs without work (PAIRED = false) an item is one tile:
 // tile B's warps then idle and the tile's S takes both S buffers in turn, so that the S of the next
 // keys is computed while the softmax of these runs.
-//   warp 0        TMA: K and V tiles into rings of two stages each that run on
-//                 across items, every lane issuing one of a stage's loads (a page may hold no more
-//                 than 16 keys).  A key stage is free again as soon as the last Q.K^T that uses it
-//                 is done, its values' stage after the last P.V.
-//   warp 1        MMA: for each query tile in turn, O += P V of the tile's current keys (P read from
+//   warps 0, 3    TMA: warp 0 the K tiles, warp 3 the V tiles, into rings of two stages each (three of keys
+//                 without pairs) that run on across items.  A tile is eight loads of 16 keys (a page may hold
+//                 no more) per 64 dims; lane b looks up block b's page, an elected lane issues all of them.
+//                 A key stage is free again as soon as the last Q.K^T that uses it is done, its values'
+//                 stage after the last P.V.
+//   warp 1        MMA (the whole warp walks the loop and waits, an elected lane issues): for each query tile
+//                 in turn, O += P V of the tile's current keys (P read from
 //                 tensor memory, V as an MN-major operand from shared memory) as soon as its softmax
 //                 warpgroup has written P, then S = Q K^T of the next keys into the tile's S.
 //   warp 2        TMA: an item's Q tiles, each as soon as the last Q.K^T of the item before has read
@@ -47,7 +49,7 @@
 #define RESCALE_STEP 8.0f
 #define QT 128              // query rows per tile
 #define KT 128              // keys per tile
-#define ATTN_THREADS 640    // warps 0..3: TMA of keys and values, MMA, TMA of queries, idle; 4..11 and 12..19: softmax
+#define ATTN_THREADS 640    // warps 0..3: TMA of keys, MMA, TMA of queries, TMA of values; 4..11 and 12..19: softmax
 
 namespace {
 
