@@ -898,7 +898,8 @@ static int choose_tile_width(int tiles_m, int N, int K, int step) {
 }
 
 // K splits of the few-token kernel and the k blocks of each.
-static int swap_splits(int tiles, int total_kb, int epilogue, int force_splits, int* per_split) {
+// `tokens`: the rows of the narrow side; `least`: the fewest splits the epilogue works with.
+static int swap_splits(int tiles, int total_kb, int epilogue, int force_splits, int tokens, int least, int* per_split) {
   int splits = 1;
   if (epilogue == 1) splits = 1;                  // the fused activation needs whole sums
   else if (force_splits > 0) splits = force_splits;
@@ -906,6 +907,10 @@ static int swap_splits(int tiles, int total_kb, int epilogue, int force_splits, 
     // a power of two, at most 4: clusters of 8 CTAs do not all find room at once (measured: a
     // 2048 x 8192 product takes 22.5 us at 8 splits, 13.2 us at 4), and at most 4/3 CTAs per SM in all
     while (splits < 4 && tiles * splits * 2 <= device_sms() + device_sms() / 3 && total_kb / (splits * 2) >= 4) splits *= 2;
+    // From 32 tokens on the partial sums that cross between the CTAs of a cluster weigh more than the SMs a
+    // second, partly filled round of CTAs adds (6144 x 4096, 48 tiles: 64 tokens 18.2 us at 4 splits, 16.3 at 2,
+    // 14.6 at 1; 32 tokens 14.1 / 13.6 / 13.4; 8 tokens 11.3 / 11.8 / 12.6)
+    if (tokens >= 32 && tiles * splits > device_sms()) splits = least;
   }
   if (splits > total_kb) splits = total_kb;
   const int per = (total_kb + splits - 1) / splits;
@@ -936,7 +941,7 @@ static int gemm_bf16_entry(void* C, const void* A, const void* W, const void* pa
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     const int tiles = (N + BM - 1) / BM;
     int per = 0;
-    const int splits = swap_splits(tiles, total_kb, epilogue, force_splits, &per);
+    const int splits = swap_splits(tiles, total_kb, epilogue, force_splits, M, 1, &per);
     args.rows_wide = N; args.rows_narrow = M; args.kblocks_per_split = per; args.splits = splits;
     if (!make_map(&mn, A, M, K, lda, bn)) return QV_ERR_UNSUPPORTED;
     if (packed) { args.packed = (const uint8_t*)packed; mw = mn; }
@@ -1030,7 +1035,7 @@ extern "C" int qv_gemm_bf16_norm(void* C, const void* A, const void* packed, int
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   const int tiles = (N + BM - 1) / BM, total_kb = (K + BK - 1) / BK;
   int per = 0;
-  const int splits = swap_splits(tiles, total_kb, epilogue, 0, &per);
+  const int splits = swap_splits(tiles, total_kb, epilogue, 0, M, residual ? 2 : 1, &per);
   if (residual && splits < 2) return QV_ERR_UNSUPPORTED;
   GemmArgs args;
   args.C = C; args.err = err; args.packed = (const uint8_t*)packed; args.bn = 0;
