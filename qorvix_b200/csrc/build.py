@@ -227,7 +227,33 @@ def build_cli(verbose: bool = True) -> Path:
     return out
 
 
+def build_issue_bench(verbose: bool = True) -> Path:
+    """The microbenchmark of what issuing tensor-core products costs a warp (csrc/bench/mma_issue.cu), as an
+    executable beside the libraries; returns its path."""
+    src = CSRC / "bench" / "mma_issue.cu"
+    out = build_dir() / f"mma_issue-{_source_hash(src)}"
+    if out.is_file():
+        return out
+    tmp = out.with_name(out.name + f".tmp{os.getpid()}")
+    cmd = [find_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-I", str(CSRC),
+           "-o", str(tmp), str(src)]
+    if verbose:
+        _say("compiling the issue microbenchmark ...")
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        raise KernelBuildError(f"the compiler failed on {src.name}:\n{proc.stdout}")
+    os.replace(tmp, out)
+    for old in out.parent.glob("mma_issue-*"):
+        if old != out and ".tmp" not in old.name:
+            try:
+                old.unlink()
+            except OSError:
+                pass
+    return out
+
+
 def build_all(verbose: bool = True) -> list:
     built = [compile_library(n, verbose) for n in LIBRARIES if (CSRC / LIBRARIES[n]).is_file()]
     built.append(build_cli(verbose))
+    built.append(build_issue_bench(verbose))
     return built
